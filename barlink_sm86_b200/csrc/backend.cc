@@ -1,0 +1,515 @@
+// SPDX-License-Identifier: MIT
+//
+// c10d backend "barlink": routes torch.distributed collectives onto the link
+// core (CUDA tensors) or onto an inner gloo backend (CPU tensors).
+// See backend.h for the contract kept from the reference's Python backend
+// (torch_ext/barlink_sm86/process_group.py:134-520).
+#include "backend.h"
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+namespace blpg {
+
+static blCtx* g_ctx = nullptr;
+blCtx* global_ctx() { return g_ctx; }
+void set_global_ctx(blCtx* ctx) { g_ctx = ctx; }
+
+int dtype_code(at::ScalarType t) {
+  switch (t) {
+    case at::kByte: return BL_DTYPE_U8;
+    case at::kFloat: return BL_DTYPE_FP32;
+    case at::kDouble: return BL_DTYPE_FP64;
+    case at::kBFloat16: return BL_DTYPE_BF16;
+    case at::kHalf: return BL_DTYPE_FP16;
+    case at::kFloat8_e4m3fn: return BL_DTYPE_FP8E4M3;
+    case at::kFloat8_e5m2: return BL_DTYPE_FP8E5M2;
+    default: return -1;
+  }
+}
+
+DoneWork::DoneWork(int rank, c10d::OpType op, std::vector<at::Tensor> outputs)
+    : c10d::Work(rank, op), outputs_(std::move(outputs)) {
+  future_ = c10::make_intrusive<c10::ivalue::Future>(c10::ListType::create(c10::TensorType::get()));
+  future_->markCompleted(c10::IValue(outputs_));
+}
+c10::intrusive_ptr<c10::ivalue::Future> DoneWork::getFuture() { return future_; }
+
+BarlinkBackend::BarlinkBackend(int rank, int size, c10::intrusive_ptr<c10d::Backend> cpu_backend,
+                               bool use_link)
+    : c10d::Backend(rank, size), cpu_(std::move(cpu_backend)), use_link_(use_link) {
+  if (use_link_ && size > 1) {
+    blCtx* c = global_ctx();
+    TORCH_CHECK(c != nullptr, "barlink: the link is not initialised (call init_peer first)");
+    TORCH_CHECK(bl_is_peer(c), "barlink: a process group needs the SPMD link (init_peer), not init()");
+    TORCH_CHECK(bl_world(c) == size && bl_rank(c) == rank,
+                "barlink: process group (rank ", rank, " of ", size,
+                ") does not match the link (rank ", bl_rank(c), " of ", bl_world(c),
+                "); groups smaller than the world are supported only with one member");
+  }
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::done(c10d::OpType op, std::vector<at::Tensor> outs) {
+  return c10::make_intrusive<DoneWork>(getRank(), op, std::move(outs));
+}
+
+c10d::Backend& BarlinkBackend::cpu(const char* what) {
+  TORCH_CHECK(cpu_, "barlink: ", what, " on a CPU tensor needs the gloo companion backend, which this group was created without");
+  ++n_cpu;
+  return *cpu_;
+}
+
+static void* cur_stream(const at::Tensor& t) {
+  return at::cuda::getCurrentCUDAStream(t.device().index()).stream();
+}
+static bool aligned_ok(const at::Tensor& t) {
+  return t.is_contiguous() && (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15u) == 0 &&
+         (t.nbytes() & 15u) == 0 && t.nbytes() > 0;
+}
+#define BL_CALL(expr)                              \
+  do {                                             \
+    char _e[512] = {0};                            \
+    char* err = _e;                                \
+    size_t errlen = sizeof(_e);                    \
+    int _rc = (expr);                              \
+    TORCH_CHECK(_rc == 0, _e[0] ? _e : "barlink: link call failed"); \
+  } while (0)
+
+blCtx* BarlinkBackend::link() {
+  TORCH_CHECK(use_link_,
+              "barlink: this group has no GPU link (it was created on a host without CUDA, with "
+              "BL_CPU_ONLY=1, or it is a subgroup of 2..world-1 ranks, which the link does not serve); "
+              "CUDA tensors cannot be communicated through it");
+  blCtx* c = global_ctx();
+  TORCH_CHECK(c != nullptr, "barlink: the link is not initialised");
+  return c;
+}
+
+// padded flat staging copy of a tensor: numel rounded up so that bytes % 16 == 0
+static at::Tensor padded_copy(const at::Tensor& t) {
+  const int64_t isz = t.element_size();
+  const int64_t per = 16 / std::min<int64_t>(16, isz) > 0 ? 16 / std::min<int64_t>(16, isz) : 1;
+  const int64_t n = t.numel();
+  const int64_t np = (n + per - 1) / per * per;
+  at::Tensor tmp = at::zeros({np}, t.options());
+  tmp.narrow(0, 0, n).copy_(t.reshape({-1}));
+  return tmp;
+}
+
+void BarlinkBackend::allreduce_cuda(at::Tensor& t) {
+  const int code = dtype_code(t.scalar_type());
+  TORCH_CHECK(code >= 0, "barlink: all_reduce does not support dtype ", t.scalar_type(),
+              " (supported: uint8, float16, bfloat16, float32, float64, float8_e4m3fn, float8_e5m2)");
+  if (t.numel() == 0) return;
+  blCtx* c = link();
+  c10::cuda::CUDAGuard guard(t.device());
+  void* st = cur_stream(t);
+  const size_t chunk = bl_max_chunk(c) & ~size_t(15);
+  auto run = [&](char* p, size_t bytes) {
+    for (size_t off = 0; off < bytes; off += chunk) {
+      const size_t len = std::min(chunk, bytes - off);
+      BL_CALL(bl_allreduce_into_peer(c, p + off, p + off, len, code, BL_ALGO_AUTO, st, err, errlen));
+    }
+  };
+  if (aligned_ok(t)) {
+    ++n_zero_copy;
+    run(static_cast<char*>(t.data_ptr()), t.nbytes());
+  } else {
+    ++n_staged;
+    at::Tensor tmp = padded_copy(t);
+    run(static_cast<char*>(tmp.data_ptr()), tmp.nbytes());
+    t.copy_(tmp.narrow(0, 0, t.numel()).view(t.sizes()));
+  }
+}
+
+void BarlinkBackend::allgather_cuda(at::Tensor& out, const at::Tensor& in) {
+  const int world = getSize();
+  TORCH_CHECK(out.numel() == in.numel() * world && out.scalar_type() == in.scalar_type(),
+              "barlink: all_gather output must hold world x input elements of the same dtype");
+  if (in.numel() == 0) return;
+  blCtx* c = link();
+  c10::cuda::CUDAGuard guard(in.device());
+  void* st = cur_stream(in);
+  const size_t slice = (bl_max_chunk(c) / size_t(world)) & ~size_t(15);
+  auto run = [&](const char* ip, char* op, size_t bytes) {
+    for (size_t off = 0; off < bytes; off += slice) {
+      const size_t len = std::min(slice, bytes - off);
+      BL_CALL(bl_allgather_peer(c, ip + off, op + off, len, bytes, st, err, errlen));
+    }
+  };
+  if (aligned_ok(in) && aligned_ok(out)) {
+    ++n_zero_copy;
+    run(static_cast<const char*>(in.data_ptr()), static_cast<char*>(out.data_ptr()), in.nbytes());
+  } else {
+    ++n_staged;
+    at::Tensor ti = padded_copy(in);
+    at::Tensor to = at::empty({world, ti.numel()}, ti.options());
+    run(static_cast<const char*>(ti.data_ptr()), static_cast<char*>(to.data_ptr()), ti.nbytes());
+    out.copy_(to.narrow(1, 0, in.numel()).reshape(out.sizes()));
+  }
+}
+
+void BarlinkBackend::reduce_scatter_cuda(at::Tensor& out, const at::Tensor& in) {
+  const int world = getSize();
+  const int code = dtype_code(in.scalar_type());
+  TORCH_CHECK(code >= 0, "barlink: reduce_scatter does not support dtype ", in.scalar_type());
+  TORCH_CHECK(in.numel() == out.numel() * world && out.scalar_type() == in.scalar_type(),
+              "barlink: reduce_scatter input must hold world x output elements of the same dtype");
+  if (out.numel() == 0) return;
+  blCtx* c = link();
+  c10::cuda::CUDAGuard guard(in.device());
+  void* st = cur_stream(in);
+  const size_t slice = (bl_max_chunk(c) / size_t(world)) & ~size_t(15);
+  auto run = [&](const char* ip, char* op, size_t bytes) {
+    for (size_t off = 0; off < bytes; off += slice) {
+      const size_t len = std::min(slice, bytes - off);
+      BL_CALL(bl_reduce_scatter_peer(c, ip + off, op + off, len, bytes, code, st, err, errlen));
+    }
+  };
+  if (aligned_ok(in) && aligned_ok(out)) {
+    ++n_zero_copy;
+    run(static_cast<const char*>(in.data_ptr()), static_cast<char*>(out.data_ptr()), out.nbytes());
+  } else {
+    ++n_staged;
+    const int64_t n = out.numel();
+    at::Tensor to = padded_copy(out);
+    at::Tensor ti = at::zeros({world, to.numel()}, in.options());
+    ti.narrow(1, 0, n).copy_(in.reshape({world, n}));
+    run(static_cast<const char*>(ti.data_ptr()), static_cast<char*>(to.data_ptr()), to.nbytes());
+    out.copy_(to.narrow(0, 0, n).view(out.sizes()));
+  }
+}
+
+void BarlinkBackend::broadcast_cuda(at::Tensor& t, int root) {
+  if (t.numel() == 0) return;
+  blCtx* c = link();
+  c10::cuda::CUDAGuard guard(t.device());
+  void* st = cur_stream(t);
+  const size_t slice = (bl_max_chunk(c) / size_t(getSize())) & ~size_t(15);
+  auto run = [&](char* p, size_t bytes) {
+    for (size_t off = 0; off < bytes; off += slice) {
+      const size_t len = std::min(slice, bytes - off);
+      BL_CALL(bl_broadcast_peer(c, p + off, len, root, st, err, errlen));
+    }
+  };
+  if (aligned_ok(t)) {
+    ++n_zero_copy;
+    run(static_cast<char*>(t.data_ptr()), t.nbytes());
+  } else {
+    ++n_staged;
+    at::Tensor tmp = padded_copy(t);
+    run(static_cast<char*>(tmp.data_ptr()), tmp.nbytes());
+    if (getRank() != root) t.copy_(tmp.narrow(0, 0, t.numel()).view(t.sizes()));
+  }
+}
+
+static size_t p2p_chunk(blCtx* c) { return bl_p2p_chunk(c) & ~size_t(15); }
+
+void BarlinkBackend::send_cuda(const at::Tensor& t, int dst) {
+  TORCH_CHECK(dst != getRank(), "barlink: send to self is not supported");
+  TORCH_CHECK(dst >= 0 && dst < getSize(), "barlink: send destination ", dst, " out of range");
+  if (t.numel() == 0) return;
+  blCtx* c = link();
+  c10::cuda::CUDAGuard guard(t.device());
+  void* st = cur_stream(t);
+  const size_t chunk = p2p_chunk(c);
+  at::Tensor src = t;
+  if (!aligned_ok(t)) {
+    ++n_staged;
+    src = padded_copy(t);
+  } else {
+    ++n_zero_copy;
+  }
+  const char* p = static_cast<const char*>(src.data_ptr());
+  const size_t bytes = src.nbytes();
+  for (size_t off = 0; off < bytes; off += chunk) {
+    const size_t len = std::min(chunk, bytes - off);
+    BL_CALL(bl_send_into_peer(c, p + off, len, dst, st, err, errlen));
+  }
+  // the caller may overwrite or free the tensor once we return in stream order
+  bl_join_sends(c, st);
+}
+
+void BarlinkBackend::recv_cuda(at::Tensor& t, int src) {
+  TORCH_CHECK(src != getRank(), "barlink: recv from self is not supported");
+  TORCH_CHECK(src >= 0 && src < getSize(), "barlink: recv source ", src, " out of range");
+  if (t.numel() == 0) return;
+  blCtx* c = link();
+  c10::cuda::CUDAGuard guard(t.device());
+  void* st = cur_stream(t);
+  const size_t chunk = p2p_chunk(c);
+  const bool direct = aligned_ok(t);
+  at::Tensor dst = direct ? t : padded_copy(t);
+  direct ? ++n_zero_copy : ++n_staged;
+  char* p = static_cast<char*>(dst.data_ptr());
+  const size_t bytes = dst.nbytes();
+  for (size_t off = 0; off < bytes; off += chunk) {
+    const size_t len = std::min(chunk, bytes - off);
+    BL_CALL(bl_recv_into_peer(c, p + off, len, src, st, err, errlen));
+  }
+  if (!direct) t.copy_(dst.narrow(0, 0, t.numel()).view(t.sizes()));
+}
+
+// ---------------------------------------------------------------------------
+
+static void check_sum(const c10d::ReduceOp& op, const char* what) {
+  TORCH_CHECK(op == c10d::ReduceOp::SUM, "barlink: ", what,
+              " supports only ReduceOp.SUM on CUDA tensors");
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::allreduce(std::vector<at::Tensor>& tensors,
+                                                         const c10d::AllreduceOptions& opts) {
+  TORCH_CHECK(tensors.size() == 1, "barlink: all_reduce takes one tensor");
+  at::Tensor& t = tensors[0];
+  if (getSize() == 1) {
+    ++n_local;
+    return done(c10d::OpType::ALLREDUCE, tensors);
+  }
+  if (t.is_cuda()) {
+    // argument errors surface before any rank has put traffic on the link
+    check_sum(opts.reduceOp, "all_reduce");
+    allreduce_cuda(t);
+    return done(c10d::OpType::ALLREDUCE, tensors);
+  }
+  return cpu("all_reduce").allreduce(tensors, opts);
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::allreduce_coalesced(
+    std::vector<at::Tensor>& tensors, const c10d::AllreduceCoalescedOptions& opts) {
+  if (getSize() == 1) return done(c10d::OpType::ALLREDUCE_COALESCED, tensors);
+  if (!tensors.empty() && tensors[0].is_cuda()) {
+    check_sum(opts.reduceOp, "all_reduce_coalesced");
+    for (auto& t : tensors) allreduce_cuda(t);
+    return done(c10d::OpType::ALLREDUCE_COALESCED, tensors);
+  }
+  return cpu("all_reduce_coalesced").allreduce_coalesced(tensors, opts);
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::broadcast(std::vector<at::Tensor>& tensors,
+                                                         const c10d::BroadcastOptions& opts) {
+  TORCH_CHECK(tensors.size() == 1, "barlink: broadcast takes one tensor");
+  if (getSize() == 1) {
+    ++n_local;
+    return done(c10d::OpType::BROADCAST, tensors);
+  }
+  if (tensors[0].is_cuda()) {
+    TORCH_CHECK(opts.rootRank >= 0 && opts.rootRank < getSize(), "barlink: broadcast root out of range");
+    broadcast_cuda(tensors[0], int(opts.rootRank));
+    return done(c10d::OpType::BROADCAST, tensors);
+  }
+  return cpu("broadcast").broadcast(tensors, opts);
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::barrier(const c10d::BarrierOptions& opts) {
+  if (getSize() == 1) {
+    ++n_local;
+    return done(c10d::OpType::BARRIER, {});
+  }
+  if (use_link_) {
+    blCtx* c = link();
+    void* st = at::cuda::getCurrentCUDAStream().stream();
+    BL_CALL(bl_barrier_peer(c, st, err, errlen));
+    // a c10d barrier is a host-side meeting point as well
+    AT_CUDA_CHECK(cudaStreamSynchronize(static_cast<cudaStream_t>(st)));
+    return done(c10d::OpType::BARRIER, {});
+  }
+  return cpu("barrier").barrier(opts);
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::_allgather_base(at::Tensor& output, at::Tensor& input,
+                                                               const c10d::AllgatherOptions& opts) {
+  if (getSize() == 1) {
+    ++n_local;
+    output.copy_(input.reshape(output.sizes()));
+    return done(c10d::OpType::_ALLGATHER_BASE, {output});
+  }
+  if (input.is_cuda()) {
+    allgather_cuda(output, input);
+    return done(c10d::OpType::_ALLGATHER_BASE, {output});
+  }
+  return cpu("all_gather_into_tensor")._allgather_base(output, input, opts);
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::allgather(
+    std::vector<std::vector<at::Tensor>>& outputs, std::vector<at::Tensor>& inputs,
+    const c10d::AllgatherOptions& opts) {
+  TORCH_CHECK(inputs.size() == 1 && outputs.size() == 1, "barlink: all_gather takes one input tensor");
+  TORCH_CHECK(int(outputs[0].size()) == getSize(), "barlink: all_gather output list must have world entries");
+  if (getSize() == 1) {
+    ++n_local;
+    outputs[0][0].copy_(inputs[0]);
+    return done(c10d::OpType::ALLGATHER, outputs[0]);
+  }
+  if (inputs[0].is_cuda()) {
+    at::Tensor flat = at::empty({getSize(), inputs[0].numel()}, inputs[0].options());
+    at::Tensor in = inputs[0].contiguous();
+    allgather_cuda(flat, in);
+    for (int r = 0; r < getSize(); ++r) outputs[0][r].copy_(flat[r].view(outputs[0][r].sizes()));
+    return done(c10d::OpType::ALLGATHER, outputs[0]);
+  }
+  return cpu("all_gather").allgather(outputs, inputs, opts);
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::allgather_into_tensor_coalesced(
+    std::vector<at::Tensor>& outputs, std::vector<at::Tensor>& inputs,
+    const c10d::AllgatherOptions& opts) {
+  TORCH_CHECK(outputs.size() == inputs.size(), "barlink: coalesced all_gather needs matching lists");
+  if (!inputs.empty() && !inputs[0].is_cuda() && getSize() > 1)
+    return cpu("all_gather_into_tensor_coalesced").allgather_into_tensor_coalesced(outputs, inputs, opts);
+  for (size_t i = 0; i < inputs.size(); ++i) {
+    if (getSize() == 1) outputs[i].copy_(inputs[i].reshape(outputs[i].sizes()));
+    else allgather_cuda(outputs[i], inputs[i]);
+  }
+  return done(c10d::OpType::ALLGATHER_COALESCED, outputs);
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::_reduce_scatter_base(
+    at::Tensor& output, at::Tensor& input, const c10d::ReduceScatterOptions& opts) {
+  if (getSize() == 1) {
+    ++n_local;
+    output.copy_(input.reshape(output.sizes()));
+    return done(c10d::OpType::_REDUCE_SCATTER_BASE, {output});
+  }
+  if (input.is_cuda()) {
+    check_sum(opts.reduceOp, "reduce_scatter");
+    reduce_scatter_cuda(output, input);
+    return done(c10d::OpType::_REDUCE_SCATTER_BASE, {output});
+  }
+  return cpu("reduce_scatter_tensor")._reduce_scatter_base(output, input, opts);
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::reduce_scatter(
+    std::vector<at::Tensor>& outputs, std::vector<std::vector<at::Tensor>>& inputs,
+    const c10d::ReduceScatterOptions& opts) {
+  TORCH_CHECK(outputs.size() == 1 && inputs.size() == 1, "barlink: reduce_scatter takes one output tensor");
+  TORCH_CHECK(int(inputs[0].size()) == getSize(), "barlink: reduce_scatter input list must have world entries");
+  if (getSize() == 1) {
+    ++n_local;
+    outputs[0].copy_(inputs[0][0]);
+    return done(c10d::OpType::REDUCE_SCATTER, outputs);
+  }
+  if (outputs[0].is_cuda()) {
+    check_sum(opts.reduceOp, "reduce_scatter");
+    std::vector<at::Tensor> flat;
+    for (auto& t : inputs[0]) flat.push_back(t.reshape({-1}));
+    at::Tensor in = at::cat(flat, 0);
+    reduce_scatter_cuda(outputs[0], in);
+    return done(c10d::OpType::REDUCE_SCATTER, outputs);
+  }
+  return cpu("reduce_scatter").reduce_scatter(outputs, inputs, opts);
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::reduce_scatter_tensor_coalesced(
+    std::vector<at::Tensor>& outputs, std::vector<at::Tensor>& inputs,
+    const c10d::ReduceScatterOptions& opts) {
+  TORCH_CHECK(outputs.size() == inputs.size(), "barlink: coalesced reduce_scatter needs matching lists");
+  if (!inputs.empty() && !inputs[0].is_cuda() && getSize() > 1)
+    return cpu("reduce_scatter_tensor_coalesced").reduce_scatter_tensor_coalesced(outputs, inputs, opts);
+  if (getSize() > 1) check_sum(opts.reduceOp, "reduce_scatter");
+  for (size_t i = 0; i < inputs.size(); ++i) {
+    if (getSize() == 1) outputs[i].copy_(inputs[i].reshape(outputs[i].sizes()));
+    else reduce_scatter_cuda(outputs[i], inputs[i]);
+  }
+  return done(c10d::OpType::COALESCED, outputs);
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::reduce(std::vector<at::Tensor>& tensors,
+                                                      const c10d::ReduceOptions& opts) {
+  TORCH_CHECK(tensors.size() == 1, "barlink: reduce takes one tensor");
+  if (getSize() == 1) return done(c10d::OpType::REDUCE, tensors);
+  if (tensors[0].is_cuda()) {
+    check_sum(opts.reduceOp, "reduce");
+    // every rank computes the sum; only the root keeps it
+    at::Tensor tmp = tensors[0].clone();
+    allreduce_cuda(tmp);
+    if (getRank() == opts.rootRank) tensors[0].copy_(tmp);
+    return done(c10d::OpType::REDUCE, tensors);
+  }
+  return cpu("reduce").reduce(tensors, opts);
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::gather(std::vector<std::vector<at::Tensor>>& outputs,
+                                                      std::vector<at::Tensor>& inputs,
+                                                      const c10d::GatherOptions& opts) {
+  TORCH_CHECK(inputs.size() == 1, "barlink: gather takes one input tensor");
+  if (getSize() == 1) {
+    if (!outputs.empty()) outputs[0][0].copy_(inputs[0]);
+    return done(c10d::OpType::GATHER, {});
+  }
+  if (inputs[0].is_cuda()) {
+    at::Tensor flat = at::empty({getSize(), inputs[0].numel()}, inputs[0].options());
+    at::Tensor in = inputs[0].contiguous();
+    allgather_cuda(flat, in);
+    if (getRank() == opts.rootRank) {
+      TORCH_CHECK(outputs.size() == 1 && int(outputs[0].size()) == getSize(),
+                  "barlink: gather root needs a list of world output tensors");
+      for (int r = 0; r < getSize(); ++r) outputs[0][r].copy_(flat[r].view(outputs[0][r].sizes()));
+    }
+    return done(c10d::OpType::GATHER, {});
+  }
+  return cpu("gather").gather(outputs, inputs, opts);
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::scatter(std::vector<at::Tensor>& outputs,
+                                                       std::vector<std::vector<at::Tensor>>& inputs,
+                                                       const c10d::ScatterOptions& opts) {
+  TORCH_CHECK(outputs.size() == 1, "barlink: scatter takes one output tensor");
+  if (getSize() == 1) {
+    outputs[0].copy_(inputs[0][0]);
+    return done(c10d::OpType::SCATTER, outputs);
+  }
+  if (outputs[0].is_cuda()) {
+    // the root broadcasts the concatenation, every rank keeps its part
+    at::Tensor all = at::empty({getSize(), outputs[0].numel()}, outputs[0].options());
+    if (getRank() == opts.rootRank) {
+      TORCH_CHECK(inputs.size() == 1 && int(inputs[0].size()) == getSize(),
+                  "barlink: scatter root needs a list of world input tensors");
+      for (int r = 0; r < getSize(); ++r) all[r].copy_(inputs[0][r].reshape({-1}));
+    }
+    broadcast_cuda(all, int(opts.rootRank));
+    outputs[0].copy_(all[getRank()].view(outputs[0].sizes()));
+    return done(c10d::OpType::SCATTER, outputs);
+  }
+  return cpu("scatter").scatter(outputs, inputs, opts);
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::alltoall_base(at::Tensor& output, at::Tensor& input,
+                                                             std::vector<int64_t>& outSplit,
+                                                             std::vector<int64_t>& inSplit,
+                                                             const c10d::AllToAllOptions& opts) {
+  if (getSize() == 1) {
+    output.copy_(input.reshape(output.sizes()));
+    return done(c10d::OpType::ALLTOALL_BASE, {output});
+  }
+  if (!input.is_cuda()) return cpu("all_to_all").alltoall_base(output, input, outSplit, inSplit, opts);
+  TORCH_CHECK(false, "barlink: all_to_all on CUDA tensors is not implemented (no model of this library uses it)");
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::send(std::vector<at::Tensor>& tensors, int dstRank,
+                                                    int tag) {
+  TORCH_CHECK(tensors.size() == 1, "barlink: send takes one tensor");
+  if (tensors[0].is_cuda()) {
+    send_cuda(tensors[0], dstRank);
+    return done(c10d::OpType::SEND, {});
+  }
+  return cpu("send").send(tensors, dstRank, tag);
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::recv(std::vector<at::Tensor>& tensors, int srcRank,
+                                                    int tag) {
+  TORCH_CHECK(tensors.size() == 1, "barlink: recv takes one tensor");
+  if (tensors[0].is_cuda()) {
+    recv_cuda(tensors[0], srcRank);
+    return done(c10d::OpType::RECV, tensors);
+  }
+  return cpu("recv").recv(tensors, srcRank, tag);
+}
+
+c10::intrusive_ptr<c10d::Work> BarlinkBackend::recvAnysource(std::vector<at::Tensor>& tensors,
+                                                             int tag) {
+  TORCH_CHECK(!tensors.empty() && !tensors[0].is_cuda(),
+              "barlink: recv from any source is not supported on CUDA tensors (messages are matched by per-pair order)");
+  return cpu("recv").recvAnysource(tensors, tag);
+}
+
+}  // namespace blpg

@@ -1,0 +1,175 @@
+/* SPDX-License-Identifier: MIT
+ *
+ * Compute ops of barlink for B200: plain-C launchers of the sm_100a kernels
+ * (tcgen05 GEMMs, W8A16, norm / RoPE / activation / attention kernels, fused
+ * GEMM+collective kernels).  Pointers are device pointers, streams are
+ * cudaStream_t passed as void*.  0 on success, -1 with a message otherwise.
+ *
+ * The reference's compute surface is its W8A16 pair (torch_ext/barlink_sm86/
+ * w8a16.cu:165-212); everything else it takes from cuBLAS and HF/vLLM eager
+ * kernels (demos/qwen_tp/qwen38_int8/worker.py:84-129, 208-241).
+ */
+#ifndef BARLINK_B200_OPS_H
+#define BARLINK_B200_OPS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "bl_core.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* D[i, j] = sum_k A[i, k] * B[j, k]; A [ra x k] pitch lda, B [rb x k] pitch
+ * ldb, bf16, K-major.  swap = 0: out[i, j]; swap = 1: out[j, i] (A = weight
+ * rows, B = tokens: the decode orientation).  out is bf16 with pitch ldo.
+ * bias is per output feature, residual has out's layout.  silu_mul: output
+ * features are interleaved (gate, up) pairs and out gets silu(gate)*up in
+ * column feature/2.  bn = 0 and splits = 0 choose automatically.  ws/counters
+ * are the split-K scratch: ws_bytes >= tiles*splits*bn*128*4, counters zeroed
+ * once (the kernel leaves them zero). */
+typedef struct blGemmArgs {
+  const void* a;
+  int ra, lda;
+  const void* b;
+  int rb, ldb;
+  int k;
+  void* out;
+  int ldo;
+  int swap;
+  const void* bias;
+  const void* residual;
+  int silu_mul;
+  int bn;
+  int splits;
+  void* ws;
+  size_t ws_bytes;
+  void* counters;
+  int n_counters;
+  void* err_flag; /* u32 in device or host-mapped memory, set to 1 on a wait that ran out */
+} blGemmArgs;
+int bl_gemm_bf16(const blGemmArgs* a, void* stream, char* err, size_t errlen);
+
+/* W8A16: x [m x k] bf16, wq [n x k] int8 (row = output channel), scale [n]
+ * bf16 (per channel) or scales [k/group x n] fp32 (group > 0).  out [m x n]
+ * bf16.  The int8 tile is widened to bf16 in shared memory inside the main
+ * loop and multiplied on the tensor cores. */
+typedef struct blW8A16Args {
+  const void* x;
+  int m, ldx;
+  const void* wq;
+  int n, k;
+  const void* scale;  /* bf16 [n] */
+  const void* bias;   /* bf16 [n] or null */
+  void* out;
+  int ldo;
+  int silu_mul;
+  int splits;
+  void* ws;
+  size_t ws_bytes;
+  void* counters;
+  int n_counters;
+  void* err_flag;
+} blW8A16Args;
+int bl_w8a16_linear(const blW8A16Args* a, void* stream, char* err, size_t errlen);
+/* reference-compatible pair (w8a16.cu:165-212): per-token int8 activation
+ * quantisation and the int8 x int8 GEMM with group-128 weight scales */
+int bl_w8a16_quant_act(const void* x, int m, int k, void* xq, void* xs, void* stream, char* err,
+                       size_t errlen);
+int bl_w8a16_gemm(const void* xq, const void* xs, const void* wq_t, const void* sw_t, void* out,
+                  int m, int n, int k, int splits, void* ws, void* stream, char* err,
+                  size_t errlen);
+
+/* out = RMSNorm(x (+ residual)) * gamma; when residual is given, x + residual
+ * is also written to residual_out (may alias residual). */
+int bl_rmsnorm(const void* x, const void* residual, const void* gamma, void* out,
+               void* residual_out, int rows, int hidden, float eps, void* stream, char* err,
+               size_t errlen);
+/* qkv [rows x (nq+2*nkv)*hd]: rotate q and k in place (rotate-half RoPE at
+ * positions[rows]) and write k, v into the paged cache at slot[rows]
+ * (slot = block*block_size + offset; negative = skip).  Cache layout
+ * [blocks, nkv, block_size, hd]. */
+int bl_rope_kv_write(void* qkv, const int* positions, const int* slots, void* k_cache,
+                     void* v_cache, int rows, int nq, int nkv, int hd, int block_size, float theta,
+                     void* stream, char* err, size_t errlen);
+/* plain RoPE on [rows x heads x hd] (2-D variant: positions has 2 ints per
+ * row and each half of hd rotates by its own axis) */
+int bl_rope(void* x, const int* positions, int rows, int heads, int hd, int row_stride, float theta,
+            int axes, void* stream, char* err, size_t errlen);
+int bl_silu_mul(const void* gate_up, void* out, int rows, int inter, int interleaved, void* stream,
+                char* err, size_t errlen);
+int bl_embedding(const int* ids, const void* table, void* out, int rows, int hidden, int vocab_lo,
+                 int vocab_hi, void* stream, char* err, size_t errlen);
+/* Decode attention over a paged KV cache.  q rows live in qkv (pitch
+ * q_stride elements), nq query heads share nkv KV heads (nq % nkv == 0,
+ * group <= 16).  block_tables [batch x max_blocks], ctx_lens [batch].
+ * scratch: fp32, batch*nq*splits*(hd+2) floats (splits = 0: chosen here;
+ * returns the number used through *splits_out). */
+int bl_paged_attn_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                         const int* block_tables, const int* ctx_lens, void* out, int batch, int nq,
+                         int nkv, int hd, int block_size, int max_blocks, float scale, int splits,
+                         void* scratch, size_t scratch_bytes, void* stream, char* err,
+                         size_t errlen);
+/* Dense attention (prefill / joint attention): q [tq x nq x hd], k, v
+ * [tk x nkv x hd] per sequence, sequences given by cu_seqlens (batch+1);
+ * causal aligns the last query with the last key. */
+int bl_attn_fwd(const void* q, const void* k, const void* v, void* out, const int* cu_q,
+                const int* cu_k, int batch, int max_q, int nq, int nkv, int hd, int q_stride,
+                int k_stride, int v_stride, int o_stride, float scale, int causal, void* stream,
+                char* err, size_t errlen);
+/* arg max over the last dim of [rows x n] bf16 logits -> idx (int32) and
+ * value (fp32); `offset` is added to the index (vocab-parallel shards). */
+int bl_argmax(const void* logits, int rows, int n, int ld, int offset, int* idx, float* val,
+              void* stream, char* err, size_t errlen);
+
+/* ---- fused GEMM + collective (tensor-parallel linears) ------------------- */
+/* Row-parallel linear fused with reduce-scatter over tokens: every rank
+ * multiplies its K-shard, the epilogue pushes each finished tile straight
+ * into the inbox of the rank that owns those tokens; the owner then sums the
+ * world partials (+ residual), optionally RMS-normalises, and (gather = 1)
+ * pushes its finished rows to every rank's all-gather buffer.  All buffers
+ * named *_off are offsets into the symmetric arena. */
+typedef struct blGemmRsArgs {
+  const void* x;      /* [tokens x k_local] bf16 */
+  int tokens, ldx;
+  const void* w;      /* [n x k_local] bf16 */
+  int n, k_local;
+  size_t inbox_off;   /* arena: [world][tokens_per_rank x n] bf16 partials */
+  void* err_flag;
+  void* ws; size_t ws_bytes; void* counters; int n_counters;
+} blGemmRsArgs;
+int bl_gemm_rs(blCtx* ctx, const blGemmRsArgs* a, void* stream, char* err, size_t errlen);
+/* second half: reduce my token slice from the inbox, add residual, norm,
+ * write residual_out (local) and push normed rows into gather_off of every
+ * rank (or only locally when gather = 0). */
+typedef struct blRsFinishArgs {
+  size_t inbox_off;
+  int tokens, n;           /* full token count (padded to world), hidden */
+  const void* residual_in; /* [tokens_per_rank x n] local rows or null */
+  void* residual_out;      /* [tokens_per_rank x n] */
+  const void* gamma;       /* null: no norm, gather the sum itself */
+  float eps;
+  size_t gather_off;       /* arena: [tokens x n] bf16, filled on every rank */
+  int gather;
+} blRsFinishArgs;
+int bl_rs_finish(blCtx* ctx, const blRsFinishArgs* a, void* stream, char* err, size_t errlen);
+/* Column-parallel linear fused with the all-gather: waits (per source rank)
+ * for the rows that bl_rs_finish pushed, then runs the GEMM on them. */
+typedef struct blAgGemmArgs {
+  size_t gather_off;  /* arena: [tokens x k] bf16 */
+  int tokens, k;
+  const void* w;      /* [n_local x k] */
+  int n_local;
+  const void* bias;
+  void* out; int ldo;
+  int silu_mul;
+  void* err_flag;
+  void* ws; size_t ws_bytes; void* counters; int n_counters;
+} blAgGemmArgs;
+int bl_ag_gemm(blCtx* ctx, const blAgGemmArgs* a, void* stream, char* err, size_t errlen);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

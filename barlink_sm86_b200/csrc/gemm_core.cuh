@@ -1,0 +1,297 @@
+// SPDX-License-Identifier: MIT
+//
+// tcgen05 GEMM core for sm_100a:  D[i, j] = sum_k A[i, k] * B[j, k]
+// with A [ra x K] and B [rb x K] both K-major bf16/fp16 in global memory.
+//
+//   warp 0      TMA producer: 128x64 tile of A and BNx64 tile of B per stage
+//               (128-byte swizzle), ring of kStages shared-memory stages
+//   warp 1      allocates TMEM, one elected lane issues tcgen05.mma
+//               (M=128, N=BN, K=16, fp32 accumulate in TMEM), commits stage
+//               release and accumulator-ready barriers
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (lane = row of A),
+//               hand 32-column chunks to a Sink
+// Two accumulators (2*BN TMEM columns) let the epilogue of one tile overlap
+// the main loop of the next; the kernel is persistent over work units
+// (tile_a, tile_b, k-split).  With k-splits, partial tiles go through an fp32
+// workspace and the CTA that arrives last for a tile reduces them in split
+// order (deterministic) and runs the Sink.
+//
+// The same core serves decode ("swap" orientation: A = weight rows, B = the
+// few tokens, BN = 16..64) and prefill (A = tokens, B = weight rows, BN = 256)
+// and the fused GEMM+collective kernels, which differ only in their Sink.
+//
+// The reference has no tensor-core GEMM of its own: its linears are cuBLAS
+// F.linear / torch._int_mm calls (demos/qwen_tp/qwen38_int8/worker.py:84-93,
+// 224); this file is what replaces those library calls on the hot path.
+#pragma once
+
+#include <cuda.h>
+
+#include "ptx.cuh"
+
+namespace bl {
+
+constexpr int kGemmThreads = 192;
+constexpr int kTileA = 128;
+constexpr int kTileK = 64;
+
+struct GemmShape {
+  int ra, rb, k;            // rows of A, rows of B, reduction length
+  int tiles_a, tiles_b;     // ceil(ra/128), ceil(rb/BN)
+  int kblocks;              // ceil(k/64)
+  int splits;               // k-splits per tile
+  int ab_fmt;               // 1 = bf16, 0 = fp16
+  float* ws;                // [tiles*splits][BN][128] fp32 partials (splits > 1)
+  uint32_t* counters;       // [tiles] arrival counters, zero between launches
+  uint32_t* err;            // set to 1 when a wait inside the kernel ran out
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kStageA = kTileA * kTileK * 2;
+  static constexpr int kStageB = BN * kTileK * 2;
+  static constexpr int kStageBytes = kStageA + kStageB;
+  static constexpr int kStages = (BN <= 64) ? 8 : (BN <= 128 ? 6 : 4);
+  static constexpr int kBarBytes = 1024;
+  // + 1024 so that the tile ring can be aligned to the swizzle atom
+  static constexpr int kBytes = kStages * kStageBytes + kBarBytes + 1024;
+  static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+};
+
+// Sink concept:
+//   __device__ void operator()(int tile_a, int tile_b, int row_in_tile, int col0,
+//                              const float (&v)[32], int ncols) const;
+// called by each of the 128 epilogue threads (row_in_tile = TMEM lane) once per
+// 32-column chunk of a finished tile; all 32 threads of a warp call it together.
+
+template <int BN, class Sink>
+__device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUtensorMap* tmap_b,
+                                          const GemmShape& g, const Sink& sink, uint64_t hint_a,
+                                          uint64_t hint_b) {
+  using S = GemmSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // barriers first, then the 1024-aligned stage ring
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem_raw);
+  uint64_t* empty_bar = full_bar + S::kStages;
+  uint64_t* tfull_bar = empty_bar + S::kStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile uint32_t* s_abort = tmem_slot + 1;
+  uint32_t* s_last = tmem_slot + 2;
+  const uint32_t ring = (smem_u32(smem_raw) + S::kBarBytes + 1023u) & ~1023u;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles = g.tiles_a * g.tiles_b;
+  const int units = tiles * g.splits;
+  const int kb_per = (g.kblocks + g.splits - 1) / g.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 128);
+    }
+    *s_abort = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(tmap_a);
+    tma_prefetch_desc(tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, S::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int armed = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        const int tile = u / g.splits, sp = u - tile * g.splits;
+        const int ta = tile / g.tiles_b, tb = tile - ta * g.tiles_b;
+        const int kb0 = sp * kb_per;
+        const int kb1 = min(g.kblocks, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, s_abort)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full_bar[stage], S::kStageBytes);
+          const uint32_t sa = ring + stage * S::kStageBytes;
+          tma_load_2d_hint_s(sa, tmap_a, smem_u32(&full_bar[stage]), kb * kTileK, ta * kTileA,
+                             hint_a);
+          tma_load_2d_hint_s(sa + S::kStageA, tmap_b, smem_u32(&full_bar[stage]), kb * kTileK,
+                             tb * BN, hint_b);
+          ++armed;
+          if (++stage == S::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // Let copies that are still in flight land before the CTA goes away:
+        // the stages armed in the last lap complete their full barriers.
+        int n = armed < S::kStages ? armed : S::kStages;
+        int s = stage;
+        uint32_t ph = phase;
+        for (int i = 0; i < n; ++i) {
+          if (--s < 0) {
+            s = S::kStages - 1;
+            ph ^= 1u;
+          }
+          for (uint32_t p = 0; p < (1u << 20); ++p)
+            if (mbar_try_wait(&full_bar[s], ph)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ----------------------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_f16(kTileA, BN, g.ab_fmt);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t tphase[2] = {0, 0};
+      int it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++it) {
+        const int tile = u / g.splits, sp = u - tile * g.splits;
+        const int kb0 = sp * kb_per;
+        const int kb1 = min(g.kblocks, kb0 + kb_per);
+        const int acc = it & 1;
+        if (!mbar_wait_bounded(&tempty_bar[acc], tphase[acc] ^ 1u, s_abort)) break;
+        tphase[acc] ^= 1u;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, s_abort)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = ring + stage * S::kStageBytes;
+          const uint64_t da = umma_desc_k_sw128(sa);
+          const uint64_t db = umma_desc_k_sw128(sa + S::kStageA);
+#pragma unroll
+          for (int k = 0; k < kTileK / 16; ++k) {
+            // +32 bytes along K inside the swizzle atom = +2 in the address field
+            umma_f16_ss(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), idesc,
+                        (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == S::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int row = q * 32 + lane;
+    const int et = threadIdx.x - 64;  // 0..127
+    uint32_t tphase[2] = {0, 0};
+    int it = 0;
+    for (int u = blockIdx.x; u < units; u += gridDim.x, ++it) {
+      const int tile = u / g.splits, sp = u - tile * g.splits;
+      const int ta = tile / g.tiles_b, tb = tile - ta * g.tiles_b;
+      const int acc = it & 1;
+      if (!mbar_wait_bounded(&tfull_bar[acc], tphase[acc], s_abort)) break;
+      tphase[acc] ^= 1u;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN);
+      if (g.splits == 1) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          float v[32];
+          if constexpr (BN >= 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c0, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          } else {
+            uint32_t r[16];
+            tmem_ld_32x16(taddr + c0, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+#pragma unroll
+            for (int i = 16; i < 32; ++i) v[i] = 0.f;
+          }
+          sink(ta, tb, row, c0, v, BN < 32 ? BN : 32);
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&tempty_bar[acc]);
+      } else {
+        // partial tile -> workspace [unit][col][row]
+        float* wp = g.ws + size_t(u) * (BN * kTileA);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if constexpr (BN >= 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + c0, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) wp[(c0 + i) * kTileA + row] = __uint_as_float(r[i]);
+          } else {
+            uint32_t r[16];
+            tmem_ld_32x16(taddr + c0, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) wp[(c0 + i) * kTileA + row] = __uint_as_float(r[i]);
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&tempty_bar[acc]);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et == 0) {
+          const uint32_t old = atomicAdd(&g.counters[tile], 1u);
+          *s_last = (old == uint32_t(g.splits - 1)) ? 1u : 0u;
+          if (old == uint32_t(g.splits - 1)) g.counters[tile] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*s_last) {
+          __threadfence();
+          const float* base = g.ws + size_t(tile) * g.splits * (BN * kTileA);
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            for (int s2 = 0; s2 < g.splits; ++s2) {
+              const float* p = base + size_t(s2) * (BN * kTileA) + c0 * kTileA + row;
+#pragma unroll
+              for (int i = 0; i < (BN < 32 ? BN : 32); ++i) v[i] += __ldcg(p + i * kTileA);
+            }
+            sink(ta, tb, row, c0, v, BN < 32 ? BN : 32);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, S::kTmemCols);
+  }
+  if (threadIdx.x == 0 && *s_abort && g.err) *g.err = 1u;
+}
+
+}  // namespace bl

@@ -1,0 +1,319 @@
+// SPDX-License-Identifier: MIT
+//
+// bf16 linear layers on the tcgen05 core: kernel instantiations, the local
+// epilogue (bias / residual / SiLU*mul on interleaved gate-up rows), tensor
+// map cache and launch heuristics.  These are the kernels behind every
+// nn.Linear of the tensor-parallel models; the reference runs the same
+// layers through cuBLAS (demos/qwen_tp/qwen38_int8/worker.py:224) or its
+// dp4a kernel (torch_ext/barlink_sm86/w8a16.cu:94-153).
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "bl_ops.h"
+#include "gemm_core.cuh"
+#include "heap.h"
+
+namespace bl {
+
+// Epilogue that stores to local memory.
+//   swap = 0: A rows are tokens (m), B rows are output features (n)
+//   swap = 1: A rows are output features (n), B rows are tokens (m)
+// out is [tokens, ldo] bf16.  epi bits: 1 bias[n], 2 residual[m, n] added,
+// 4 SiLU(gate)*up where gate/up rows are interleaved (even n = gate, odd n =
+// up) and the result lands in column n/2.
+template <int BN>
+struct LocalSink {
+  __nv_bfloat16* out;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  int ldo, ra, rb, swap, epi;
+
+  __device__ __forceinline__ void operator()(int ta, int tb, int row, int c0, const float (&v)[32],
+                                             int ncols) const {
+    const int i = ta * kTileA + row;
+    const int j0 = tb * BN + c0;
+    if (!swap) {
+      const int m = i;
+      if (m >= ra) return;
+      if (epi & 4) {
+        // pairs (gate, up) sit in adjacent columns of this thread
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          const int n = j0 + c;
+          if (c < ncols && n + 1 < rb) {
+            float gte = v[c], up = v[c + 1];
+            if (epi & 1) {
+              gte += __bfloat162float(bias[n]);
+              up += __bfloat162float(bias[n + 1]);
+            }
+            const float r = gte / (1.f + __expf(-gte)) * up;
+            out[size_t(m) * ldo + (n >> 1)] = __float2bfloat16(r);
+          }
+        }
+        return;
+      }
+      __nv_bfloat16* orow = out + size_t(m) * ldo;
+      const __nv_bfloat16* rrow = residual ? residual + size_t(m) * ldo : nullptr;
+      if (ncols == 32 && j0 + 32 <= rb && (ldo & 7) == 0) {
+#pragma unroll
+        for (int c = 0; c < 32; c += 8) {
+          float x[8];
+#pragma unroll
+          for (int t = 0; t < 8; ++t) x[t] = v[c + t];
+          if (epi & 1) {
+            const uint4 b = *reinterpret_cast<const uint4*>(bias + j0 + c);
+            const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z),
+                         b3 = unpack_bf16x2(b.w);
+            x[0] += b0.x; x[1] += b0.y; x[2] += b1.x; x[3] += b1.y;
+            x[4] += b2.x; x[5] += b2.y; x[6] += b3.x; x[7] += b3.y;
+          }
+          if (epi & 2) {
+            const uint4 b = *reinterpret_cast<const uint4*>(rrow + j0 + c);
+            const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z),
+                         b3 = unpack_bf16x2(b.w);
+            x[0] += b0.x; x[1] += b0.y; x[2] += b1.x; x[3] += b1.y;
+            x[4] += b2.x; x[5] += b2.y; x[6] += b3.x; x[7] += b3.y;
+          }
+          *reinterpret_cast<uint4*>(orow + j0 + c) =
+              make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]),
+                         pack_bf16x2(x[6], x[7]));
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int n = j0 + c;
+          if (c < ncols && n < rb) {
+            float x = v[c];
+            if (epi & 1) x += __bfloat162float(bias[n]);
+            if (epi & 2) x += __bfloat162float(rrow[n]);
+            orow[n] = __float2bfloat16(x);
+          }
+        }
+      }
+    } else {
+      const int n = i;
+      const bool nok = n < ra;
+      const float bv = (nok && (epi & 1)) ? __bfloat162float(bias[n]) : 0.f;
+      if (epi & 4) {
+        // even lane holds the gate row, odd lane the matching up row
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float mine = v[c] + bv;
+          const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+          const int m = j0 + c;
+          if (c < ncols && m < rb && nok && !(row & 1)) {
+            const float r = mine / (1.f + __expf(-mine)) * other;
+            out[size_t(m) * ldo + (n >> 1)] = __float2bfloat16(r);
+          }
+        }
+        return;
+      }
+      if (!nok) return;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        const int m = j0 + c;
+        if (c < ncols && m < rb) {
+          float x = v[c] + bv;
+          if (epi & 2) x += __bfloat162float(residual[size_t(m) * ldo + n]);
+          out[size_t(m) * ldo + n] = __float2bfloat16(x);
+        }
+      }
+    }
+  }
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    k_gemm(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+           GemmShape g, LocalSink<BN> sink, uint64_t hint_a, uint64_t hint_b) {
+  gemm_body<BN>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
+}
+
+// ---------------------------------------------------------------------------
+// tensor map cache
+// ---------------------------------------------------------------------------
+struct TmapKey {
+  const void* ptr;
+  uint64_t rows, cols, ld;
+  uint32_t box_rows, esize;
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld &&
+           box_rows == o.box_rows && esize == o.esize;
+  }
+};
+struct TmapHash {
+  size_t operator()(const TmapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h = h * 1000003u ^ k.rows;
+    h = h * 1000003u ^ k.cols;
+    h = h * 1000003u ^ k.ld;
+    h = h * 1000003u ^ k.box_rows;
+    return h * 31u + k.esize;
+  }
+};
+static std::unordered_map<TmapKey, CUtensorMap, TmapHash> g_tmaps;
+static std::mutex g_tmap_mu;
+
+// K-major matrix [rows x cols] of 1- or 2-byte elements, row pitch ld
+// elements, box = box_rows x 128 bytes, 128-byte swizzle.
+int make_tmap_kmajor(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                     uint32_t esize, CUtensorMap* out, char* err, size_t errlen) {
+  TmapKey key{ptr, rows, cols, ld, box_rows, esize};
+  {
+    std::lock_guard<std::mutex> g(g_tmap_mu);
+    auto it = g_tmaps.find(key);
+    if (it != g_tmaps.end()) {
+      *out = it->second;
+      return 0;
+    }
+  }
+  const DriverApi* d = driver(err, errlen);
+  if (!d) return -1;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) || ((ld * esize) & 15u)) {
+    set_err(err, errlen,
+            "barlink: GEMM operand must be 16-byte aligned with a row pitch that is a multiple of 16 bytes (ptr %p, pitch %llu B)",
+            ptr, (unsigned long long)(ld * esize));
+    return -1;
+  }
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * esize};
+  cuuint32_t box[2] = {128u / esize, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = d->cuTensorMapEncodeTiled(
+      &m, esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+      const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    const char* s = nullptr;
+    d->cuGetErrorString(r, &s);
+    set_err(err, errlen, "barlink: cuTensorMapEncodeTiled(rows %llu, cols %llu, box %u) failed: %s",
+            (unsigned long long)rows, (unsigned long long)cols, box_rows, s ? s : "?");
+    return -1;
+  }
+  {
+    std::lock_guard<std::mutex> g(g_tmap_mu);
+    if (g_tmaps.size() > 65536) g_tmaps.clear();
+    g_tmaps[key] = m;
+  }
+  *out = m;
+  return 0;
+}
+
+static int g_sm_count = 0;
+int sm_count() {
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (g_sm_count <= 0) g_sm_count = 148;
+  }
+  return g_sm_count;
+}
+
+// splits such that tiles*splits fills the SMs once and every split is non-empty
+int pick_splits(int tiles, int kblocks, int sms, int want) {
+  int s = want;
+  if (s <= 0) {
+    s = 1;
+    if (tiles * 2 <= sms) {
+      s = sms / tiles;
+      const int max_by_k = kblocks / 4 > 0 ? kblocks / 4 : 1;  // >= 4 k-blocks per split
+      if (s > max_by_k) s = max_by_k;
+    }
+  }
+  if (s > kblocks) s = kblocks;
+  if (s < 1) s = 1;
+  const int per = (kblocks + s - 1) / s;
+  return (kblocks + per - 1) / per;
+}
+
+template <int BN>
+static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, char* err,
+                       size_t errlen) {
+  using S = GemmSmem<BN>;
+  CUtensorMap ta, tb;
+  if (make_tmap_kmajor(a.a, a.ra, a.k, a.lda, kTileA, 2, &ta, err, errlen) != 0) return -1;
+  if (make_tmap_kmajor(a.b, a.rb, a.k, a.ldb, BN, 2, &tb, err, errlen) != 0) return -1;
+  GemmShape g;
+  g.ra = a.ra;
+  g.rb = a.rb;
+  g.k = a.k;
+  g.tiles_a = (a.ra + kTileA - 1) / kTileA;
+  g.tiles_b = (a.rb + BN - 1) / BN;
+  g.kblocks = (a.k + kTileK - 1) / kTileK;
+  const int tiles = g.tiles_a * g.tiles_b;
+  const int sms = sm_count();
+  g.splits = pick_splits(tiles, g.kblocks, sms, splits_want);
+  if (g.splits > 1) {
+    const size_t need = size_t(tiles) * g.splits * BN * kTileA * sizeof(float);
+    if (!a.ws || a.ws_bytes < need || !a.counters || a.n_counters < tiles) g.splits = 1;
+  }
+  g.ab_fmt = 1;
+  g.ws = static_cast<float*>(a.ws);
+  g.counters = static_cast<uint32_t*>(a.counters);
+  g.err = static_cast<uint32_t*>(a.err_flag);
+  LocalSink<BN> sink;
+  sink.out = static_cast<__nv_bfloat16*>(a.out);
+  sink.bias = static_cast<const __nv_bfloat16*>(a.bias);
+  sink.residual = static_cast<const __nv_bfloat16*>(a.residual);
+  sink.ldo = a.ldo;
+  sink.ra = a.ra;
+  sink.rb = a.rb;
+  sink.swap = a.swap;
+  sink.epi = (a.bias ? 1 : 0) | (a.residual ? 2 : 0) | (a.silu_mul ? 4 : 0);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(k_gemm<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         S::kBytes);
+    if (e != cudaSuccess) {
+      set_err(err, errlen, "barlink: cannot raise shared memory to %d B: %s", S::kBytes,
+              cudaGetErrorString(e));
+      return -1;
+    }
+    attr_set = true;
+  }
+  const int units = tiles * g.splits;
+  const int grid = units < sms ? units : sms;
+  // weights stream through L2 once, activations are re-read by every CTA
+  const uint64_t hint_w = kHintEvictFirst, hint_x = kHintEvictLast;
+  k_gemm<BN><<<grid, kGemmThreads, S::kBytes, st>>>(ta, tb, g, sink, a.swap ? hint_w : hint_x,
+                                                    a.swap ? hint_x : hint_w);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_err(err, errlen, "barlink: GEMM launch failed: %s", cudaGetErrorString(e));
+    return -1;
+  }
+  return 0;
+}
+
+}  // namespace bl
+
+using namespace bl;
+
+extern "C" int bl_gemm_bf16(const blGemmArgs* a, void* stream, char* err, size_t errlen) {
+  if (!a || !a->a || !a->b || !a->out || a->ra < 1 || a->rb < 1 || a->k < 8 || (a->k & 7)) {
+    set_err(err, errlen, "barlink: gemm needs non-null operands and K a multiple of 8");
+    return -1;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int bn = a->bn;
+  if (bn <= 0) {
+    if (a->swap) bn = a->rb <= 16 ? 16 : a->rb <= 32 ? 32 : a->rb <= 64 ? 64 : a->rb <= 128 ? 128 : 256;
+    else bn = a->rb >= 256 ? 256 : a->rb > 64 ? 128 : 64;
+  }
+  switch (bn) {
+    case 16: return launch_gemm<16>(*a, a->splits, st, err, errlen);
+    case 32: return launch_gemm<32>(*a, a->splits, st, err, errlen);
+    case 64: return launch_gemm<64>(*a, a->splits, st, err, errlen);
+    case 128: return launch_gemm<128>(*a, a->splits, st, err, errlen);
+    case 256: return launch_gemm<256>(*a, a->splits, st, err, errlen);
+    default:
+      set_err(err, errlen, "barlink: gemm tile width %d not in {16,32,64,128,256}", bn);
+      return -1;
+  }
+}

@@ -1,0 +1,671 @@
+// SPDX-License-Identifier: MIT
+//
+// Decode-path kernels for sm_100a that are bandwidth bound rather than GEMM
+// shaped: RMSNorm (+residual), RoPE fused with the paged-KV write, SiLU*mul,
+// embedding gather, arg max, and paged-KV decode attention (tensor-core
+// QK^T/PV on 16-token pages, split over the context, log-sum-exp merge).
+// The reference takes all of these from HF transformers / vLLM eager kernels
+// (about 29 k launches per token, BUILD_AND_TEST.md:373-376); here each is
+// one launch per layer.
+#include <stdio.h>
+
+#include "bl_ops.h"
+#include "heap.h"
+#include "ptx.cuh"
+
+namespace bl {
+
+#define OPS_LAUNCH_CHECK(what)                                                         \
+  do {                                                                                 \
+    cudaError_t _e = cudaGetLastError();                                               \
+    if (_e != cudaSuccess) {                                                           \
+      set_err(err, errlen, "barlink: %s launch failed: %s", what, cudaGetErrorString(_e)); \
+      return -1;                                                                       \
+    }                                                                                  \
+  } while (0)
+
+// ---------------------------------------------------------------------------
+// RMSNorm (+ residual add)
+// ---------------------------------------------------------------------------
+constexpr int kNormMaxVpt = 4;
+
+__global__ void __launch_bounds__(512) k_rmsnorm(const uint4* __restrict__ x,
+                                                 const uint4* __restrict__ residual,
+                                                 const uint4* __restrict__ gamma,
+                                                 uint4* __restrict__ out,
+                                                 uint4* __restrict__ residual_out, int vpr,
+                                                 float eps) {
+  __shared__ float s_part[16];
+  __shared__ float s_rstd;
+  const size_t row = blockIdx.x;
+  float v[kNormMaxVpt][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < kNormMaxVpt; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < vpr) {
+      const uint4 a = x[row * vpr + i];
+      float2 p0 = unpack_bf16x2(a.x), p1 = unpack_bf16x2(a.y), p2 = unpack_bf16x2(a.z),
+             p3 = unpack_bf16x2(a.w);
+      float f[8] = {p0.x, p0.y, p1.x, p1.y, p2.x, p2.y, p3.x, p3.y};
+      if (residual) {
+        const uint4 b = residual[row * vpr + i];
+        float2 q0 = unpack_bf16x2(b.x), q1 = unpack_bf16x2(b.y), q2 = unpack_bf16x2(b.z),
+               q3 = unpack_bf16x2(b.w);
+        const float r[8] = {q0.x, q0.y, q1.x, q1.y, q2.x, q2.y, q3.x, q3.y};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] += r[j];
+        const uint4 packed = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
+                                        pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+        residual_out[row * vpr + i] = packed;
+        // the norm sees the stored (rounded) sum
+        p0 = unpack_bf16x2(packed.x); p1 = unpack_bf16x2(packed.y);
+        p2 = unpack_bf16x2(packed.z); p3 = unpack_bf16x2(packed.w);
+        f[0] = p0.x; f[1] = p0.y; f[2] = p1.x; f[3] = p1.y;
+        f[4] = p2.x; f[5] = p2.y; f[6] = p3.x; f[7] = p3.y;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[k][j] = f[j];
+        ss += f[j] * f[j];
+      }
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? s_part[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) s_rstd = rsqrtf(t / float(vpr * 8) + eps);
+  }
+  __syncthreads();
+  const float rstd = s_rstd;
+#pragma unroll
+  for (int k = 0; k < kNormMaxVpt; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < vpr) {
+      const uint4 gm = gamma[i];
+      const float2 g0 = unpack_bf16x2(gm.x), g1 = unpack_bf16x2(gm.y), g2 = unpack_bf16x2(gm.z),
+                   g3 = unpack_bf16x2(gm.w);
+      const float gg[8] = {g0.x, g0.y, g1.x, g1.y, g2.x, g2.y, g3.x, g3.y};
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        o[j] = __bfloat162float(__float2bfloat16(v[k][j] * rstd)) * gg[j];
+      out[row * vpr + i] = make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]),
+                                      pack_bf16x2(o[4], o[5]), pack_bf16x2(o[6], o[7]));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// RoPE (rotate-half) on q and k of a fused qkv row + paged KV write
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) k_rope_kv_write(__nv_bfloat16* __restrict__ qkv,
+                                                       const int* __restrict__ positions,
+                                                       const int* __restrict__ slots,
+                                                       __nv_bfloat16* __restrict__ k_cache,
+                                                       __nv_bfloat16* __restrict__ v_cache, int nq,
+                                                       int nkv, int hd, int block_size,
+                                                       float log2_theta) {
+  const int row = blockIdx.x;
+  const int half = hd >> 1;
+  const int groups = blockDim.x / half;  // heads handled in parallel
+  const int i = threadIdx.x % half;
+  const int grp = threadIdx.x / half;
+  __nv_bfloat16* base = qkv + size_t(row) * (nq + 2 * nkv) * hd;
+  const int slot = slots ? slots[row] : -1;
+  const int blk = slot >= 0 ? slot / block_size : 0;
+  const int off = slot >= 0 ? slot % block_size : 0;
+  if (grp < groups) {
+    const float pos = float(positions[row]);
+    const float inv = exp2f(-log2_theta * (2.f * float(i) / float(hd)));
+    float sn, cs;
+    sincosf(pos * inv, &sn, &cs);
+    for (int h = grp; h < nq + nkv; h += groups) {
+      __nv_bfloat16* p = base + size_t(h) * hd;
+      const float x1 = __bfloat162float(p[i]), x2 = __bfloat162float(p[i + half]);
+      const __nv_bfloat16 o1 = __float2bfloat16(x1 * cs - x2 * sn);
+      const __nv_bfloat16 o2 = __float2bfloat16(x2 * cs + x1 * sn);
+      p[i] = o1;
+      p[i + half] = o2;
+      if (h >= nq && slot >= 0) {
+        __nv_bfloat16* c =
+            k_cache + ((size_t(blk) * nkv + (h - nq)) * block_size + off) * hd;
+        c[i] = o1;
+        c[i + half] = o2;
+      }
+    }
+  }
+  if (slot >= 0) {
+    // v: plain copy, 16 bytes per thread
+    const int vec_per_head = hd / 8;
+    for (int t = threadIdx.x; t < nkv * vec_per_head; t += blockDim.x) {
+      const int h = t / vec_per_head, c = t % vec_per_head;
+      const uint4 val = *reinterpret_cast<const uint4*>(base + size_t(nq + nkv + h) * hd + c * 8);
+      *reinterpret_cast<uint4*>(v_cache + ((size_t(blk) * nkv + h) * block_size + off) * hd +
+                                c * 8) = val;
+    }
+  }
+}
+
+// plain RoPE; axes = 2 rotates each half of the head by its own position
+__global__ void __launch_bounds__(128) k_rope(__nv_bfloat16* __restrict__ x,
+                                              const int* __restrict__ positions, int heads, int hd,
+                                              int row_stride, float log2_theta, int axes) {
+  const int row = blockIdx.x;
+  const int sub = hd / axes;   // dims rotated by one axis
+  const int half = sub >> 1;
+  const int pairs = half * axes;
+  for (int t = threadIdx.x; t < heads * pairs; t += blockDim.x) {
+    const int h = t / pairs, r = t % pairs;
+    const int ax = r / half, i = r % half;
+    const float pos = float(positions[row * axes + ax]);
+    const float inv = exp2f(-log2_theta * (2.f * float(i) / float(sub)));
+    float sn, cs;
+    sincosf(pos * inv, &sn, &cs);
+    __nv_bfloat16* p = x + size_t(row) * row_stride + size_t(h) * hd + ax * sub;
+    const float x1 = __bfloat162float(p[i]), x2 = __bfloat162float(p[i + half]);
+    p[i] = __float2bfloat16(x1 * cs - x2 * sn);
+    p[i + half] = __float2bfloat16(x2 * cs + x1 * sn);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// SiLU(gate) * up
+// ---------------------------------------------------------------------------
+__global__ void k_silu_mul(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                           int rows, int inter, int interleaved) {
+  const size_t total = size_t(rows) * inter;
+  for (size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+       t += size_t(gridDim.x) * blockDim.x) {
+    const size_t r = t / inter, c = t % inter;
+    float g, u;
+    if (interleaved) {
+      const __nv_bfloat162 p = *reinterpret_cast<const __nv_bfloat162*>(gu + r * 2 * inter + 2 * c);
+      g = __bfloat162float(p.x);
+      u = __bfloat162float(p.y);
+    } else {
+      g = __bfloat162float(gu[r * 2 * inter + c]);
+      u = __bfloat162float(gu[r * 2 * inter + inter + c]);
+    }
+    out[t] = __float2bfloat16(g / (1.f + __expf(-g)) * u);
+  }
+}
+
+__global__ void k_embedding(const int* __restrict__ ids, const uint4* __restrict__ table,
+                            uint4* __restrict__ out, int vpr, int lo, int hi) {
+  const int row = blockIdx.x;
+  const int id = ids[row];
+  const bool mine = id >= lo && id < hi;
+  for (int i = threadIdx.x; i < vpr; i += blockDim.x)
+    out[size_t(row) * vpr + i] = mine ? table[size_t(id - lo) * vpr + i] : make_uint4(0, 0, 0, 0);
+}
+
+// ---------------------------------------------------------------------------
+// arg max (ties: lowest index)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) k_argmax(const __nv_bfloat16* __restrict__ logits, int n,
+                                                 int ld, int offset, int* __restrict__ idx,
+                                                 float* __restrict__ val) {
+  __shared__ float s_v[32];
+  __shared__ int s_i[32];
+  const __nv_bfloat16* p = logits + size_t(blockIdx.x) * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float f = __bfloat162float(p[i]);
+    if (f > best || (f == best && i < bi)) {
+      best = f;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if ((threadIdx.x & 31) == 0) {
+    s_v[threadIdx.x >> 5] = best;
+    s_i[threadIdx.x >> 5] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = threadIdx.x < (blockDim.x >> 5) ? s_v[threadIdx.x] : -INFINITY;
+    bi = threadIdx.x < (blockDim.x >> 5) ? s_i[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) {
+        best = ov;
+        bi = oi;
+      }
+    }
+    if (threadIdx.x == 0) {
+      idx[blockIdx.x] = bi + offset;
+      val[blockIdx.x] = best;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// paged decode attention
+// ---------------------------------------------------------------------------
+constexpr int kPageTokens = 16;
+constexpr int kHd = 128;
+constexpr int kRowPitch = kHd * 2 + 16;               // bytes, padded against bank conflicts
+constexpr int kPageBytes = kPageTokens * kRowPitch;   // one K or V page in shared memory
+constexpr int kWarpSmem = 4 * kPageBytes;             // K,V x 2 buffers
+constexpr int kAttnWarps = 4;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                        uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                          uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// grid (nkv, batch, splits), 128 threads.  Each warp walks its own pages with
+// a private double buffer (cp.async), the four warps are merged through
+// shared memory, splits through `scratch` and k_attn_merge.
+__global__ void __launch_bounds__(kAttnWarps * 32)
+    k_paged_attn_decode(const __nv_bfloat16* __restrict__ q, int q_stride,
+                        const __nv_bfloat16* __restrict__ k_cache,
+                        const __nv_bfloat16* __restrict__ v_cache,
+                        const int* __restrict__ block_tables, const int* __restrict__ ctx_lens,
+                        __nv_bfloat16* __restrict__ out, float* __restrict__ scratch, int nq,
+                        int nkv, int max_blocks, float scale_log2) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int h = blockIdx.x, b = blockIdx.y, sp = blockIdx.z, nsplit = gridDim.z;
+  const int G = nq / nkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int ctx = ctx_lens[b];
+  const int n_pages = (ctx + kPageTokens - 1) / kPageTokens;
+  const int per = (n_pages + nsplit - 1) / nsplit;
+  const int p0 = sp * per;
+  const int p1 = min(n_pages, p0 + per);
+  const int* table = block_tables + size_t(b) * max_blocks;
+
+  // Q fragments (rows = heads of this group, zero beyond G)
+  uint32_t qa[kHd / 16][4];
+  {
+    const __nv_bfloat16* qb = q + size_t(b) * q_stride + size_t(h) * G * kHd;
+#pragma unroll
+    for (int ks = 0; ks < kHd / 16; ++ks) {
+      const int c = ks * 16 + 2 * t;
+      qa[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(qb + g * kHd + c) : 0u;
+      qa[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * kHd + c) : 0u;
+      qa[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(qb + g * kHd + c + 8) : 0u;
+      qa[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * kHd + c + 8) : 0u;
+    }
+  }
+  float o[kHd / 8][4];
+#pragma unroll
+  for (int d = 0; d < kHd / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  const uint32_t wbase = smem_u32(smem) + warp * kWarpSmem;
+  auto issue = [&](int page, int buf) {
+    const int blk = table[page];
+    const uint8_t* ks = reinterpret_cast<const uint8_t*>(k_cache) +
+                        (size_t(blk) * nkv + h) * (kPageTokens * kHd * 2);
+    const uint8_t* vs = reinterpret_cast<const uint8_t*>(v_cache) +
+                        (size_t(blk) * nkv + h) * (kPageTokens * kHd * 2);
+    const uint32_t kd = wbase + buf * 2 * kPageBytes, vd = kd + kPageBytes;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = lane + i * 32;  // 256 chunks of 16 B per page
+      const int r = c >> 4, cc = c & 15;
+      cp_async16(kd + r * kRowPitch + cc * 16, ks + c * 16);
+      cp_async16(vd + r * kRowPitch + cc * 16, vs + c * 16);
+    }
+    cp_async_commit();
+  };
+
+  int page = p0 + warp;
+  int buf = 0;
+  if (page < p1) issue(page, 0);
+  for (; page < p1; page += kAttnWarps, buf ^= 1) {
+    const int nxt = page + kAttnWarps;
+    if (nxt < p1) {
+      issue(nxt, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncwarp();
+    const uint32_t kd = wbase + buf * 2 * kPageBytes, vd = kd + kPageBytes;
+    // S = Q K^T for 16 tokens (two n8 tiles)
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    {
+      const int mi = lane >> 3, r = lane & 7;
+      const uint32_t a0 = kd + ((mi >> 1) * 8 + r) * kRowPitch + (mi & 1) * 16;
+#pragma unroll
+      for (int ks = 0; ks < kHd / 16; ++ks) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(a0 + ks * 32, b0, b1, b2, b3);
+        mma_bf16_16816(s[0], qa[ks], b0, b1);
+        mma_bf16_16816(s[1], qa[ks], b2, b3);
+      }
+    }
+    // mask, online softmax
+    const int tok0 = page * kPageTokens;
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int tok = tok0 + nt * 8 + 2 * t + (e & 1);
+        float x = s[nt][e] * scale_log2;
+        if (tok >= ctx) x = -INFINITY;
+        s[nt][e] = x;
+        if (e < 2) mx0 = fmaxf(mx0, x);
+        else mx1 = fmaxf(mx1, x);
+      }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+    const float al0 = exp2f(m0 - n0), al1 = exp2f(m1 - n1);  // m = -inf -> 0
+    m0 = n0;
+    m1 = n1;
+    float ps0 = 0.f, ps1 = 0.f;
+    uint32_t pa[4];
+    {
+      float pv[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        pv[nt][0] = exp2f(s[nt][0] - n0);
+        pv[nt][1] = exp2f(s[nt][1] - n0);
+        pv[nt][2] = exp2f(s[nt][2] - n1);
+        pv[nt][3] = exp2f(s[nt][3] - n1);
+        ps0 += pv[nt][0] + pv[nt][1];
+        ps1 += pv[nt][2] + pv[nt][3];
+      }
+      pa[0] = pack_bf16x2(pv[0][0], pv[0][1]);
+      pa[1] = pack_bf16x2(pv[0][2], pv[0][3]);
+      pa[2] = pack_bf16x2(pv[1][0], pv[1][1]);
+      pa[3] = pack_bf16x2(pv[1][2], pv[1][3]);
+    }
+    l0 = l0 * al0 + ps0;
+    l1 = l1 * al1 + ps1;
+#pragma unroll
+    for (int d = 0; d < kHd / 8; ++d) {
+      o[d][0] *= al0;
+      o[d][1] *= al0;
+      o[d][2] *= al1;
+      o[d][3] *= al1;
+    }
+    // O += P V
+    {
+      const int mi = lane >> 3, r = lane & 7;
+      const uint32_t a0 = vd + ((mi & 1) * 8 + r) * kRowPitch + (mi >> 1) * 16;
+#pragma unroll
+      for (int d = 0; d < kHd / 8; d += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(a0 + d * 16, b0, b1, b2, b3);
+        mma_bf16_16816(o[d], pa, b0, b1);
+        mma_bf16_16816(o[d + 1], pa, b2, b3);
+      }
+    }
+    __syncwarp();
+  }
+  // row sums live spread over the quad
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+  // ---- merge the four warps ----------------------------------------------
+  float* wo = reinterpret_cast<float*>(smem + warp * kWarpSmem);  // [16][128] + m[16] + l[16]
+  float* wm = wo + 16 * kHd;
+  float* wl = wm + 16;
+#pragma unroll
+  for (int d = 0; d < kHd / 8; ++d) {
+    *reinterpret_cast<float2*>(wo + g * kHd + d * 8 + 2 * t) = make_float2(o[d][0], o[d][1]);
+    *reinterpret_cast<float2*>(wo + (g + 8) * kHd + d * 8 + 2 * t) = make_float2(o[d][2], o[d][3]);
+  }
+  if (t == 0) {
+    wm[g] = m0;
+    wm[g + 8] = m1;
+    wl[g] = l0;
+    wl[g + 8] = l1;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < G * kHd; e += blockDim.x) {
+    const int r = e / kHd, d = e % kHd;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w)
+      M = fmaxf(M, reinterpret_cast<const float*>(smem + w * kWarpSmem)[16 * kHd + r]);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float* base = reinterpret_cast<const float*>(smem + w * kWarpSmem);
+      const float mw = base[16 * kHd + r];
+      const float sc = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      L += base[16 * kHd + 16 + r] * sc;
+      acc += base[r * kHd + d] * sc;
+    }
+    const int head = h * G + r;
+    if (nsplit == 1) {
+      out[size_t(b) * nq * kHd + size_t(head) * kHd + d] =
+          __float2bfloat16(L > 0.f ? acc / L : 0.f);
+    } else {
+      float* sc = scratch + ((size_t(b) * nq + head) * nsplit + sp) * (kHd + 2);
+      sc[d] = acc;
+      if (d == 0) {
+        sc[kHd] = M;
+        sc[kHd + 1] = L;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kHd) k_attn_merge(const float* __restrict__ scratch,
+                                                    __nv_bfloat16* __restrict__ out, int nsplit) {
+  const size_t bh = blockIdx.x;  // batch*nq + head
+  const float* base = scratch + bh * nsplit * (kHd + 2);
+  const int d = threadIdx.x;
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, base[s * (kHd + 2) + kHd]);
+  float L = 0.f, acc = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float mw = base[s * (kHd + 2) + kHd];
+    const float sc = mw == -INFINITY ? 0.f : exp2f(mw - M);
+    L += base[s * (kHd + 2) + kHd + 1] * sc;
+    acc += base[s * (kHd + 2) + d] * sc;
+  }
+  out[bh * kHd + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
+}
+
+// merge per-rank (value, index) pairs of a vocab-parallel arg max:
+// pairs [world][rows] as float2(value, index-as-int-bits)
+__global__ void k_argmax_merge(const float2* __restrict__ pairs, int world, int rows,
+                               int* __restrict__ idx) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int w = 0; w < world; ++w) {
+    const float2 p = pairs[size_t(w) * rows + r];
+    const int i = __float_as_int(p.y);
+    if (p.x > best || (p.x == best && i < bi)) {
+      best = p.x;
+      bi = i;
+    }
+  }
+  idx[r] = bi;
+}
+
+}  // namespace bl
+
+using namespace bl;
+
+extern "C" int bl_rmsnorm(const void* x, const void* residual, const void* gamma, void* out,
+                          void* residual_out, int rows, int hidden, float eps, void* stream,
+                          char* err, size_t errlen) {
+  if (rows < 1 || hidden < 8 || (hidden & 7) || hidden / 8 > 512 * kNormMaxVpt) {
+    set_err(err, errlen, "barlink: rmsnorm needs hidden %% 8 == 0 and hidden <= %d", 512 * kNormMaxVpt * 8);
+    return -1;
+  }
+  const int vpr = hidden / 8;
+  int threads = (vpr + 31) / 32 * 32;
+  if (threads > 512) threads = 512;
+  k_rmsnorm<<<rows, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), static_cast<const uint4*>(residual),
+      static_cast<const uint4*>(gamma), static_cast<uint4*>(out), static_cast<uint4*>(residual_out),
+      vpr, eps);
+  OPS_LAUNCH_CHECK("rmsnorm");
+  return 0;
+}
+
+extern "C" int bl_rope_kv_write(void* qkv, const int* positions, const int* slots, void* k_cache,
+                                void* v_cache, int rows, int nq, int nkv, int hd, int block_size,
+                                float theta, void* stream, char* err, size_t errlen) {
+  if (rows < 1 || hd < 16 || (hd & 15) || hd > 256) {
+    set_err(err, errlen, "barlink: rope_kv_write needs head_dim in 16..256, multiple of 16");
+    return -1;
+  }
+  k_rope_kv_write<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(qkv), positions, slots, static_cast<__nv_bfloat16*>(k_cache),
+      static_cast<__nv_bfloat16*>(v_cache), nq, nkv, hd, block_size, log2f(theta));
+  OPS_LAUNCH_CHECK("rope_kv_write");
+  return 0;
+}
+
+extern "C" int bl_rope(void* x, const int* positions, int rows, int heads, int hd, int row_stride,
+                       float theta, int axes, void* stream, char* err, size_t errlen) {
+  if (rows < 1 || axes < 1 || axes > 2 || (hd % (2 * axes))) {
+    set_err(err, errlen, "barlink: rope needs head_dim divisible by 2*axes (axes 1 or 2)");
+    return -1;
+  }
+  k_rope<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(x), positions, heads, hd, row_stride, log2f(theta), axes);
+  OPS_LAUNCH_CHECK("rope");
+  return 0;
+}
+
+extern "C" int bl_silu_mul(const void* gate_up, void* out, int rows, int inter, int interleaved,
+                           void* stream, char* err, size_t errlen) {
+  const size_t total = size_t(rows) * inter;
+  int grid = int((total + 255) / 256);
+  if (grid > 148 * 8) grid = 148 * 8;
+  if (grid < 1) grid = 1;
+  k_silu_mul<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter,
+      interleaved);
+  OPS_LAUNCH_CHECK("silu_mul");
+  return 0;
+}
+
+extern "C" int bl_embedding(const int* ids, const void* table, void* out, int rows, int hidden,
+                            int vocab_lo, int vocab_hi, void* stream, char* err, size_t errlen) {
+  if (hidden & 7) {
+    set_err(err, errlen, "barlink: embedding needs hidden %% 8 == 0");
+    return -1;
+  }
+  k_embedding<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      ids, static_cast<const uint4*>(table), static_cast<uint4*>(out), hidden / 8, vocab_lo,
+      vocab_hi);
+  OPS_LAUNCH_CHECK("embedding");
+  return 0;
+}
+
+extern "C" int bl_argmax(const void* logits, int rows, int n, int ld, int offset, int* idx,
+                         float* val, void* stream, char* err, size_t errlen) {
+  k_argmax<<<rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits), n, ld, offset, idx, val);
+  OPS_LAUNCH_CHECK("argmax");
+  return 0;
+}
+
+extern "C" int bl_argmax_merge(const void* pairs, int world, int rows, int* idx, void* stream,
+                               char* err, size_t errlen) {
+  k_argmax_merge<<<(rows + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float2*>(pairs), world, rows, idx);
+  OPS_LAUNCH_CHECK("argmax_merge");
+  return 0;
+}
+
+extern "C" int bl_paged_attn_decode(const void* q, int q_stride, const void* k_cache,
+                                    const void* v_cache, const int* block_tables,
+                                    const int* ctx_lens, void* out, int batch, int nq, int nkv,
+                                    int hd, int block_size, int max_blocks, float scale, int splits,
+                                    void* scratch, size_t scratch_bytes, void* stream, char* err,
+                                    size_t errlen) {
+  if (hd != kHd || block_size != kPageTokens) {
+    set_err(err, errlen, "barlink: paged attention is built for head_dim %d and block size %d", kHd,
+            kPageTokens);
+    return -1;
+  }
+  if (nkv < 1 || nq % nkv || nq / nkv > 16) {
+    set_err(err, errlen, "barlink: paged attention needs nq %% nkv == 0 and at most 16 query heads per KV head");
+    return -1;
+  }
+  if (splits <= 0) {
+    const int want = (2 * sm_count() + batch * nkv - 1) / (batch * nkv);
+    const int by_len = max_blocks / (2 * kAttnWarps) > 0 ? max_blocks / (2 * kAttnWarps) : 1;
+    splits = want < by_len ? want : by_len;
+    if (splits > 32) splits = 32;
+    if (splits < 1) splits = 1;
+  }
+  const size_t need = size_t(batch) * nq * splits * (kHd + 2) * sizeof(float);
+  if (splits > 1 && (!scratch || scratch_bytes < need)) splits = 1;
+  static bool attr = false;
+  const int smem = kAttnWarps * kWarpSmem;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(k_paged_attn_decode,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+      set_err(err, errlen, "barlink: paged attention shared memory opt-in failed: %s",
+              cudaGetErrorString(e));
+      return -1;
+    }
+    attr = true;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  k_paged_attn_decode<<<dim3(nkv, batch, splits), kAttnWarps * 32, smem, st>>>(
+      static_cast<const __nv_bfloat16*>(q), q_stride, static_cast<const __nv_bfloat16*>(k_cache),
+      static_cast<const __nv_bfloat16*>(v_cache), block_tables, ctx_lens,
+      static_cast<__nv_bfloat16*>(out), static_cast<float*>(scratch), nq, nkv, max_blocks,
+      scale_log2);
+  OPS_LAUNCH_CHECK("paged_attn_decode");
+  if (splits > 1) {
+    k_attn_merge<<<batch * nq, kHd, 0, st>>>(static_cast<const float*>(scratch),
+                                             static_cast<__nv_bfloat16*>(out), splits);
+    OPS_LAUNCH_CHECK("attn_merge");
+  }
+  return 0;
+}
