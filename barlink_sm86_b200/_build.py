@@ -21,6 +21,7 @@ SOURCES = [
     "comm_kernels.cu",
     "gemm_kernels.cu",
     "ops_kernels.cu",
+    "attn_kernels.cu",
     "backend.cc",
     "binding.cc",
     "binding_extra.cc",

@@ -90,6 +90,17 @@ int bl_copy_(blCtx* ctx, void* dstPtr, int dstIdx, void* srcPtr, int srcIdx, siz
 int bl_allreduce_(blCtx* ctx, void* const* ptrs, const int* idxs, int n, size_t bytes,
                   int dtype, void* const* streams, char* err, size_t errlen);
 
+/* the SPMD collectives below in single-process form, one pointer per arena:
+ * kind 0 all-reduce, 1 reduce-scatter, 2 all-gather, 3 broadcast,
+ * 4 all-reduce + residual + RMSNorm, 5 barrier (bytes is per rank for 1, 2) */
+int bl_sp_collective(blCtx* ctx, int kind, const void* const* in, void* const* out,
+                     const void* const* aux_in, void* const* aux_out, const void* const* gamma,
+                     size_t bytes, int dtype, int algo, int root, int rows, int hidden, float eps,
+                     void* const* streams, char* err, size_t errlen);
+/* send as rank src then recv as rank dst on one stream (ranks sharing a GPU) */
+int bl_sp_sendrecv(blCtx* ctx, int src, int dst, const void* in, void* out, size_t bytes,
+                   void* stream, char* err, size_t errlen);
+
 /* ---- SPMD collectives on arbitrary device pointers --------------------- */
 /* algo: BL_ALGO_*; AUTO picks by size.  in == out allowed. */
 int bl_allreduce_into_peer(blCtx* ctx, const void* inPtr, void* outPtr, size_t bytes,

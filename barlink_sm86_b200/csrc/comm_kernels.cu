@@ -1218,15 +1218,12 @@ extern "C" int bl_allreduce_(blCtx* ctx, void* const* ptrs, const int* idxs, int
   return allreduce_local(ctx, pr, bytes, dtype, BL_ALGO_AUTO, err, errlen);
 }
 
-static int staged_peer(blCtx* ctx, int mode, const void* in, void* out, size_t per_rank_bytes,
-                       size_t stride_bytes, int dtype, int root, void* stream, char* err,
-                       size_t errlen) {
-  if (!ctx || !ctx->peer_mode) {
-    set_err(err, errlen, "barlink: this collective needs an SPMD context (init_peer)");
-    return -1;
-  }
+static int staged_local(blCtx* ctx, int mode, const PerRank* pr, size_t per_rank_bytes,
+                        size_t stride_bytes, int dtype, int root, char* err, size_t errlen) {
   if (check_health(ctx, err, errlen) != 0) return -1;
-  if (per_rank_bytes == 0 || (per_rank_bytes & 15u) || !aligned16(in) || !aligned16(out)) {
+  bool al = true;
+  for (int l = 0; l < ctx->local_ranks(); ++l) al = al && aligned16(pr[l].in) && aligned16(pr[l].out);
+  if (per_rank_bytes == 0 || (per_rank_bytes & 15u) || !al) {
     set_err(err, errlen, "barlink: collective needs 16-byte aligned pointers and a size that is a non-zero multiple of 16 (%zu)",
             per_rank_bytes);
     return -1;
@@ -1246,19 +1243,29 @@ static int staged_peer(blCtx* ctx, int mode, const void* in, void* out, size_t p
   a.slice_stride = stride_bytes / 16;
   a.mode = mode;
   a.root = root;
-  PerRank pr;
-  pr.in = in;
-  pr.out = out;
-  pr.stream = stream;
   const int grid = pick_grid(ctx, a.nvec, kThreads, 128);
   int rc = -1;
   rc = dispatch_dtype(dtype, err, errlen, [&](auto tag) -> int {
     constexpr int DT = decltype(tag)::value;
-    return launch_local(ctx, k_staged<DT>, a, &pr, grid, kThreads, err, errlen);
+    return launch_local(ctx, k_staged<DT>, a, pr, grid, kThreads, err, errlen);
   });
   ctx->stats[BL_STAT_OPS]++;
   ctx->stats[BL_STAT_BYTES] += per_rank_bytes;
   return rc;
+}
+
+static int staged_peer(blCtx* ctx, int mode, const void* in, void* out, size_t per_rank_bytes,
+                       size_t stride_bytes, int dtype, int root, void* stream, char* err,
+                       size_t errlen) {
+  if (!ctx || !ctx->peer_mode) {
+    set_err(err, errlen, "barlink: this collective needs an SPMD context (init_peer)");
+    return -1;
+  }
+  PerRank pr;
+  pr.in = in;
+  pr.out = out;
+  pr.stream = stream;
+  return staged_local(ctx, mode, &pr, per_rank_bytes, stride_bytes, dtype, root, err, errlen);
 }
 
 extern "C" int bl_allgather_peer(blCtx* ctx, const void* inPtr, void* outPtr, size_t bytesPerRank,
@@ -1291,14 +1298,8 @@ extern "C" int bl_barrier_peer(blCtx* ctx, void* stream, char* err, size_t errle
   return launch_local(ctx, k_barrier, a, pr, 1, 32, err, errlen);
 }
 
-extern "C" int bl_allreduce_rmsnorm_peer(blCtx* ctx, const void* inPtr, const void* residualIn,
-                                         const void* gamma, void* residualOut, void* normedOut,
-                                         int rows, int hidden, float eps, int dtype, void* stream,
-                                         char* err, size_t errlen) {
-  if (!ctx || !ctx->peer_mode) {
-    set_err(err, errlen, "barlink: allreduce_rmsnorm needs an SPMD context (init_peer)");
-    return -1;
-  }
+static int norm_local(blCtx* ctx, const PerRank* pr, int rows, int hidden, float eps, int dtype,
+                      char* err, size_t errlen) {
   if (check_health(ctx, err, errlen) != 0) return -1;
   const int esz = dtype == BL_DTYPE_FP32 ? 4 : 2;
   if (dtype != BL_DTYPE_BF16 && dtype != BL_DTYPE_FP16 && dtype != BL_DTYPE_FP32) {
@@ -1317,17 +1318,50 @@ extern "C" int bl_allreduce_rmsnorm_peer(blCtx* ctx, const void* inPtr, const vo
             bytes, ctx->layout.lamport_slice);
     return -1;
   }
-  if (!aligned16(inPtr) || !aligned16(gamma) || !aligned16(residualOut) || !aligned16(normedOut) ||
-      !aligned16(residualIn)) {
-    set_err(err, errlen, "barlink: allreduce_rmsnorm pointers must be 16-byte aligned");
-    return -1;
-  }
+  for (int l = 0; l < ctx->local_ranks(); ++l)
+    if (!aligned16(pr[l].in) || !aligned16(pr[l].gamma) || !aligned16(pr[l].aux_out) ||
+        !aligned16(pr[l].out) || !aligned16(pr[l].aux_in)) {
+      set_err(err, errlen, "barlink: allreduce_rmsnorm pointers must be 16-byte aligned");
+      return -1;
+    }
   CollArgs a;
   memset(&a, 0, sizeof(a));
   a.nvec = bytes / 16;
   a.rows = rows;
   a.vec_per_row = int(row_bytes / 16);
   a.eps = eps;
+  int grid = rows < 64 ? rows : 64;
+  if (!ctx->peer_mode && grid > 8) grid = 8;
+  int rc = -1;
+  // one thread per vector up to the block limit keeps short rows from
+  // wasting a 512-thread block
+  int threads = (a.vec_per_row + 31) / 32 * 32;
+  if (threads > kThreads) threads = kThreads;
+  if (threads < 64) threads = 64;
+  switch (dtype) {
+    case BL_DTYPE_BF16:
+      rc = launch_local(ctx, k_lamport<BL_DTYPE_BF16, true>, a, pr, grid, threads, err, errlen);
+      break;
+    case BL_DTYPE_FP16:
+      rc = launch_local(ctx, k_lamport<BL_DTYPE_FP16, true>, a, pr, grid, threads, err, errlen);
+      break;
+    default:
+      rc = launch_local(ctx, k_lamport<BL_DTYPE_FP32, true>, a, pr, grid, threads, err, errlen);
+  }
+  ctx->stats[BL_STAT_OPS]++;
+  ctx->stats[BL_STAT_FUSED_NORM]++;
+  ctx->stats[BL_STAT_BYTES] += bytes;
+  return rc;
+}
+
+extern "C" int bl_allreduce_rmsnorm_peer(blCtx* ctx, const void* inPtr, const void* residualIn,
+                                         const void* gamma, void* residualOut, void* normedOut,
+                                         int rows, int hidden, float eps, int dtype, void* stream,
+                                         char* err, size_t errlen) {
+  if (!ctx || !ctx->peer_mode) {
+    set_err(err, errlen, "barlink: allreduce_rmsnorm needs an SPMD context (init_peer)");
+    return -1;
+  }
   PerRank pr;
   pr.in = inPtr;
   pr.out = normedOut;
@@ -1335,26 +1369,96 @@ extern "C" int bl_allreduce_rmsnorm_peer(blCtx* ctx, const void* inPtr, const vo
   pr.aux_out = residualOut;
   pr.gamma = gamma;
   pr.stream = stream;
-  const int grid = rows < 64 ? rows : 64;
-  int rc = -1;
-  // one warp per ~4 vectors keeps short rows from wasting a 512-thread block
-  int threads = (a.vec_per_row + 31) / 32 * 32;
-  if (threads > kThreads) threads = kThreads;
-  if (threads < 64) threads = 64;
-  switch (dtype) {
-    case BL_DTYPE_BF16:
-      rc = launch_local(ctx, k_lamport<BL_DTYPE_BF16, true>, a, &pr, grid, threads, err, errlen);
-      break;
-    case BL_DTYPE_FP16:
-      rc = launch_local(ctx, k_lamport<BL_DTYPE_FP16, true>, a, &pr, grid, threads, err, errlen);
-      break;
-    default:
-      rc = launch_local(ctx, k_lamport<BL_DTYPE_FP32, true>, a, &pr, grid, threads, err, errlen);
+  return norm_local(ctx, &pr, rows, hidden, eps, dtype, err, errlen);
+}
+
+// Single-process form of the SPMD collectives: one pointer per arena.  With
+// ranks that share a GPU this is how an N-rank protocol is exercised on one
+// device (one cooperative kernel over all ranks' data).
+// kind: 0 all-reduce, 1 reduce-scatter, 2 all-gather, 3 broadcast,
+//       4 all-reduce + residual + RMSNorm, 5 barrier
+extern "C" int bl_sp_collective(blCtx* ctx, int kind, const void* const* in, void* const* out,
+                                const void* const* aux_in, void* const* aux_out,
+                                const void* const* gamma, size_t bytes, int dtype, int algo, int root,
+                                int rows, int hidden, float eps, void* const* streams, char* err,
+                                size_t errlen) {
+  if (!ctx || ctx->peer_mode) {
+    set_err(err, errlen, "barlink: sp_collective is the single-process call (init, not init_peer)");
+    return -1;
   }
-  ctx->stats[BL_STAT_OPS]++;
-  ctx->stats[BL_STAT_FUSED_NORM]++;
-  ctx->stats[BL_STAT_BYTES] += bytes;
-  return rc;
+  PerRank pr[kMaxRanks];
+  for (int r = 0; r < ctx->world; ++r) {
+    pr[r].in = in ? in[r] : nullptr;
+    pr[r].out = out ? out[r] : nullptr;
+    pr[r].aux_in = aux_in ? aux_in[r] : nullptr;
+    pr[r].aux_out = aux_out ? aux_out[r] : nullptr;
+    pr[r].gamma = gamma ? gamma[r] : nullptr;
+    pr[r].stream = streams ? streams[r] : nullptr;
+  }
+  switch (kind) {
+    case 0: return allreduce_local(ctx, pr, bytes, dtype, algo, err, errlen);
+    case 1: return staged_local(ctx, 1, pr, bytes, 0, dtype, 0, err, errlen);
+    case 2: return staged_local(ctx, 2, pr, bytes, 0, BL_DTYPE_U8, 0, err, errlen);
+    case 3: return staged_local(ctx, 3, pr, bytes, 0, BL_DTYPE_U8, root, err, errlen);
+    case 4: return norm_local(ctx, pr, rows, hidden, eps, dtype, err, errlen);
+    case 5: {
+      if (check_health(ctx, err, errlen) != 0) return -1;
+      CollArgs a;
+      memset(&a, 0, sizeof(a));
+      return launch_local(ctx, k_barrier, a, pr, 1, 32, err, errlen);
+    }
+    default:
+      set_err(err, errlen, "barlink: unknown collective kind %d", kind);
+      return -1;
+  }
+}
+
+// Single-process p2p: the send runs as rank `src`, then the recv as rank
+// `dst`, in that order on one stream (a send never waits for the message it
+// carries to be consumed, so the pair cannot block on a shared GPU).
+extern "C" int bl_sp_sendrecv(blCtx* ctx, int src, int dst, const void* in, void* out, size_t bytes,
+                              void* stream, char* err, size_t errlen) {
+  if (!ctx || ctx->peer_mode) {
+    set_err(err, errlen, "barlink: sp_sendrecv is the single-process call");
+    return -1;
+  }
+  if (src < 0 || dst < 0 || src >= ctx->world || dst >= ctx->world || src == dst) {
+    set_err(err, errlen, "barlink: sp_sendrecv needs two different ranks below %d", ctx->world);
+    return -1;
+  }
+  if (ctx->arena[src].device != ctx->arena[dst].device) {
+    set_err(err, errlen, "barlink: sp_sendrecv is for ranks that share a GPU; use copy_ across GPUs");
+    return -1;
+  }
+  if (bytes == 0 || (bytes & 15u) || !aligned16(in) || !aligned16(out) || bytes > ctx->layout.p2p_slice) {
+    set_err(err, errlen, "barlink: sp_sendrecv needs aligned pointers and a multiple of 16 bytes up to %zu",
+            ctx->layout.p2p_slice);
+    return -1;
+  }
+  if (check_health(ctx, err, errlen) != 0) return -1;
+  int cur = 0;
+  cudaGetDevice(&cur);
+  RT_TRY(cudaSetDevice(ctx->arena[src].device), "cudaSetDevice");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CollArgs a;
+  memset(&a, 0, sizeof(a));
+  a.nvec = bytes / 16;
+  size_t g = (a.nvec + kThreads - 1) / kThreads;
+  const int grid = int(g > 32 ? 32 : g);
+  a.pack.c = ctx->comm_for(src);
+  a.peer = dst;
+  a.in[0] = in;
+  k_p2p_send<<<grid, kThreads, 0, st>>>(a);
+  RT_TRY(cudaGetLastError(), "send launch");
+  a.pack.c = ctx->comm_for(dst);
+  a.peer = src;
+  a.in[0] = nullptr;
+  a.out[0] = out;
+  k_p2p_recv<<<grid, kThreads, 0, st>>>(a);
+  RT_TRY(cudaGetLastError(), "recv launch");
+  cudaSetDevice(cur);
+  ctx->stats[BL_STAT_P2P] += 2;
+  return 0;
 }
 
 // ---- p2p ---------------------------------------------------------------------

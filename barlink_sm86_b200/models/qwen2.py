@@ -1,0 +1,344 @@
+# SPDX-License-Identifier: MIT
+"""Qwen2-style decoder with tensor parallelism, paged KV cache and a
+CUDA-graphed decode step.
+
+The reference runs HF `transformers` Qwen models and patches them from the
+outside: linears are swapped for quantised ones and row-parallel modules get
+an all-reduce hook (demos/qwen_tp/qwen38_int8/worker.py:248-441), the
+lm_head is vocab-parallel with an exchange (:208-241), decode is captured in a
+CUDA graph with a static cache (:539-614).  There is no network on the build
+machines and no checkpoints, so this model owns its layers instead: weights
+are random-init N(0, 0.02) from a seed, generated as FULL tensors and then
+sharded, so TP=N and TP=1 hold the same model.
+
+Per layer and decode step (CUDA): fused add+RMSNorm (TP: fused with the
+all-reduce over NVLink), QKV GEMM with bias, RoPE + paged KV write, paged
+attention, o_proj GEMM, fused add+RMSNorm, gate/up GEMM with SiLU*mul in the
+epilogue, down GEMM.  All GEMMs are tcgen05 kernels.
+"""
+import math
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..parallel import TPComm, head_plan, interleave_gate_up, shard_cols, shard_rows
+from ..parallel.plan import gather_head_cols, gather_heads
+
+
+@dataclass
+class Qwen2Config:
+    hidden: int = 3584
+    layers: int = 28
+    n_heads: int = 28
+    n_kv_heads: int = 4
+    head_dim: int = 128
+    intermediate: int = 18944
+    vocab: int = 152064
+    eps: float = 1e-6
+    theta: float = 1e6
+    qkv_bias: bool = True
+    name: str = "qwen2.5-7b-shape"
+
+    @staticmethod
+    def qwen25_7b():
+        return Qwen2Config()
+
+    @staticmethod
+    def qwen25_32b():
+        return Qwen2Config(hidden=5120, layers=64, n_heads=40, n_kv_heads=8, head_dim=128,
+                           intermediate=27648, vocab=152064, name="qwen2.5-32b-shape")
+
+    @staticmethod
+    def tiny():
+        # the plumbing config: hidden 512, 4 layers, 8 query / 2 KV heads, head_dim 64
+        return Qwen2Config(hidden=512, layers=4, n_heads=8, n_kv_heads=2, head_dim=64,
+                           intermediate=1376, vocab=32000, name="tiny-qwen2")
+
+
+def _randn(shape, seed, device, dtype, std=0.02):
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std).to(dtype)
+
+
+class Qwen2Weights:
+    """Per-rank shards of a seeded random-init model."""
+
+    def __init__(self, cfg: Qwen2Config, tp: int, rank: int, device, dtype, seed: int = 0,
+                 layers: Optional[int] = None):
+        self.cfg, self.tp, self.rank = cfg, tp, rank
+        H, hd = cfg.hidden, cfg.head_dim
+        self.plan = head_plan(cfg.n_heads, cfg.n_kv_heads, tp, rank)
+        n_layers = cfg.layers if layers is None else layers
+        self.layers = []
+        base = seed * 1000003
+        inter_pad = -(-cfg.intermediate // (tp * 8)) * (tp * 8)  # shards stay 16-byte multiples
+        self.inter_local = inter_pad // tp
+        for l in range(n_layers):
+            s = base + l * 64
+            wq = _randn((cfg.n_heads * hd, H), s + 1, device, dtype)
+            wk = _randn((cfg.n_kv_heads * hd, H), s + 2, device, dtype)
+            wv = _randn((cfg.n_kv_heads * hd, H), s + 3, device, dtype)
+            wqkv = torch.cat([gather_heads(wq, self.plan.q_heads, hd),
+                              gather_heads(wk, self.plan.kv_heads, hd),
+                              gather_heads(wv, self.plan.kv_heads, hd)], 0).contiguous()
+            del wq, wk, wv
+            bqkv = None
+            if cfg.qkv_bias:
+                bq = _randn((cfg.n_heads * hd,), s + 4, device, dtype)
+                bk = _randn((cfg.n_kv_heads * hd,), s + 5, device, dtype)
+                bv = _randn((cfg.n_kv_heads * hd,), s + 6, device, dtype)
+                bqkv = torch.cat([gather_heads(bq[:, None], self.plan.q_heads, hd)[:, 0],
+                                  gather_heads(bk[:, None], self.plan.kv_heads, hd)[:, 0],
+                                  gather_heads(bv[:, None], self.plan.kv_heads, hd)[:, 0]]).contiguous()
+            wo_full = _randn((H, cfg.n_heads * hd), s + 7, device, dtype)
+            wo = gather_head_cols(wo_full, self.plan.q_heads, hd).contiguous()
+            del wo_full
+            gate = _randn((cfg.intermediate, H), s + 8, device, dtype)
+            up = _randn((cfg.intermediate, H), s + 9, device, dtype)
+            if inter_pad != cfg.intermediate:
+                z = torch.zeros(inter_pad - cfg.intermediate, H, dtype=dtype, device=device)
+                gate, up = torch.cat([gate, z], 0), torch.cat([up, z], 0)
+            wgu = interleave_gate_up(shard_rows(gate, tp, rank), shard_rows(up, tp, rank))
+            del gate, up
+            down = _randn((H, cfg.intermediate), s + 10, device, dtype)
+            if inter_pad != cfg.intermediate:
+                down = torch.cat([down, torch.zeros(H, inter_pad - cfg.intermediate, dtype=dtype,
+                                                    device=device)], 1)
+            wdown = shard_cols(down, tp, rank)
+            del down
+            self.layers.append(dict(
+                wqkv=wqkv, bqkv=bqkv, wo=wo, wgu=wgu, wdown=wdown,
+                ln1=torch.ones(H, dtype=dtype, device=device),
+                ln2=torch.ones(H, dtype=dtype, device=device)))
+        self.embed = _randn((cfg.vocab, H), base + 900001, device, dtype)
+        vocab_pad = -(-cfg.vocab // tp) * tp
+        head = _randn((cfg.vocab, H), base + 900002, device, dtype)
+        if vocab_pad != cfg.vocab:
+            head = torch.cat([head, torch.zeros(vocab_pad - cfg.vocab, H, dtype=dtype, device=device)], 0)
+        self.vocab_local = vocab_pad // tp
+        self.lm_head = shard_rows(head, tp, rank)
+        del head
+        self.ln_f = torch.ones(H, dtype=dtype, device=device)
+
+    def nbytes(self):
+        n = self.embed.numel() + self.lm_head.numel() + self.ln_f.numel()
+        for L in self.layers:
+            n += sum(t.numel() for t in L.values() if t is not None)
+        return n * self.embed.element_size()
+
+
+class PagedKV:
+    """Paged KV cache: [blocks, nkv_local, block_size, head_dim] per layer, one
+    contiguous run of blocks per sequence (block tables are still indirect)."""
+
+    def __init__(self, n_layers, batch, max_len, nkv, hd, device, dtype, block_size=16):
+        self.block_size = block_size
+        self.blocks_per_seq = -(-max_len // block_size)
+        n_blocks = batch * self.blocks_per_seq
+        self.k = [torch.zeros(n_blocks, nkv, block_size, hd, dtype=dtype, device=device)
+                  for _ in range(n_layers)]
+        self.v = [torch.zeros(n_blocks, nkv, block_size, hd, dtype=dtype, device=device)
+                  for _ in range(n_layers)]
+        self.block_tables = (torch.arange(n_blocks, dtype=torch.int32, device=device)
+                             .view(batch, self.blocks_per_seq).contiguous())
+
+    def slots(self, positions_2d):
+        """positions [batch, s] -> flat slot ids [batch*s] (int32)."""
+        b = torch.arange(positions_2d.shape[0], device=positions_2d.device)[:, None]
+        blk = self.block_tables[b, (positions_2d // self.block_size).long()]
+        return (blk * self.block_size + positions_2d % self.block_size).to(torch.int32).reshape(-1)
+
+
+class Qwen2Model:
+    def __init__(self, cfg: Qwen2Config, comm: Optional[TPComm] = None, device="cpu",
+                 dtype=torch.float32, seed=0, layers=None):
+        self.cfg = cfg
+        self.comm = comm or TPComm(None)
+        self.device, self.dtype = torch.device(device), dtype
+        self.w = Qwen2Weights(cfg, self.comm.world, self.comm.rank, self.device, dtype, seed, layers)
+        self.nq, self.nkv, self.hd = self.w.plan.nq, self.w.plan.nkv, cfg.head_dim
+        self.scale = 1.0 / math.sqrt(cfg.head_dim)
+
+    def _run_layers(self, ids, positions, attn_factory):
+        """ids [T] int32 -> final normed hidden [T, hidden] (replicated on every rank)."""
+        cfg, c, w = self.cfg, self.comm, self.w
+        h = ops.embedding(ids, w.embed)
+        res = torch.zeros_like(h)
+        pending = False  # h holds a partial sum that still needs the all-reduce
+        for li, L in enumerate(w.layers):
+            if pending:
+                normed, res = c.allreduce_rmsnorm(h, res, L["ln1"], cfg.eps)
+            else:
+                normed, res = ops.rmsnorm(h, L["ln1"], cfg.eps, res)
+            qkv = ops.linear(normed, L["wqkv"], L["bqkv"])
+            a = attn_factory(li)(qkv)
+            h = ops.linear(a, L["wo"])
+            normed, res = c.allreduce_rmsnorm(h, res, L["ln2"], cfg.eps)
+            act = ops.linear(normed, L["wgu"], silu_mul=True)
+            h = ops.linear(act, L["wdown"])
+            pending = True
+        if pending:
+            normed, res = c.allreduce_rmsnorm(h, res, w.ln_f, cfg.eps)
+        else:
+            normed, res = ops.rmsnorm(h, w.ln_f, cfg.eps, res)
+        return normed
+
+    # ---- prefill: dense causal attention, optional KV write ----------------
+    def prefill(self, ids_2d, cache: Optional[PagedKV] = None, chunk_rows: int = 0):
+        """ids [batch, seq] -> final normed hidden [batch*seq, hidden]."""
+        batch, seq = ids_2d.shape
+        dev = ids_2d.device
+        pos2d = torch.arange(seq, device=dev, dtype=torch.int32)[None, :].expand(batch, seq).contiguous()
+        positions = pos2d.reshape(-1)
+        slots = cache.slots(pos2d) if cache is not None else None
+        cu = torch.arange(0, (batch + 1) * seq, seq, device=dev, dtype=torch.int32)
+        nq, nkv, hd = self.nq, self.nkv, self.hd
+
+        def attn_factory(li):
+            def attn(qkv):
+                kc = cache.k[li] if cache is not None else None
+                vc = cache.v[li] if cache is not None else None
+                ops.rope_kv_write(qkv, positions, slots, kc, vc, nq, nkv, hd,
+                                  cache.block_size if cache is not None else 16, self.cfg.theta)
+                T = qkv.shape[0]
+                v3 = qkv.view(T, nq + 2 * nkv, hd)
+                o = ops.attention(v3[:, :nq], v3[:, nq:nq + nkv], v3[:, nq + nkv:], cu, cu, seq,
+                                  self.scale, True)
+                return o.reshape(T, nq * hd)
+            return attn
+
+        return self._run_layers(ids_2d.reshape(-1).to(torch.int32), positions, attn_factory)
+
+    # ---- decode: one token per sequence against the paged cache ------------
+    def decode_hidden(self, ids, positions, slots, ctx_lens, cache: PagedKV, splits=0):
+        nq, nkv, hd = self.nq, self.nkv, self.hd
+
+        def attn_factory(li):
+            def attn(qkv):
+                ops.rope_kv_write(qkv, positions, slots, cache.k[li], cache.v[li], nq, nkv, hd,
+                                  cache.block_size, self.cfg.theta)
+                return ops.paged_attn_decode(qkv, cache.k[li], cache.v[li], cache.block_tables,
+                                             ctx_lens, nq, nkv, hd, self.scale, splits)
+            return attn
+
+        return self._run_layers(ids, positions, attn_factory)
+
+    def logits_local(self, hidden):
+        return ops.linear(hidden, self.w.lm_head)
+
+    def logits(self, hidden):
+        """Full-vocabulary logits (vocab-parallel head + gather)."""
+        full = self.comm.all_gather_cols(self.logits_local(hidden))
+        return full[:, : self.cfg.vocab]
+
+    def next_tokens(self, hidden):
+        """Greedy next token per row (local arg max + 8-byte-per-row exchange)."""
+        return self.comm.argmax_vocab_parallel(self.logits_local(hidden), self.w.vocab_local)
+
+
+class DecodeEngine:
+    """Greedy decoding with a CUDA-graphed step.
+
+    `prefill(ids)` fills the cache and returns the first generated token;
+    `step(ids)` consumes one token per sequence and returns the next one.  On
+    CUDA the step is captured once and replayed: the position, slot and
+    context-length tensors live on the device and advance inside the graph,
+    and the collectives are replay-safe (their expectations are device
+    counters).  `step_host` is the end-to-end form: token ids arrive in pinned
+    host memory and the result is read back to the host every step.
+    """
+
+    def __init__(self, model: Qwen2Model, batch: int, max_len: int, use_graph: bool = True,
+                 attn_splits: int = 0):
+        self.m = model
+        self.batch, self.max_len = batch, max_len
+        dev, dt = model.device, model.dtype
+        self.cache = PagedKV(len(model.w.layers), batch, max_len, model.nkv, model.hd, dev, dt)
+        self.ids = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.positions = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.ctx_lens = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.slots = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.out_ids = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.use_graph = use_graph and dev.type == "cuda"
+        self.graph = None
+        self.attn_splits = attn_splits
+        self.launches_per_step = 0
+        if dev.type == "cuda":
+            self.h_in = torch.zeros(batch, dtype=torch.int32).pin_memory()
+            self.h_out = torch.zeros(batch, dtype=torch.int32).pin_memory()
+
+    def set_context(self, length: int):
+        """Declare that every sequence already has `length` tokens in the cache."""
+        self.positions.fill_(length)
+        self._refresh()
+
+    def _refresh(self):
+        c = self.cache
+        b = torch.arange(self.batch, device=self.positions.device)
+        blk = c.block_tables[b, (self.positions // c.block_size).long()]
+        self.slots.copy_(blk * c.block_size + self.positions % c.block_size)
+        self.ctx_lens.copy_(self.positions + 1)
+
+    def prefill(self, ids_2d):
+        hidden = self.m.prefill(ids_2d, self.cache)
+        seq = ids_2d.shape[1]
+        last = hidden.view(self.batch, seq, -1)[:, -1].contiguous()
+        nxt = self.m.next_tokens(last)
+        self.set_context(seq)
+        return nxt
+
+    def _step_body(self):
+        hidden = self.m.decode_hidden(self.ids, self.positions, self.slots, self.ctx_lens, self.cache,
+                                      self.attn_splits)
+        nxt = self.m.next_tokens(hidden)
+        self.out_ids.copy_(nxt)
+        self.ids.copy_(nxt)  # replays feed themselves unless the caller overwrites ids
+        self.positions.add_(1)
+        self._refresh()
+
+    def capture(self, warmup: int = 2):
+        """Warm up (allocator, lazy attributes) and capture the step."""
+        if not self.use_graph:
+            return
+        saved = (self.positions.clone(), self.ids.clone())
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(warmup):
+                self._step_body()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        self.positions.copy_(saved[0])
+        self._refresh()
+        before = ops.launch_count
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self._step_body()
+        self.launches_per_step = ops.launch_count - before
+        # the captured run did not execute; state is as before the capture
+        self.positions.copy_(saved[0])
+        self.ids.copy_(saved[1])
+        self._refresh()
+        torch.cuda.synchronize()
+
+    def step(self, ids=None):
+        if ids is not None:
+            self.ids.copy_(ids)
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            before = ops.launch_count
+            self._step_body()
+            self.launches_per_step = ops.launch_count - before
+        return self.out_ids
+
+    def step_host(self, ids_host):
+        """ids_host: pinned int32 [batch] on the host -> pinned int32 [batch] (next tokens)."""
+        self.ids.copy_(ids_host, non_blocking=True)
+        self.step()
+        self.h_out.copy_(self.out_ids, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.h_out

@@ -1,0 +1,112 @@
+# SPDX-License-Identifier: MIT
+"""Op surface used by the models.
+
+CUDA tensors always run the sm_100a kernels of the compiled extension (and
+fail loudly when it is missing); CPU tensors run the fp32 PyTorch statements
+in `reference.py`, which are also the oracles of the GPU tests.  The
+reference's op surface is `w8a16_quant_act` / `w8a16_gemm`
+(torch_ext/barlink_sm86/binding.cpp:434-490); everything else here replaces
+library or eager-framework kernels that its demos call.
+"""
+import torch
+
+from .. import load_extension
+from . import reference as ref
+
+# number of sm_100a kernel launches issued through this module (bench.py reports it)
+launch_count = 0
+
+
+def _C():
+    return load_extension()
+
+
+def _count(n=1):
+    global launch_count
+    launch_count += n
+
+
+def linear(x, weight, bias=None, residual=None, silu_mul=False, out=None):
+    if x.is_cuda:
+        _count()
+        x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
+        y = _C().linear(x2, weight, bias, residual, silu_mul, out)
+        return y if x.dim() == 2 else y.view(*x.shape[:-1], y.shape[-1])
+    return ref.linear(x, weight, bias, residual, silu_mul)
+
+
+def rmsnorm(x, gamma, eps, residual=None, out=None):
+    """Returns (normed, residual); the residual tensor is updated in place on CUDA."""
+    if x.is_cuda:
+        _count()
+        return _C().rmsnorm(x, gamma, eps, residual, out)
+    return ref.rmsnorm(x, gamma, eps, residual)
+
+
+def rope_kv_write(qkv, positions, slots, k_cache, v_cache, nq, nkv, hd, block_size, theta):
+    if qkv.is_cuda:
+        _count()
+        _C().rope_kv_write(qkv, positions, slots, k_cache, v_cache, nq, nkv, hd, block_size, theta)
+        return qkv
+    return ref.rope_kv_write(qkv, positions, slots, k_cache, v_cache, nq, nkv, hd, block_size, theta)
+
+
+def rope(x, positions, theta, axes=1):
+    """x [rows, heads, hd]; rotated in place on CUDA."""
+    if x.is_cuda:
+        _count()
+        rows, heads, hd = x.shape
+        _C().rope(x.view(rows, heads * hd), positions, heads, hd, theta, axes)
+        return x
+    return ref.rope(x, positions, theta, axes)
+
+
+def silu_mul(gate_up, interleaved=False):
+    if gate_up.is_cuda:
+        _count()
+        return _C().silu_mul(gate_up, interleaved)
+    return ref.silu_mul(gate_up, interleaved)
+
+
+def embedding(ids, table, vocab_lo=0, out=None):
+    if table.is_cuda:
+        _count()
+        return _C().embedding(ids, table, vocab_lo, out)
+    return ref.embedding(ids, table, vocab_lo)
+
+
+def argmax(logits, offset=0):
+    if logits.is_cuda:
+        _count()
+        return _C().argmax(logits, offset)
+    return ref.argmax(logits, offset)
+
+
+def paged_attn_decode(qkv, k_cache, v_cache, block_tables, ctx_lens, nq, nkv, hd, scale, splits=0,
+                      out=None):
+    if qkv.is_cuda:
+        _count(2 if splits != 1 else 1)
+        return _C().paged_attn_decode(qkv, k_cache, v_cache, block_tables, ctx_lens, nq, nkv, hd,
+                                      scale, splits, out)
+    return ref.paged_attn_decode(qkv, k_cache, v_cache, block_tables, ctx_lens, nq, nkv, hd, scale)
+
+
+def attention(q, k, v, cu_q, cu_k, max_q, scale, causal):
+    """Dense attention over packed sequences (prefill, joint attention)."""
+    if q.is_cuda:
+        _count()
+        return _C().attn_fwd(q, k, v, cu_q, cu_k, max_q, scale, causal)
+    return ref.attention(q, k, v, cu_q, cu_k, scale, causal)
+
+
+def w8a16_linear(x, wq, scale, bias=None, silu_mul=False):
+    if x.is_cuda:
+        _count()
+        return _C().w8a16_linear(x, wq, scale, bias, silu_mul)
+    return ref.w8a16_linear(x, wq, scale, bias, silu_mul)
+
+
+__all__ = [
+    "linear", "rmsnorm", "rope_kv_write", "rope", "silu_mul", "embedding", "argmax",
+    "paged_attn_decode", "attention", "w8a16_linear", "ref",
+]

@@ -1,0 +1,139 @@
+# SPDX-License-Identifier: MIT
+"""Communicator used by the tensor-parallel layers.
+
+On CUDA with the link up, every call is one hand-written kernel of the link
+core (`_C.allreduce_into`, `_C.allreduce_rmsnorm`, `_C.allgather_into`): no
+c10d dispatch on the hot path.  On CPU (or with a foreign backend such as
+gloo / nccl for A/B runs) the same calls go through `torch.distributed`.
+The reference's equivalent is the `dist.all_reduce` forward hook on
+row-parallel modules (demos/qwen_tp/qwen38_int8/worker.py:167-183) and the
+isend/irecv lm_head exchange (:223-241).
+"""
+import torch
+import torch.distributed as dist
+
+from .. import load_extension
+from ..ops import reference as ref
+from .. import ops as _ops
+
+
+class TPComm:
+    def __init__(self, group=None, use_link=None):
+        if group is None and dist.is_available() and dist.is_initialized():
+            group = dist.group.WORLD
+        self.group = group
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        if use_link is None:
+            use_link = False
+            if self.world > 1 and torch.cuda.is_available():
+                try:
+                    info = load_extension().info()
+                    use_link = bool(info.get("initialized") and info.get("peer_mode")
+                                    and info.get("world") == self.world)
+                except ImportError:
+                    use_link = False
+        self.use_link = use_link
+        self.oneshot_max = load_extension().info()["oneshot_max"] if use_link else 0
+        self.ar_calls = 0
+        self.ar_bytes = 0
+
+    @classmethod
+    def single(cls):
+        """A communicator of one rank: every collective is a local no-op."""
+        c = cls.__new__(cls)
+        c.group, c.world, c.rank = None, 1, 0
+        c.use_link, c.oneshot_max, c.ar_calls, c.ar_bytes = False, 0, 0, 0
+        return c
+
+    # ---- collectives -----------------------------------------------------
+    def all_reduce(self, x):
+        """In-place sum over the group; returns x."""
+        if self.world == 1:
+            return x
+        self.ar_calls += 1
+        self.ar_bytes += x.numel() * x.element_size()
+        if self.use_link and x.is_cuda and x.is_contiguous() and (x.numel() * x.element_size()) % 16 == 0 \
+                and x.data_ptr() % 16 == 0:
+            _ops._count()
+            load_extension().allreduce_into(x, x)
+            return x
+        dist.all_reduce(x, group=self.group)
+        return x
+
+    def all_gather_cols(self, x):
+        """[rows, n_local] on every rank -> [rows, world * n_local] (rank-major columns)."""
+        if self.world == 1:
+            return x
+        rows, n = x.shape
+        flat = torch.empty(self.world, rows, n, dtype=x.dtype, device=x.device)
+        xc = x.contiguous()
+        if self.use_link and x.is_cuda and (xc.numel() * xc.element_size()) % 16 == 0:
+            _ops._count()
+            load_extension().allgather_into(flat.view(-1), xc.view(-1))
+        else:
+            dist.all_gather_into_tensor(flat.view(-1), xc.view(-1), group=self.group)
+        return flat.permute(1, 0, 2).reshape(rows, self.world * n)
+
+    def all_gather_rows(self, x):
+        """[rows_local, n] -> [world * rows_local, n]."""
+        if self.world == 1:
+            return x
+        xc = x.contiguous()
+        out = torch.empty(self.world * xc.shape[0], *xc.shape[1:], dtype=x.dtype, device=x.device)
+        if self.use_link and x.is_cuda and (xc.numel() * xc.element_size()) % 16 == 0:
+            _ops._count()
+            load_extension().allgather_into(out.view(-1), xc.view(-1))
+        else:
+            dist.all_gather_into_tensor(out.view(-1), xc.view(-1), group=self.group)
+        return out
+
+    def allreduce_rmsnorm(self, x, residual, gamma, eps):
+        """(normed, new_residual) where new_residual = all_reduce(x) + residual.
+
+        One kernel on the link when the message fits the one-shot inbox;
+        otherwise all-reduce followed by the add+norm kernel."""
+        if self.world == 1:
+            return _ops.rmsnorm(x, gamma, eps, residual)
+        nbytes = x.numel() * x.element_size()
+        if self.use_link and x.is_cuda and nbytes <= self.oneshot_max and x.is_contiguous():
+            self.ar_calls += 1
+            self.ar_bytes += nbytes
+            _ops._count()
+            normed, res = load_extension().allreduce_rmsnorm(x, residual, gamma, eps, None, residual)
+            return normed, res
+        self.all_reduce(x)
+        if residual is None:
+            normed, _ = _ops.rmsnorm(x, gamma, eps)
+            return normed, x
+        return _ops.rmsnorm(x, gamma, eps, residual)
+
+    def argmax_vocab_parallel(self, logits_local, vocab_per_rank):
+        """Global arg max over vocab-parallel logits [rows, vocab_per_rank]."""
+        idx, val = _ops.argmax(logits_local, self.rank * vocab_per_rank)
+        if self.world == 1:
+            return idx
+        pairs = torch.stack([val, idx.view(torch.float32) if idx.dtype == torch.int32 else idx.float()], -1)
+        if logits_local.is_cuda and self.use_link:
+            rows = pairs.shape[0]
+            pad = (-rows) % 2  # 8 bytes per row: pad to a 16-byte multiple
+            if pad:
+                pairs = torch.cat([pairs, pairs.new_zeros(pad, 2)], 0)
+            allp = torch.empty(self.world, rows + pad, 2, dtype=torch.float32, device=pairs.device)
+            _ops._count(2)
+            load_extension().allgather_into(allp.view(-1), pairs.contiguous().view(-1))
+            return load_extension().argmax_merge(allp[:, :rows].contiguous())
+        vals = [torch.empty_like(val) for _ in range(self.world)]
+        idxs = [torch.empty_like(idx) for _ in range(self.world)]
+        dist.all_gather(vals, val.contiguous(), group=self.group)
+        dist.all_gather(idxs, idx.contiguous(), group=self.group)
+        v = torch.stack(vals, 0)
+        i = torch.stack(idxs, 0)
+        # highest value, lowest index on ties
+        best = v.max(0).values
+        cand = torch.where(v == best[None], i, torch.full_like(i, 2 ** 31 - 1))
+        return cand.min(0).values.to(torch.int32)
+
+    def barrier(self):
+        if self.world > 1:
+            dist.barrier(group=self.group)

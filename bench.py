@@ -1,0 +1,268 @@
+#!/usr/bin/env python
+# SPDX-License-Identifier: MIT
+"""Headline benchmark: greedy decode throughput of a Qwen2.5-7B-shaped decoder
+with tensor parallelism over N GPUs (TP = N), bf16, paged KV cache (block 16),
+1024-token prompts, batch 64 by default.
+
+    python bench.py --gpus 1 --steps 64 --warmup 8
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 64 --warmup 8
+
+A step is one decode step: every sequence of the batch gets its next token.
+`value` is tokens per second of the whole job, timed on the device with CUDA
+events around exactly `--steps` graph replays (max over ranks).  `e2e` is the
+same loop through the public `DecodeEngine.step_host` call: token ids come
+from pinned host memory every step and the sampled ids are read back to the
+host every step.  Weights are random-init N(0, 0.02), prompts are uniform
+random ids (there is no network for checkpoints or datasets).
+
+The reference publishes this metric for other models on 2x RTX 3080
+(demos/qwen_tp/qwen38_int8/worker.py:515-661 is its harness); `--impl
+reference` runs the reference's own code when it can be installed here.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=64)
+    p.add_argument("--warmup", type=int, default=8)
+    p.add_argument("--impl", default="barlink", choices=["barlink", "reference"])
+    p.add_argument("--batch", type=int, default=64)
+    p.add_argument("--prompt", type=int, default=1024)
+    p.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the result invalid)")
+    p.add_argument("--prefill", default="real", choices=["real", "synthetic"],
+                   help="real: run the 1024-token prompts through the model; synthetic: random KV")
+    p.add_argument("--no-graph", action="store_true")
+    p.add_argument("--out", default="")
+    return p.parse_args()
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def reference_arm(args):
+    """The unmodified reference, installed under baseline/_ref, through its own API."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        from baseline.reference_arm import run_reference
+    except Exception as e:  # pragma: no cover
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/reference_arm.py failed to import: %s" % e}))
+        return 0
+    return run_reference(args)
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+
+    import barlink_sm86_b200 as bl
+    from barlink_sm86_b200 import ops, process_group as blpg
+    from barlink_sm86_b200.models import DecodeEngine, Qwen2Config, Qwen2Model
+    from barlink_sm86_b200.parallel import TPComm
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit("bench.py: --gpus %d but WORLD_SIZE=%d" % (args.gpus, world))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("BL_POOL_MB", "1024")
+        blpg.init_process_group(rank=rank, world_size=world)
+        comm = TPComm(dist.group.WORLD)
+    else:
+        comm = TPComm.single()
+
+    cfg = Qwen2Config.qwen25_7b()
+    n_layers = args.layers if args.layers > 0 else None
+    t0 = time.time()
+    model = Qwen2Model(cfg, comm, dev, torch.bfloat16, seed=0, layers=n_layers)
+    torch.cuda.synchronize()
+    load_s = time.time() - t0
+
+    B, S = args.batch, args.prompt
+    total_steps = args.warmup * 2 + args.steps * 2 + 8
+    eng = DecodeEngine(model, B, S + total_steps + 16, use_graph=not args.no_graph)
+    g = torch.Generator(device="cpu").manual_seed(1234)
+    prompt = torch.randint(0, cfg.vocab, (B, S), generator=g, dtype=torch.int32)
+    t0 = time.time()
+    if args.prefill == "real":
+        first = eng.prefill(prompt.to(dev))
+    else:
+        gg = torch.Generator(device=dev).manual_seed(99)
+        for k, v in zip(eng.cache.k, eng.cache.v):
+            k.copy_(torch.randn(k.shape, generator=gg, device=dev, dtype=torch.float32).to(k.dtype))
+            v.copy_(torch.randn(v.shape, generator=gg, device=dev, dtype=torch.float32).to(v.dtype))
+        eng.set_context(S)
+        first = prompt[:, -1].to(dev)
+    torch.cuda.synchronize()
+    prefill_s = time.time() - t0
+    eng.ids.copy_(first)
+    eng.capture()
+
+    def barrier():
+        if world > 1:
+            comm.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-timed: K graph replays back to back --------------------------
+    for _ in range(args.warmup):
+        eng.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = ops.launch_count
+    e0.record()
+    for _ in range(args.steps):
+        eng.step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    launches = eng.launches_per_step * args.steps if eng.graph is not None else ops.launch_count - launches0
+
+    # ---- end to end: ids from pinned host memory in, sampled ids back out -----
+    h_ids = torch.zeros(B, dtype=torch.int32).pin_memory()
+    h_ids.copy_(eng.out_ids.cpu())
+    for _ in range(args.warmup):
+        h_ids.copy_(eng.step_host(h_ids))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        h_ids.copy_(eng.step_host(h_ids))
+    barrier()
+    e2e_s = time.perf_counter() - t0
+
+    t = torch.tensor([ms, e2e_s * 1e3], dtype=torch.float64)
+    if world > 1:
+        tc = t.clone()
+        dist.all_reduce(tc, op=dist.ReduceOp.MAX)
+        t = tc
+    ms, e2e_ms = float(t[0]), float(t[1])
+    tokens = B * args.steps
+    value = tokens / (ms / 1e3)
+    status = bl.status() if world > 1 else {"code": 0}
+    gemm_err = bl.load_extension().gemm_error_flag(local_rank)
+    if rank == 0:
+        out = {
+            "metric": "decode_tokens_per_s",
+            "value": round(value, 1),
+            "unit": "tokens/s",
+            "n_gpus": args.gpus,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": round(ms / args.steps, 4),
+            "higher_is_better": True,
+            "scaling": "strong",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic (uniform random prompt ids, random-init N(0,0.02) weights, seed 0)",
+            "impl": "barlink",
+            "config": {
+                "model": cfg.name + (" TRUNCATED to %d layers (invalid for comparison)" % args.layers
+                                     if args.layers else ""),
+                "hidden": cfg.hidden, "layers": len(model.w.layers), "heads": cfg.n_heads,
+                "kv_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim,
+                "intermediate": cfg.intermediate, "vocab": cfg.vocab,
+                "global_batch": B, "seq_len": S, "decode": "greedy, 1 token/sequence/step",
+                "kv_cache": "paged, block 16", "parallelism": "tp%d" % args.gpus,
+                "prefill": args.prefill,
+                "cuda_graph": eng.graph is not None,
+                "l2": "each step streams %.1f GB of weights plus the KV cache per GPU, far above the 126 MB L2"
+                      % (model.w.nbytes() / 1e9),
+            },
+            "e2e": {
+                "value": round(tokens / (e2e_ms / 1e3), 1),
+                "unit": "tokens/s",
+                "ms_per_step": round(e2e_ms / args.steps, 4),
+                "h2d_bytes_per_step": B * 4,
+                "d2h_bytes_per_step": B * 4,
+            },
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "load_s": round(load_s, 1),
+            "prefill_s": round(prefill_s, 2),
+            "link_status": status.get("code", 0),
+            "gemm_error_flag": gemm_err,
+        }
+        line = json.dumps(out)
+        print(line)
+        if args.out:
+            with open(args.out, "w") as f:
+                f.write(line + "\n")
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+        bl.shutdown()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,162 @@
+# SPDX-License-Identifier: MIT
+"""Numerics of the single-GPU sm_100a kernels against fp32 PyTorch statements
+of the same ops (`barlink_sm86_b200.ops.reference`)."""
+import math
+
+import pytest
+import torch
+
+from conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf(*shape, seed=0, std=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device="cuda") * std).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("tokens,n,k", [
+    (1, 256, 128), (7, 384, 448), (16, 1000, 256), (33, 512, 4096), (64, 3584, 1024),
+    (128, 640, 192), (64, 256, 18944),
+])
+def test_linear_decode_orientation(ext, tokens, n, k):
+    from barlink_sm86_b200.ops import reference as ref
+    x, w = _bf(tokens, k, seed=1), _bf(n, k, seed=2, std=0.05)
+    y = ext.linear(x, w)
+    torch.cuda.synchronize()
+    assert ext.gemm_error_flag(0) == 0
+    want = ref.linear(x, w)
+    assert rel_l2(y, want) < 1e-2, (tokens, n, k)
+
+
+@pytest.mark.parametrize("tokens,n,k", [(256, 512, 256), (300, 640, 320), (1024, 1024, 512), (130, 264, 64)])
+def test_linear_prefill_orientation(ext, tokens, n, k):
+    from barlink_sm86_b200.ops import reference as ref
+    x, w = _bf(tokens, k, seed=3), _bf(n, k, seed=4, std=0.05)
+    y = ext.linear(x, w)
+    torch.cuda.synchronize()
+    assert ext.gemm_error_flag(0) == 0
+    assert rel_l2(y, ref.linear(x, w)) < 1e-2
+
+
+@pytest.mark.parametrize("bn", [16, 32, 64, 128, 256])
+@pytest.mark.parametrize("swap", [0, 1])
+def test_linear_every_tile_width(ext, bn, swap):
+    from barlink_sm86_b200.ops import reference as ref
+    tokens, n, k = (48, 384, 512) if swap else (384, 520, 512)
+    x, w = _bf(tokens, k, seed=5), _bf(n, k, seed=6, std=0.05)
+    y = ext.linear(x, w, force_swap=swap, bn=bn)
+    torch.cuda.synchronize()
+    assert ext.gemm_error_flag(0) == 0
+    assert rel_l2(y, ref.linear(x, w)) < 1e-2
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 8])
+def test_linear_split_k_is_deterministic(ext, splits):
+    from barlink_sm86_b200.ops import reference as ref
+    x, w = _bf(24, 2048, seed=7), _bf(256, 2048, seed=8, std=0.05)
+    y1 = ext.linear(x, w, splits=splits)
+    y2 = ext.linear(x, w, splits=splits)
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y2)
+    assert rel_l2(y1, ref.linear(x, w)) < 1e-2
+
+
+@pytest.mark.parametrize("tokens", [5, 64, 200])
+def test_linear_epilogues(ext, tokens):
+    from barlink_sm86_b200.ops import reference as ref
+    n, k = 512, 256
+    x, w = _bf(tokens, k, seed=9), _bf(n, k, seed=10, std=0.05)
+    b, r = _bf(n, seed=11), _bf(tokens, n, seed=12)
+    assert rel_l2(ext.linear(x, w, b), ref.linear(x, w, b)) < 1e-2
+    assert rel_l2(ext.linear(x, w, b, r), ref.linear(x, w, b, r)) < 1e-2
+    got = ext.linear(x, w, None, None, True)
+    want = ref.linear(x, w, silu_mul=True)
+    assert got.shape == (tokens, n // 2)
+    assert rel_l2(got, want) < 2e-2
+    torch.cuda.synchronize()
+    assert ext.gemm_error_flag(0) == 0
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 3584), (64, 3584), (3, 5120), (17, 512), (5, 8192)])
+def test_rmsnorm(ext, rows, hidden):
+    from barlink_sm86_b200.ops import reference as ref
+    x, g = _bf(rows, hidden, seed=1), _bf(hidden, seed=2)
+    out, _ = ext.rmsnorm(x, g, 1e-6)
+    want, _ = ref.rmsnorm(x, g, 1e-6)
+    assert rel_l2(out, want) < 5e-3
+    res = _bf(rows, hidden, seed=3)
+    res_c = res.clone()
+    out, new_res = ext.rmsnorm(x, g, 1e-6, res)
+    want, want_res = ref.rmsnorm(x, g, 1e-6, res_c)
+    assert torch.equal(new_res, want_res)
+    assert rel_l2(out, want) < 5e-3
+
+
+def test_rope_kv_write(ext):
+    from barlink_sm86_b200.ops import reference as ref
+    rows, nq, nkv, hd, bs = 9, 7, 2, 128, 16
+    qkv = _bf(rows, (nq + 2 * nkv) * hd, seed=1)
+    pos = torch.tensor([0, 1, 5, 17, 100, 1023, 31, 32, 4000], dtype=torch.int32, device="cuda")
+    slots = torch.tensor([3, 17, 40, -1, 64, 65, 2, 99, 130], dtype=torch.int32, device="cuda")
+    kc = torch.zeros(10, nkv, bs, hd, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    q2, kc2, vc2 = qkv.clone(), kc.clone(), vc.clone()
+    ext.rope_kv_write(qkv, pos, slots, kc, vc, nq, nkv, hd, bs, 1e6)
+    ref.rope_kv_write(q2, pos, slots, kc2, vc2, nq, nkv, hd, bs, 1e6)
+    assert rel_l2(qkv, q2) < 5e-3
+    assert rel_l2(kc, kc2) < 5e-3
+    assert torch.equal(vc, vc2)
+
+
+def test_rope_2d(ext):
+    from barlink_sm86_b200.ops import reference as ref
+    rows, heads, hd = 33, 3, 128
+    x = _bf(rows, heads, hd, seed=4)
+    pos = torch.randint(0, 64, (rows, 2), dtype=torch.int32, device="cuda")
+    want = ref.rope(x.clone(), pos, 1e4, axes=2)
+    ext.rope(x.view(rows, heads * hd), pos.contiguous(), heads, hd, 1e4, 2)
+    assert rel_l2(x, want) < 5e-3
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_silu_mul(ext, interleaved):
+    from barlink_sm86_b200.ops import reference as ref
+    gu = _bf(13, 2 * 1376, seed=5)
+    assert rel_l2(ext.silu_mul(gu, interleaved), ref.silu_mul(gu, interleaved)) < 5e-3
+
+
+def test_embedding_and_argmax(ext):
+    from barlink_sm86_b200.ops import reference as ref
+    table = _bf(1000, 512, seed=6)
+    ids = torch.tensor([0, 5, 999, 1000, 250], dtype=torch.int32, device="cuda")
+    assert torch.equal(ext.embedding(ids, table, 0), ref.embedding(ids, table, 0))
+    assert torch.equal(ext.embedding(ids, table[200:600].contiguous(), 200),
+                       ref.embedding(ids, table[200:600], 200))
+    logits = _bf(9, 152064, seed=7)
+    logits[3, 77] = 100.0
+    logits[4, 5] = logits[4, 4000] = 50.0  # tie: lowest index wins
+    idx, val = ext.argmax(logits, 10)
+    want_idx, want_val = ref.argmax(logits, 10)
+    assert torch.equal(idx, want_idx)
+    assert torch.equal(val, want_val)
+    assert idx[4].item() == 15
+
+
+@pytest.mark.parametrize("nq,nkv", [(28, 4), (4, 1), (14, 2), (16, 1)])
+@pytest.mark.parametrize("splits", [1, 0, 3])
+def test_paged_attention_decode(ext, nq, nkv, splits):
+    from barlink_sm86_b200.ops import reference as ref
+    batch, hd, bs, max_blocks = 5, 128, 16, 40
+    ctx = torch.tensor([1, 16, 17, 300, 640], dtype=torch.int32, device="cuda")
+    n_blocks = batch * max_blocks
+    kc = _bf(n_blocks, nkv, bs, hd, seed=1)
+    vc = _bf(n_blocks, nkv, bs, hd, seed=2)
+    perm = torch.randperm(n_blocks, device="cuda", generator=torch.Generator("cuda").manual_seed(3))
+    bt = perm.to(torch.int32).view(batch, max_blocks).contiguous()
+    qkv = _bf(batch, (nq + 2 * nkv) * hd, seed=4)
+    scale = 1.0 / math.sqrt(hd)
+    got = ext.paged_attn_decode(qkv, kc, vc, bt, ctx, nq, nkv, hd, scale, splits)
+    want = ref.paged_attn_decode(qkv, kc, vc, bt, ctx, nq, nkv, hd, scale)
+    assert rel_l2(got, want) < 1e-2
