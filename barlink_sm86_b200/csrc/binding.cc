@@ -440,7 +440,8 @@ int gemm_error_flag(int dev) {
 // are interleaved gate/up pairs and y is [tokens, n/2])
 at::Tensor linear(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
                   const c10::optional<at::Tensor>& residual, bool silu_mul,
-                  c10::optional<at::Tensor> out_opt, int force_swap, int bn, int splits) {
+                  c10::optional<at::Tensor> out_opt, int force_swap, int bn, int splits,
+                  bool dynamic_weights, c10::optional<at::Tensor> trace) {
   check_bf16(w, "weight");
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
               "barlink: x must be a 2-D bfloat16 CUDA tensor with unit inner stride");
@@ -487,6 +488,53 @@ at::Tensor linear(const at::Tensor& x, const at::Tensor& w, const c10::optional<
   a.counters = s.counters.data_ptr();
   a.n_counters = int(s.counters.numel());
   a.err_flag = s.err_flag.data_ptr();
+  a.dynamic_weights = dynamic_weights ? 1 : 0;
+  if (trace) {
+    TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == at::kLong && trace->numel() >= 8 * 296,
+                "barlink: trace must be an int64 CUDA tensor of at least 2368 entries");
+    a.trace = trace->data_ptr();
+  }
+  void* st = at::cuda::getCurrentCUDAStream(dev).stream();
+  {
+    py::gil_scoped_release nogil;
+    BL_CHECK(bl_gemm_bf16(&a, st, err, errlen));
+  }
+  return out;
+}
+
+int gemm_splits(int n, int k, int tokens) { return bl_gemm_splits(n, k, tokens); }
+
+// Split-K linear without a reduction: returns fp32 slabs [splits, tokens, n] that
+// the next kernel (rmsnorm / rope_kv_write / the fused all-reduce) sums as it reads.
+at::Tensor linear_partial(const at::Tensor& x, const at::Tensor& w, int splits,
+                          c10::optional<at::Tensor> out_opt) {
+  check_bf16(w, "weight");
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
+              "barlink: x must be a 2-D bfloat16 CUDA tensor with unit inner stride");
+  TORCH_CHECK(w.dim() == 2 && w.size(1) == x.size(1), "barlink: weight must be [n, k] with k = x.shape[1]");
+  const int tokens = int(x.size(0)), k = int(x.size(1)), n = int(w.size(0));
+  TORCH_CHECK(tokens >= 1 && tokens <= 256, "barlink: linear_partial is the decode path (1..256 tokens)");
+  if (splits <= 0) splits = bl_gemm_splits(n, k, tokens);
+  at::Tensor out = out_opt ? *out_opt
+                           : at::empty({splits, tokens, n}, x.options().dtype(at::kFloat));
+  TORCH_CHECK(out.is_contiguous() && out.scalar_type() == at::kFloat && out.dim() == 3 &&
+                  out.size(0) == splits && out.size(1) == tokens && out.size(2) == n,
+              "barlink: out must be a contiguous float32 [splits, tokens, n] tensor");
+  const int dev = x.device().index();
+  c10::cuda::CUDAGuard guard(x.device());
+  Scratch& s = scratch_for(dev);
+  blGemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.a = w.data_ptr(); a.ra = n; a.lda = k;
+  a.b = x.data_ptr(); a.rb = tokens; a.ldb = int(x.stride(0));
+  a.k = k;
+  a.ldo = n;
+  a.swap = 1;
+  a.partial_out = out.data_ptr();
+  a.partial_stride = size_t(tokens) * n;
+  a.partial_splits = splits;
+  a.splits = splits;
+  a.err_flag = s.err_flag.data_ptr();
   void* st = at::cuda::getCurrentCUDAStream(dev).stream();
   {
     py::gil_scoped_release nogil;
@@ -498,33 +546,66 @@ at::Tensor linear(const at::Tensor& x, const at::Tensor& w, const c10::optional<
 std::tuple<at::Tensor, at::Tensor> rmsnorm(const at::Tensor& x, const at::Tensor& gamma, double eps,
                                            const c10::optional<at::Tensor>& residual,
                                            c10::optional<at::Tensor> out_opt) {
-  check_bf16(x, "x");
   check_bf16(gamma, "gamma");
+  const bool from_slabs = x.scalar_type() == at::kFloat;
+  if (from_slabs) {
+    TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 3,
+                "barlink: split-K slabs must be a contiguous float32 [splits, rows, hidden] CUDA tensor");
+  } else {
+    check_bf16(x, "x");
+  }
   const int hidden = int(x.size(-1));
-  const int rows = int(x.numel() / hidden);
+  const int nsplit = from_slabs ? int(x.size(0)) : 0;
+  const int rows = int(x.numel() / hidden / (from_slabs ? nsplit : 1));
   TORCH_CHECK(gamma.numel() == hidden, "barlink: gamma must have hidden elements");
-  at::Tensor out = out_opt ? *out_opt : at::empty_like(x);
+  at::Tensor out = out_opt ? *out_opt
+                           : at::empty({rows, hidden}, x.options().dtype(at::kBFloat16));
   at::Tensor res_out;
   const void* rin = nullptr;
   void* rout = nullptr;
   if (residual) {
     check_bf16(*residual, "residual");
-    TORCH_CHECK(residual->sizes() == x.sizes(), "barlink: residual must match x");
+    TORCH_CHECK(residual->numel() == int64_t(rows) * hidden, "barlink: residual must match x");
     res_out = *residual;  // updated in place
     rin = residual->data_ptr();
     rout = res_out.data_ptr();
   }
   c10::cuda::CUDAGuard guard(x.device());
   if (rows > 0)
-    BL_CHECK(bl_rmsnorm(x.data_ptr(), rin, gamma.data_ptr(), out.data_ptr(), rout, rows, hidden,
-                        float(eps), stream_of(x), err, errlen));
+    BL_CHECK(bl_rmsnorm(from_slabs ? nullptr : x.data_ptr(), rin, gamma.data_ptr(), out.data_ptr(),
+                        rout, rows, hidden, float(eps), from_slabs ? x.data_ptr() : nullptr, nsplit,
+                        size_t(rows) * hidden, stream_of(x), err, errlen));
   return {out, res_out};
 }
 
-void rope_kv_write(const at::Tensor& qkv, const at::Tensor& positions,
-                   const c10::optional<at::Tensor>& slots, const c10::optional<at::Tensor>& k_cache,
-                   const c10::optional<at::Tensor>& v_cache, int nq, int nkv, int hd, int block_size,
-                   double theta) {
+at::Tensor rope_kv_write(const at::Tensor& qkv_in, const at::Tensor& positions,
+                         const c10::optional<at::Tensor>& slots,
+                         const c10::optional<at::Tensor>& k_cache,
+                         const c10::optional<at::Tensor>& v_cache, int nq, int nkv, int hd,
+                         int block_size, double theta, const c10::optional<at::Tensor>& bias,
+                         c10::optional<at::Tensor> out_opt) {
+  const bool from_slabs = qkv_in.scalar_type() == at::kFloat;
+  at::Tensor qkv = qkv_in;
+  const void* slabs = nullptr;
+  int nsplit = 0;
+  size_t slab = 0;
+  const void* bias_p = nullptr;
+  if (from_slabs) {
+    TORCH_CHECK(qkv_in.is_cuda() && qkv_in.is_contiguous() && qkv_in.dim() == 3,
+                "barlink: split-K slabs must be a contiguous float32 [splits, rows, width] CUDA tensor");
+    nsplit = int(qkv_in.size(0));
+    slab = size_t(qkv_in.size(1)) * size_t(qkv_in.size(2));
+    slabs = qkv_in.data_ptr();
+    qkv = out_opt ? *out_opt
+                  : at::empty({qkv_in.size(1), qkv_in.size(2)}, qkv_in.options().dtype(at::kBFloat16));
+    if (bias) {
+      check_bf16(*bias, "bias");
+      TORCH_CHECK(bias->numel() == qkv_in.size(2), "barlink: bias must match the qkv width");
+      bias_p = bias->data_ptr();
+    }
+  } else {
+    TORCH_CHECK(!bias, "barlink: bias is applied only when the input is split-K slabs");
+  }
   check_bf16(qkv, "qkv");
   TORCH_CHECK(positions.is_cuda() && positions.scalar_type() == at::kInt && positions.is_contiguous(),
               "barlink: positions must be a contiguous int32 CUDA tensor");
@@ -545,8 +626,10 @@ void rope_kv_write(const at::Tensor& qkv, const at::Tensor& positions,
   }
   c10::cuda::CUDAGuard guard(qkv.device());
   if (rows > 0)
-    BL_CHECK(bl_rope_kv_write(qkv.data_ptr(), positions.data_ptr<int>(), sl, kc, vc, rows, nq, nkv,
-                              hd, block_size, float(theta), stream_of(qkv), err, errlen));
+    BL_CHECK(bl_rope_kv_write(qkv.data_ptr(), slabs, nsplit, slab, bias_p, positions.data_ptr<int>(),
+                              sl, kc, vc, rows, nq, nkv, hd, block_size, float(theta), stream_of(qkv),
+                              err, errlen));
+  return qkv;
 }
 
 void rope(const at::Tensor& x, const at::Tensor& positions, int heads, int hd, double theta, int axes) {
@@ -601,13 +684,42 @@ std::tuple<at::Tensor, at::Tensor> argmax(const at::Tensor& logits, int offset) 
   at::Tensor val = at::empty({rows}, logits.options().dtype(at::kFloat));
   c10::cuda::CUDAGuard guard(logits.device());
   if (rows > 0)
+  {
+    Scratch& s = scratch_for(logits.device().index());
     BL_CHECK(bl_argmax(logits.data_ptr(), rows, n, int(logits.stride(0)), offset,
-                       idx.data_ptr<int>(), val.data_ptr<float>(), stream_of(logits), err, errlen));
+                       idx.data_ptr<int>(), val.data_ptr<float>(), s.attn.data_ptr(),
+                       size_t(s.attn.nbytes()), stream_of(logits), err, errlen));
+  }
   return {idx, val};
 }
 
-extern "C" int bl_argmax_merge(const void* pairs, int world, int rows, int* idx, void* stream,
-                               char* err, size_t errlen);
+void decode_advance(const at::Tensor& positions, const at::Tensor& ctx_lens, const at::Tensor& slots,
+                    const at::Tensor& block_tables, const at::Tensor& ids,
+                    const c10::optional<at::Tensor>& sampled, int block_size) {
+  auto chk = [](const at::Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous(), "barlink: ", name,
+                " must be a contiguous int32 CUDA tensor");
+  };
+  chk(positions, "positions");
+  chk(ctx_lens, "ctx_lens");
+  chk(slots, "slots");
+  chk(block_tables, "block_tables");
+  chk(ids, "ids");
+  const int batch = int(positions.numel());
+  TORCH_CHECK(block_tables.dim() == 2 && block_tables.size(0) == batch && ctx_lens.numel() == batch &&
+                  slots.numel() == batch && ids.numel() == batch,
+              "barlink: decode_advance batch mismatch");
+  const int* sp = nullptr;
+  if (sampled) {
+    chk(*sampled, "sampled");
+    sp = sampled->data_ptr<int>();
+  }
+  c10::cuda::CUDAGuard guard(positions.device());
+  BL_CHECK(bl_decode_advance(positions.data_ptr<int>(), ctx_lens.data_ptr<int>(), slots.data_ptr<int>(),
+                             block_tables.data_ptr<int>(), ids.data_ptr<int>(), sp, batch,
+                             int(block_tables.size(1)), block_size, stream_of(positions), err, errlen));
+}
+
 at::Tensor argmax_merge(const at::Tensor& pairs) {
   TORCH_CHECK(pairs.is_cuda() && pairs.scalar_type() == at::kFloat && pairs.dim() == 3 &&
                   pairs.size(2) == 2 && pairs.is_contiguous(),
@@ -689,14 +801,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 
   m.def("linear", &linear, py::arg("x"), py::arg("weight"), py::arg("bias") = py::none(),
         py::arg("residual") = py::none(), py::arg("silu_mul") = false, py::arg("out") = py::none(),
-        py::arg("force_swap") = -1, py::arg("bn") = 0, py::arg("splits") = 0);
+        py::arg("force_swap") = -1, py::arg("bn") = 0, py::arg("splits") = 0,
+        py::arg("dynamic_weights") = false, py::arg("trace") = py::none());
   m.def("gemm_error_flag", &gemm_error_flag, py::arg("device") = 0);
   m.def("rmsnorm", &rmsnorm, py::arg("x"), py::arg("gamma"), py::arg("eps"),
         py::arg("residual") = py::none(), py::arg("out") = py::none());
   m.def("rope_kv_write", &rope_kv_write, py::arg("qkv"), py::arg("positions"),
         py::arg("slots") = py::none(), py::arg("k_cache") = py::none(),
         py::arg("v_cache") = py::none(), py::arg("nq"), py::arg("nkv"), py::arg("hd"),
-        py::arg("block_size") = 16, py::arg("theta") = 1e6);
+        py::arg("block_size") = 16, py::arg("theta") = 1e6, py::arg("bias") = py::none(),
+        py::arg("out") = py::none());
+  m.def("linear_partial", &linear_partial, py::arg("x"), py::arg("weight"), py::arg("splits") = 0,
+        py::arg("out") = py::none());
+  m.def("gemm_splits", &gemm_splits, py::arg("n"), py::arg("k"), py::arg("tokens"));
   m.def("rope", &rope, py::arg("x"), py::arg("positions"), py::arg("heads"), py::arg("hd"),
         py::arg("theta") = 1e4, py::arg("axes") = 1);
   m.def("silu_mul", &silu_mul, py::arg("gate_up"), py::arg("interleaved") = false);
@@ -704,6 +821,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("out") = py::none());
   m.def("argmax", &argmax, py::arg("logits"), py::arg("offset") = 0);
   m.def("argmax_merge", &argmax_merge);
+  m.def("decode_advance", &decode_advance, py::arg("positions"), py::arg("ctx_lens"), py::arg("slots"),
+        py::arg("block_tables"), py::arg("ids"), py::arg("sampled") = py::none(),
+        py::arg("block_size") = 16);
   m.def("paged_attn_decode", &paged_attn_decode, py::arg("qkv"), py::arg("k_cache"),
         py::arg("v_cache"), py::arg("block_tables"), py::arg("ctx_lens"), py::arg("nq"),
         py::arg("nkv"), py::arg("hd"), py::arg("scale"), py::arg("splits") = 0,

@@ -48,8 +48,21 @@ typedef struct blGemmArgs {
   void* counters;
   int n_counters;
   void* err_flag; /* u32 in device or host-mapped memory, set to 1 on a wait that ran out */
+  int dynamic_weights; /* 1: the weight operand may be written by the kernel just before this
+                          one in the stream, so it is not fetched ahead of that kernel's end */
+  /* split-K without a reduction in the GEMM: when partial_out is set, split s
+   * stores its raw fp32 tile to partial_out[s * partial_stride + token * ldo +
+   * feature] and out/bias/residual/silu_mul are ignored; partial_splits is the
+   * exact number of splits (see bl_gemm_splits) */
+  void* partial_out;
+  size_t partial_stride;
+  int partial_splits;
+  void* trace; /* debug: u64[8 * grid] global-timer stamps per CTA, or null */
 } blGemmArgs;
 int bl_gemm_bf16(const blGemmArgs* a, void* stream, char* err, size_t errlen);
+/* k-splits the decode heuristic picks for n output features, k inputs and
+ * `tokens` rows (1 = no split) */
+int bl_gemm_splits(int n, int k, int tokens);
 
 /* W8A16: x [m x k] bf16, wq [n x k] int8 (row = output channel), scale [n]
  * bf16 (per channel) or scales [k/group x n] fp32 (group > 0).  out [m x n]
@@ -83,16 +96,21 @@ int bl_w8a16_gemm(const void* xq, const void* xs, const void* wq_t, const void* 
 
 /* out = RMSNorm(x (+ residual)) * gamma; when residual is given, x + residual
  * is also written to residual_out (may alias residual). */
+/* partials != null: x is instead the sum of nsplit fp32 slabs (slab elements
+ * apart) left by a split-K linear, rounded to bf16 first */
 int bl_rmsnorm(const void* x, const void* residual, const void* gamma, void* out,
-               void* residual_out, int rows, int hidden, float eps, void* stream, char* err,
-               size_t errlen);
+               void* residual_out, int rows, int hidden, float eps, const void* partials,
+               int nsplit, size_t slab, void* stream, char* err, size_t errlen);
 /* qkv [rows x (nq+2*nkv)*hd]: rotate q and k in place (rotate-half RoPE at
  * positions[rows]) and write k, v into the paged cache at slot[rows]
  * (slot = block*block_size + offset; negative = skip).  Cache layout
  * [blocks, nkv, block_size, hd]. */
-int bl_rope_kv_write(void* qkv, const int* positions, const int* slots, void* k_cache,
-                     void* v_cache, int rows, int nq, int nkv, int hd, int block_size, float theta,
-                     void* stream, char* err, size_t errlen);
+/* partials != null: the input is the sum of nsplit fp32 slabs of the QKV
+ * linear plus bias (bf16 [(nq+2nkv)*hd] or null); qkv is then output only */
+int bl_rope_kv_write(void* qkv, const void* partials, int nsplit, size_t slab, const void* bias,
+                     const int* positions, const int* slots, void* k_cache, void* v_cache, int rows,
+                     int nq, int nkv, int hd, int block_size, float theta, void* stream, char* err,
+                     size_t errlen);
 /* plain RoPE on [rows x heads x hd] (2-D variant: positions has 2 ints per
  * row and each half of hd rotates by its own axis) */
 int bl_rope(void* x, const int* positions, int rows, int heads, int hd, int row_stride, float theta,
@@ -121,7 +139,15 @@ int bl_attn_fwd(const void* q, const void* k, const void* v, void* out, const in
 /* arg max over the last dim of [rows x n] bf16 logits -> idx (int32) and
  * value (fp32); `offset` is added to the index (vocab-parallel shards). */
 int bl_argmax(const void* logits, int rows, int n, int ld, int offset, int* idx, float* val,
-              void* stream, char* err, size_t errlen);
+              void* scratch, size_t scratch_bytes, void* stream, char* err, size_t errlen);
+/* merge [parts x rows] (value, index bits) pairs: highest value, lowest index */
+int bl_argmax_merge(const void* pairs, int parts, int rows, int* idx, void* stream, char* err,
+                    size_t errlen);
+/* device-side bookkeeping of one decode step (positions, context lengths,
+ * KV slots, next input ids) so that a captured step can be replayed */
+int bl_decode_advance(int* positions, int* ctx_lens, int* slots, const int* block_tables, int* ids,
+                      const int* sampled, int batch, int max_blocks, int block_size, void* stream,
+                      char* err, size_t errlen);
 
 /* ---- fused GEMM + collective (tensor-parallel linears) ------------------- */
 /* Row-parallel linear fused with reduce-scatter over tokens: every rank

@@ -41,17 +41,24 @@ struct GemmShape {
   int kblocks;              // ceil(k/64)
   int splits;               // k-splits per tile
   int ab_fmt;               // 1 = bf16, 0 = fp16
+  int direct;               // 1: every k-split hands its raw partial tile to the Sink (no in-kernel reduce)
+  int weights_in_a;         // operand that no earlier kernel writes: 1 = A, 0 = B, 2 = neither
   float* ws;                // [tiles*splits][BN][128] fp32 partials (splits > 1)
   uint32_t* counters;       // [tiles] arrival counters, zero between launches
   uint32_t* err;            // set to 1 when a wait inside the kernel ran out
+  unsigned long long* trace; // debug: 8 global-timer stamps per CTA, or nullptr
 };
 
-template <int BN>
+template <int BN, int CPS = 1>
 struct GemmSmem {
   static constexpr int kStageA = kTileA * kTileK * 2;
   static constexpr int kStageB = BN * kTileK * 2;
   static constexpr int kStageBytes = kStageA + kStageB;
-  static constexpr int kStages = (BN <= 64) ? 8 : (BN <= 128 ? 6 : 4);
+  // narrow tiles (decode): 4 stages so that two CTAs share an SM -- the same
+  // bytes in flight per SM, but a CTA of the next kernel can move in and
+  // prefetch weights while one of this kernel is still in its epilogue
+  static constexpr int kStages = (CPS == 2) ? 4 : (BN <= 64 ? 8 : (BN <= 128 ? 6 : 4));
+  static constexpr int kCtasPerSm = CPS;
   static constexpr int kBarBytes = 1024;
   // + 1024 so that the tile ring can be aligned to the swizzle atom
   static constexpr int kBytes = kStages * kStageBytes + kBarBytes + 1024;
@@ -59,16 +66,16 @@ struct GemmSmem {
 };
 
 // Sink concept:
-//   __device__ void operator()(int tile_a, int tile_b, int row_in_tile, int col0,
+//   __device__ void operator()(int tile_a, int tile_b, int split, int row_in_tile, int col0,
 //                              const float (&v)[32], int ncols) const;
 // called by each of the 128 epilogue threads (row_in_tile = TMEM lane) once per
 // 32-column chunk of a finished tile; all 32 threads of a warp call it together.
 
-template <int BN, class Sink>
+template <int BN, int CPS, class Sink>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUtensorMap* tmap_b,
                                           const GemmShape& g, const Sink& sink, uint64_t hint_a,
                                           uint64_t hint_b) {
-  using S = GemmSmem<BN>;
+  using S = GemmSmem<BN, CPS>;
   extern __shared__ uint8_t smem_raw[];
   // barriers first, then the 1024-aligned stage ring
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem_raw);
@@ -80,6 +87,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
   uint32_t* s_last = tmem_slot + 2;
   const uint32_t ring = (smem_u32(smem_raw) + S::kBarBytes + 1023u) & ~1023u;
 
+  // the next kernel of the stream may start its own preamble from here on
+  pdl_launch_dependents();
+  unsigned long long* tr = g.trace ? g.trace + size_t(blockIdx.x) * 8 : nullptr;
+  if (tr && threadIdx.x == 0) tr[0] = globaltimer_ns();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int tiles = g.tiles_a * g.tiles_b;
@@ -108,10 +119,33 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (tr && threadIdx.x == 0) tr[1] = globaltimer_ns();
 
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
     if (lane == 0) {
+      // Weights do not depend on the kernels before this one: the first lap
+      // of weight tiles is requested before waiting for them, so HBM keeps
+      // streaming across the kernel boundary.  Activation tiles follow once
+      // the predecessors have completed.
+      int pre = 0;
+      for (int u = blockIdx.x; g.weights_in_a != 2 && u < units && pre < S::kStages; u += gridDim.x) {
+        const int tile = u / g.splits, sp = u - tile * g.splits;
+        const int ta = tile / g.tiles_b, tb = tile - ta * g.tiles_b;
+        const int kb0 = sp * kb_per;
+        const int kb1 = min(g.kblocks, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1 && pre < S::kStages; ++kb, ++pre) {
+          mbar_expect_tx(&full_bar[pre], S::kStageBytes);
+          const uint32_t sa = ring + pre * S::kStageBytes;
+          if (g.weights_in_a)
+            tma_load_2d_hint_s(sa, tmap_a, smem_u32(&full_bar[pre]), kb * kTileK, ta * kTileA, hint_a);
+          else
+            tma_load_2d_hint_s(sa + S::kStageA, tmap_b, smem_u32(&full_bar[pre]), kb * kTileK,
+                               tb * BN, hint_b);
+        }
+      }
+      pdl_wait();
+      if (tr) tr[2] = globaltimer_ns();
       int stage = 0;
       uint32_t phase = 0;
       int armed = 0;
@@ -122,16 +156,21 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
         const int kb0 = sp * kb_per;
         const int kb1 = min(g.kblocks, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, s_abort)) {
-            ok = false;
-            break;
-          }
-          mbar_expect_tx(&full_bar[stage], S::kStageBytes);
           const uint32_t sa = ring + stage * S::kStageBytes;
-          tma_load_2d_hint_s(sa, tmap_a, smem_u32(&full_bar[stage]), kb * kTileK, ta * kTileA,
-                             hint_a);
-          tma_load_2d_hint_s(sa + S::kStageA, tmap_b, smem_u32(&full_bar[stage]), kb * kTileK,
-                             tb * BN, hint_b);
+          const bool early = armed < pre;  // weight tile of this stage is already on its way
+          if (!early) {
+            if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, s_abort)) {
+              ok = false;
+              break;
+            }
+            mbar_expect_tx(&full_bar[stage], S::kStageBytes);
+          }
+          if (!early || !g.weights_in_a)
+            tma_load_2d_hint_s(sa, tmap_a, smem_u32(&full_bar[stage]), kb * kTileK, ta * kTileA,
+                               hint_a);
+          if (!early || g.weights_in_a)
+            tma_load_2d_hint_s(sa + S::kStageA, tmap_b, smem_u32(&full_bar[stage]), kb * kTileK,
+                               tb * BN, hint_b);
           ++armed;
           if (++stage == S::kStages) {
             stage = 0;
@@ -179,6 +218,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
             break;
           }
           tc_fence_after_sync();
+          if (tr && kb == kb0 && it == 0) tr[3] = globaltimer_ns();
           const uint32_t sa = ring + stage * S::kStageBytes;
           const uint64_t da = umma_desc_k_sw128(sa);
           const uint64_t db = umma_desc_k_sw128(sa + S::kStageA);
@@ -204,6 +244,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
     const int et = threadIdx.x - 64;  // 0..127
     uint32_t tphase[2] = {0, 0};
     int it = 0;
+    pdl_wait();  // outputs, residuals and the split-K scratch belong to earlier kernels until now
     for (int u = blockIdx.x; u < units; u += gridDim.x, ++it) {
       const int tile = u / g.splits, sp = u - tile * g.splits;
       const int ta = tile / g.tiles_b, tb = tile - ta * g.tiles_b;
@@ -211,8 +252,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
       if (!mbar_wait_bounded(&tfull_bar[acc], tphase[acc], s_abort)) break;
       tphase[acc] ^= 1u;
       tc_fence_after_sync();
+      if (tr && et == 0 && it == 0) tr[4] = globaltimer_ns();
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * BN);
-      if (g.splits == 1) {
+      if (g.splits == 1 || g.direct) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
           float v[32];
@@ -231,13 +273,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
 #pragma unroll
             for (int i = 16; i < 32; ++i) v[i] = 0.f;
           }
-          sink(ta, tb, row, c0, v, BN < 32 ? BN : 32);
+          sink(ta, tb, sp, row, c0, v, BN < 32 ? BN : 32);
         }
         tc_fence_before_sync();
         mbar_arrive(&tempty_bar[acc]);
       } else {
-        // partial tile -> workspace [unit][col][row]
-        float* wp = g.ws + size_t(u) * (BN * kTileA);
+        // partial tile -> workspace [unit][row][col] (each thread owns a row)
+        float4* wp = reinterpret_cast<float4*>(g.ws + (size_t(u) * kTileA + row) * BN);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
           if constexpr (BN >= 32) {
@@ -245,13 +287,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
             tmem_ld_32x32(taddr + c0, r);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) wp[(c0 + i) * kTileA + row] = __uint_as_float(r[i]);
+            for (int i = 0; i < 32; i += 4)
+              __stcg(wp + (c0 + i) / 4, make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]),
+                                                    __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])));
           } else {
             uint32_t r[16];
             tmem_ld_32x16(taddr + c0, r);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) wp[(c0 + i) * kTileA + row] = __uint_as_float(r[i]);
+            for (int i = 0; i < 16; i += 4)
+              __stcg(wp + (c0 + i) / 4, make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]),
+                                                    __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])));
           }
         }
         tc_fence_before_sync();
@@ -264,21 +310,32 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
           if (old == uint32_t(g.splits - 1)) g.counters[tile] = 0;
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (tr && et == 0 && it == 0) tr[5] = globaltimer_ns();
         if (*s_last) {
           __threadfence();
-          const float* base = g.ws + size_t(tile) * g.splits * (BN * kTileA);
+          const float* base = g.ws + (size_t(tile) * g.splits * kTileA + row) * BN;
 #pragma unroll 1
           for (int c0 = 0; c0 < BN; c0 += 32) {
+            constexpr int kW = BN < 32 ? BN : 32;
             float v[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            // splits are summed in order: the result does not depend on arrival order
             for (int s2 = 0; s2 < g.splits; ++s2) {
-              const float* p = base + size_t(s2) * (BN * kTileA) + c0 * kTileA + row;
+              const float4* p =
+                  reinterpret_cast<const float4*>(base + size_t(s2) * (BN * kTileA) + c0);
 #pragma unroll
-              for (int i = 0; i < (BN < 32 ? BN : 32); ++i) v[i] += __ldcg(p + i * kTileA);
+              for (int i = 0; i < kW / 4; ++i) {
+                const float4 f = __ldcg(p + i);
+                v[4 * i] += f.x;
+                v[4 * i + 1] += f.y;
+                v[4 * i + 2] += f.z;
+                v[4 * i + 3] += f.w;
+              }
             }
-            sink(ta, tb, row, c0, v, BN < 32 ? BN : 32);
+            sink(ta, tb, 0, row, c0, v, kW);
           }
+          if (tr && et == 0 && it == 0) tr[7] = globaltimer_ns();
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
@@ -287,6 +344,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
 
   tc_fence_before_sync();
   __syncthreads();
+  if (tr && threadIdx.x == 0) tr[6] = globaltimer_ns();
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, S::kTmemCols);

@@ -7,6 +7,7 @@
 // layers through cuBLAS (demos/qwen_tp/qwen38_int8/worker.py:224) or its
 // dp4a kernel (torch_ext/barlink_sm86/w8a16.cu:94-153).
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -15,6 +16,7 @@
 #include "bl_ops.h"
 #include "gemm_core.cuh"
 #include "heap.h"
+#include "launch.h"
 
 namespace bl {
 
@@ -31,8 +33,8 @@ struct LocalSink {
   const __nv_bfloat16* residual;
   int ldo, ra, rb, swap, epi;
 
-  __device__ __forceinline__ void operator()(int ta, int tb, int row, int c0, const float (&v)[32],
-                                             int ncols) const {
+  __device__ __forceinline__ void operator()(int ta, int tb, int /*split*/, int row, int c0,
+                                             const float (&v)[32], int ncols) const {
     const int i = ta * kTileA + row;
     const int j0 = tb * BN + c0;
     if (!swap) {
@@ -125,11 +127,55 @@ struct LocalSink {
   }
 };
 
-template <int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int BN, int CPS>
+__global__ void __launch_bounds__(kGemmThreads, CPS)
     k_gemm(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
            GemmShape g, LocalSink<BN> sink, uint64_t hint_a, uint64_t hint_b) {
-  gemm_body<BN>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
+  gemm_body<BN, CPS>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
+}
+
+// Epilogue of the split-K decode path: every k-split stores its raw fp32
+// partial tile to slab[split][token][feature]; the kernel that consumes the
+// linear's output (add+RMSNorm, RoPE+KV write, the fused all-reduce) sums the
+// slabs while it reads them, so the GEMM has no reduction tail at all.
+template <int BN>
+struct PartialSink {
+  float* out;          // [splits][tokens][n]
+  size_t slab;         // elements per split
+  int ldo, ra, rb, swap;
+
+  __device__ __forceinline__ void operator()(int ta, int tb, int split, int row, int c0,
+                                             const float (&v)[32], int ncols) const {
+    const int i = ta * kTileA + row;
+    const int j0 = tb * BN + c0;
+    float* base = out + size_t(split) * slab;
+    if (swap) {
+      if (i >= ra) return;  // i = feature, j = token: a warp stores 32 consecutive features
+#pragma unroll
+      for (int c = 0; c < 32; ++c)
+        if (c < ncols && j0 + c < rb) __stcg(base + size_t(j0 + c) * ldo + i, v[c]);
+    } else {
+      if (i >= ra) return;  // i = token, j = feature
+      float* orow = base + size_t(i) * ldo;
+      if (ncols == 32 && j0 + 32 <= rb && (ldo & 3) == 0) {
+#pragma unroll
+        for (int c = 0; c < 32; c += 4)
+          __stcg(reinterpret_cast<float4*>(orow + j0 + c), make_float4(v[c], v[c + 1], v[c + 2], v[c + 3]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          if (c < ncols && j0 + c < rb) __stcg(orow + j0 + c, v[c]);
+      }
+    }
+  }
+};
+
+template <int BN, int CPS>
+__global__ void __launch_bounds__(kGemmThreads, CPS)
+    k_gemm_partial(const __grid_constant__ CUtensorMap tmap_a,
+                   const __grid_constant__ CUtensorMap tmap_b, GemmShape g, PartialSink<BN> sink,
+                   uint64_t hint_a, uint64_t hint_b) {
+  gemm_body<BN, CPS>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
 }
 
 // ---------------------------------------------------------------------------
@@ -232,10 +278,15 @@ int pick_splits(int tiles, int kblocks, int sms, int want) {
   return (kblocks + per - 1) / per;
 }
 
-template <int BN>
+static int env_int_or(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return (v && *v) ? atoi(v) : dflt;
+}
+
+template <int BN, int CPS>
 static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, char* err,
                        size_t errlen) {
-  using S = GemmSmem<BN>;
+  using S = GemmSmem<BN, CPS>;
   CUtensorMap ta, tb;
   if (make_tmap_kmajor(a.a, a.ra, a.k, a.lda, kTileA, 2, &ta, err, errlen) != 0) return -1;
   if (make_tmap_kmajor(a.b, a.rb, a.k, a.ldb, BN, 2, &tb, err, errlen) != 0) return -1;
@@ -248,42 +299,85 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
   g.kblocks = (a.k + kTileK - 1) / kTileK;
   const int tiles = g.tiles_a * g.tiles_b;
   const int sms = sm_count();
-  g.splits = pick_splits(tiles, g.kblocks, sms, splits_want);
-  if (g.splits > 1) {
+  // CTAs launched at most (BL_GEMM_WAVE: percent of the resident slots)
+  static const int wave = env_int_or("BL_GEMM_WAVE", 100);
+  int slots = sms * S::kCtasPerSm * wave / 100;
+  if (slots < 1) slots = 1;
+  g.splits = pick_splits(tiles, g.kblocks, slots, splits_want);
+  const bool partial = a.partial_out != nullptr;
+  if (partial) {
+    if (a.partial_splits < 1 || g.splits > a.partial_splits) g.splits = a.partial_splits;
+    // the caller sized the slabs for exactly partial_splits; fewer is not allowed
+    const int per = (g.kblocks + a.partial_splits - 1) / a.partial_splits;
+    if ((g.kblocks + per - 1) / per != a.partial_splits) {
+      set_err(err, errlen, "barlink: %d k-splits do not divide %d k-blocks into non-empty parts",
+              a.partial_splits, g.kblocks);
+      return -1;
+    }
+    g.splits = a.partial_splits;
+  } else if (g.splits > 1) {
     const size_t need = size_t(tiles) * g.splits * BN * kTileA * sizeof(float);
     if (!a.ws || a.ws_bytes < need || !a.counters || a.n_counters < tiles) g.splits = 1;
   }
+  g.direct = 0;
   g.ab_fmt = 1;
+  g.weights_in_a = a.dynamic_weights ? 2 : (a.swap ? 1 : 0);
   g.ws = static_cast<float*>(a.ws);
   g.counters = static_cast<uint32_t*>(a.counters);
   g.err = static_cast<uint32_t*>(a.err_flag);
-  LocalSink<BN> sink;
-  sink.out = static_cast<__nv_bfloat16*>(a.out);
-  sink.bias = static_cast<const __nv_bfloat16*>(a.bias);
-  sink.residual = static_cast<const __nv_bfloat16*>(a.residual);
-  sink.ldo = a.ldo;
-  sink.ra = a.ra;
-  sink.rb = a.rb;
-  sink.swap = a.swap;
-  sink.epi = (a.bias ? 1 : 0) | (a.residual ? 2 : 0) | (a.silu_mul ? 4 : 0);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(k_gemm<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         S::kBytes);
-    if (e != cudaSuccess) {
-      set_err(err, errlen, "barlink: cannot raise shared memory to %d B: %s", S::kBytes,
-              cudaGetErrorString(e));
-      return -1;
-    }
-    attr_set = true;
-  }
+  g.trace = static_cast<unsigned long long*>(a.trace);
   const int units = tiles * g.splits;
-  const int grid = units < sms ? units : sms;
+  const int grid = units < slots ? units : slots;
   // weights stream through L2 once, activations are re-read by every CTA
   const uint64_t hint_w = kHintEvictFirst, hint_x = kHintEvictLast;
-  k_gemm<BN><<<grid, kGemmThreads, S::kBytes, st>>>(ta, tb, g, sink, a.swap ? hint_w : hint_x,
-                                                    a.swap ? hint_x : hint_w);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e;
+  if (partial) {
+    g.direct = 1;
+    PartialSink<BN> ps;
+    ps.out = static_cast<float*>(a.partial_out);
+    ps.slab = a.partial_stride;
+    ps.ldo = a.ldo;
+    ps.ra = a.ra;
+    ps.rb = a.rb;
+    ps.swap = a.swap;
+    static bool attr_p = false;
+    if (!attr_p) {
+      e = cudaFuncSetAttribute(k_gemm_partial<BN, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               S::kBytes);
+      if (e != cudaSuccess) {
+        set_err(err, errlen, "barlink: cannot raise shared memory to %d B: %s", S::kBytes,
+                cudaGetErrorString(e));
+        return -1;
+      }
+      attr_p = true;
+    }
+    e = launch_k(k_gemm_partial<BN, CPS>, dim3(grid), dim3(kGemmThreads), size_t(S::kBytes), st, ta,
+                 tb, g, ps, a.swap ? hint_w : hint_x, a.swap ? hint_x : hint_w);
+  } else {
+    LocalSink<BN> sink;
+    sink.out = static_cast<__nv_bfloat16*>(a.out);
+    sink.bias = static_cast<const __nv_bfloat16*>(a.bias);
+    sink.residual = static_cast<const __nv_bfloat16*>(a.residual);
+    sink.ldo = a.ldo;
+    sink.ra = a.ra;
+    sink.rb = a.rb;
+    sink.swap = a.swap;
+    sink.epi = (a.bias ? 1 : 0) | (a.residual ? 2 : 0) | (a.silu_mul ? 4 : 0);
+    static bool attr_set = false;
+    if (!attr_set) {
+      e = cudaFuncSetAttribute(k_gemm<BN, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               S::kBytes);
+      if (e != cudaSuccess) {
+        set_err(err, errlen, "barlink: cannot raise shared memory to %d B: %s", S::kBytes,
+                cudaGetErrorString(e));
+        return -1;
+      }
+      attr_set = true;
+    }
+    e = launch_k(k_gemm<BN, CPS>, dim3(grid), dim3(kGemmThreads), size_t(S::kBytes), st, ta, tb, g,
+                 sink, a.swap ? hint_w : hint_x, a.swap ? hint_x : hint_w);
+  }
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_err(err, errlen, "barlink: GEMM launch failed: %s", cudaGetErrorString(e));
     return -1;
@@ -295,8 +389,15 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
 
 using namespace bl;
 
+extern "C" int bl_gemm_splits(int n, int k, int tokens) {
+  if (tokens > 128) return 1;
+  const int tiles = (n + kTileA - 1) / kTileA;
+  const int kblocks = (k + kTileK - 1) / kTileK;
+  return pick_splits(tiles, kblocks, sm_count(), 0);
+}
+
 extern "C" int bl_gemm_bf16(const blGemmArgs* a, void* stream, char* err, size_t errlen) {
-  if (!a || !a->a || !a->b || !a->out || a->ra < 1 || a->rb < 1 || a->k < 8 || (a->k & 7)) {
+  if (!a || !a->a || !a->b || (!a->out && !a->partial_out) || a->ra < 1 || a->rb < 1 || a->k < 8 || (a->k & 7)) {
     set_err(err, errlen, "barlink: gemm needs non-null operands and K a multiple of 8");
     return -1;
   }
@@ -306,12 +407,16 @@ extern "C" int bl_gemm_bf16(const blGemmArgs* a, void* stream, char* err, size_t
     if (a->swap) bn = a->rb <= 16 ? 16 : a->rb <= 32 ? 32 : a->rb <= 64 ? 64 : a->rb <= 128 ? 128 : 256;
     else bn = a->rb >= 256 ? 256 : a->rb > 64 ? 128 : 64;
   }
+  static const int cps = env_int_or("BL_GEMM_CPS", 1);
   switch (bn) {
-    case 16: return launch_gemm<16>(*a, a->splits, st, err, errlen);
-    case 32: return launch_gemm<32>(*a, a->splits, st, err, errlen);
-    case 64: return launch_gemm<64>(*a, a->splits, st, err, errlen);
-    case 128: return launch_gemm<128>(*a, a->splits, st, err, errlen);
-    case 256: return launch_gemm<256>(*a, a->splits, st, err, errlen);
+    case 16: return cps == 2 ? launch_gemm<16, 2>(*a, a->splits, st, err, errlen)
+                             : launch_gemm<16, 1>(*a, a->splits, st, err, errlen);
+    case 32: return cps == 2 ? launch_gemm<32, 2>(*a, a->splits, st, err, errlen)
+                             : launch_gemm<32, 1>(*a, a->splits, st, err, errlen);
+    case 64: return cps == 2 ? launch_gemm<64, 2>(*a, a->splits, st, err, errlen)
+                             : launch_gemm<64, 1>(*a, a->splits, st, err, errlen);
+    case 128: return launch_gemm<128, 1>(*a, a->splits, st, err, errlen);
+    case 256: return launch_gemm<256, 1>(*a, a->splits, st, err, errlen);
     default:
       set_err(err, errlen, "barlink: gemm tile width %d not in {16,32,64,128,256}", bn);
       return -1;

@@ -11,6 +11,7 @@
 
 #include "bl_ops.h"
 #include "heap.h"
+#include "launch.h"
 #include "ptx.cuh"
 
 namespace bl {
@@ -34,7 +35,10 @@ __global__ void __launch_bounds__(512) k_rmsnorm(const uint4* __restrict__ x,
                                                  const uint4* __restrict__ gamma,
                                                  uint4* __restrict__ out,
                                                  uint4* __restrict__ residual_out, int vpr,
-                                                 float eps) {
+                                                 float eps, const float* __restrict__ partials,
+                                                 int nsplit, size_t slab) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float s_part[16];
   __shared__ float s_rstd;
   const size_t row = blockIdx.x;
@@ -44,7 +48,23 @@ __global__ void __launch_bounds__(512) k_rmsnorm(const uint4* __restrict__ x,
   for (int k = 0; k < kNormMaxVpt; ++k) {
     const int i = threadIdx.x + k * blockDim.x;
     if (i < vpr) {
-      const uint4 a = x[row * vpr + i];
+      uint4 a;
+      if (partials) {
+        // x is the sum of the k-split slabs of the linear before this norm,
+        // rounded to bf16 as that linear's output would have been
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const float* pp = partials + (row * vpr + i) * 8;
+        for (int sp = 0; sp < nsplit; ++sp) {
+          const float4 u = __ldcg(reinterpret_cast<const float4*>(pp + sp * slab));
+          const float4 w = __ldcg(reinterpret_cast<const float4*>(pp + sp * slab) + 1);
+          acc[0] += u.x; acc[1] += u.y; acc[2] += u.z; acc[3] += u.w;
+          acc[4] += w.x; acc[5] += w.y; acc[6] += w.z; acc[7] += w.w;
+        }
+        a = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                       pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+      } else {
+        a = x[row * vpr + i];
+      }
       float2 p0 = unpack_bf16x2(a.x), p1 = unpack_bf16x2(a.y), p2 = unpack_bf16x2(a.z),
              p3 = unpack_bf16x2(a.w);
       float f[8] = {p0.x, p0.y, p1.x, p1.y, p2.x, p2.y, p3.x, p3.y};
@@ -102,50 +122,75 @@ __global__ void __launch_bounds__(512) k_rmsnorm(const uint4* __restrict__ x,
 // ---------------------------------------------------------------------------
 // RoPE (rotate-half) on q and k of a fused qkv row + paged KV write
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) k_rope_kv_write(__nv_bfloat16* __restrict__ qkv,
+// grid (rows, ceil((nq+nkv+nkv)/kRopeHeads)): each block rotates kRopeHeads
+// heads of one row, one (head, pair) per thread; V heads are copied.
+constexpr int kRopeHeads = 4;
+__global__ void __launch_bounds__(256) k_rope_kv_write(__nv_bfloat16* __restrict__ qkv,
+                                                       const float* __restrict__ partials,
+                                                       int nsplit, size_t slab,
+                                                       const __nv_bfloat16* __restrict__ bias,
                                                        const int* __restrict__ positions,
                                                        const int* __restrict__ slots,
                                                        __nv_bfloat16* __restrict__ k_cache,
                                                        __nv_bfloat16* __restrict__ v_cache, int nq,
                                                        int nkv, int hd, int block_size,
                                                        float log2_theta) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const int half = hd >> 1;
-  const int groups = blockDim.x / half;  // heads handled in parallel
   const int i = threadIdx.x % half;
-  const int grp = threadIdx.x / half;
-  __nv_bfloat16* base = qkv + size_t(row) * (nq + 2 * nkv) * hd;
+  const int hpb = blockDim.x / half;  // heads per block
+  const int h = blockIdx.y * hpb + threadIdx.x / half;
+  if (threadIdx.x / half >= hpb || h >= nq + 2 * nkv) return;
+  __nv_bfloat16* p = qkv + (size_t(row) * (nq + 2 * nkv) + h) * hd;
+  // input: the qkv buffer itself, or the k-split slabs of the QKV linear (+ bias)
+  float in1, in2;
+  if (partials) {
+    const size_t e = (size_t(row) * (nq + 2 * nkv) + h) * hd;
+    float a1 = 0.f, a2 = 0.f;
+    for (int sp = 0; sp < nsplit; ++sp) {
+      a1 += __ldcg(partials + sp * slab + e + i);
+      a2 += __ldcg(partials + sp * slab + e + i + half);
+    }
+    if (bias) {
+      a1 += __bfloat162float(bias[h * hd + i]);
+      a2 += __bfloat162float(bias[h * hd + i + half]);
+    }
+    in1 = __bfloat162float(__float2bfloat16(a1));
+    in2 = __bfloat162float(__float2bfloat16(a2));
+  } else {
+    in1 = __bfloat162float(p[i]);
+    in2 = __bfloat162float(p[i + half]);
+  }
   const int slot = slots ? slots[row] : -1;
   const int blk = slot >= 0 ? slot / block_size : 0;
   const int off = slot >= 0 ? slot % block_size : 0;
-  if (grp < groups) {
+  if (h < nq + nkv) {
     const float pos = float(positions[row]);
     const float inv = exp2f(-log2_theta * (2.f * float(i) / float(hd)));
     float sn, cs;
     sincosf(pos * inv, &sn, &cs);
-    for (int h = grp; h < nq + nkv; h += groups) {
-      __nv_bfloat16* p = base + size_t(h) * hd;
-      const float x1 = __bfloat162float(p[i]), x2 = __bfloat162float(p[i + half]);
-      const __nv_bfloat16 o1 = __float2bfloat16(x1 * cs - x2 * sn);
-      const __nv_bfloat16 o2 = __float2bfloat16(x2 * cs + x1 * sn);
-      p[i] = o1;
-      p[i + half] = o2;
-      if (h >= nq && slot >= 0) {
-        __nv_bfloat16* c =
-            k_cache + ((size_t(blk) * nkv + (h - nq)) * block_size + off) * hd;
-        c[i] = o1;
-        c[i + half] = o2;
-      }
+    const float x1 = in1, x2 = in2;
+    const __nv_bfloat16 o1 = __float2bfloat16(x1 * cs - x2 * sn);
+    const __nv_bfloat16 o2 = __float2bfloat16(x2 * cs + x1 * sn);
+    p[i] = o1;
+    p[i + half] = o2;
+    if (h >= nq && slot >= 0) {
+      __nv_bfloat16* c = k_cache + ((size_t(blk) * nkv + (h - nq)) * block_size + off) * hd;
+      c[i] = o1;
+      c[i + half] = o2;
     }
-  }
-  if (slot >= 0) {
-    // v: plain copy, 16 bytes per thread
-    const int vec_per_head = hd / 8;
-    for (int t = threadIdx.x; t < nkv * vec_per_head; t += blockDim.x) {
-      const int h = t / vec_per_head, c = t % vec_per_head;
-      const uint4 val = *reinterpret_cast<const uint4*>(base + size_t(nq + nkv + h) * hd + c * 8);
-      *reinterpret_cast<uint4*>(v_cache + ((size_t(blk) * nkv + h) * block_size + off) * hd +
-                                c * 8) = val;
+  } else {
+    const __nv_bfloat16 v1 = __float2bfloat16(in1), v2 = __float2bfloat16(in2);
+    if (partials) {
+      p[i] = v1;
+      p[i + half] = v2;
+    }
+    if (slot >= 0) {
+      __nv_bfloat16* c = v_cache + ((size_t(blk) * nkv + (h - nq - nkv)) * block_size + off) * hd;
+      c[i] = v1;
+      c[i + half] = v2;
     }
   }
 }
@@ -154,6 +199,8 @@ __global__ void __launch_bounds__(128) k_rope_kv_write(__nv_bfloat16* __restrict
 __global__ void __launch_bounds__(128) k_rope(__nv_bfloat16* __restrict__ x,
                                               const int* __restrict__ positions, int heads, int hd,
                                               int row_stride, float log2_theta, int axes) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const int sub = hd / axes;   // dims rotated by one axis
   const int half = sub >> 1;
@@ -177,6 +224,8 @@ __global__ void __launch_bounds__(128) k_rope(__nv_bfloat16* __restrict__ x,
 // ---------------------------------------------------------------------------
 __global__ void k_silu_mul(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                            int rows, int inter, int interleaved) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t total = size_t(rows) * inter;
   for (size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
        t += size_t(gridDim.x) * blockDim.x) {
@@ -196,6 +245,8 @@ __global__ void k_silu_mul(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* 
 
 __global__ void k_embedding(const int* __restrict__ ids, const uint4* __restrict__ table,
                             uint4* __restrict__ out, int vpr, int lo, int hi) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const int id = ids[row];
   const bool mine = id >= lo && id < hi;
@@ -206,19 +257,53 @@ __global__ void k_embedding(const int* __restrict__ ids, const uint4* __restrict
 // ---------------------------------------------------------------------------
 // arg max (ties: lowest index)
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) k_argmax(const __nv_bfloat16* __restrict__ logits, int n,
-                                                 int ld, int offset, int* __restrict__ idx,
-                                                 float* __restrict__ val) {
-  __shared__ float s_v[32];
-  __shared__ int s_i[32];
-  const __nv_bfloat16* p = logits + size_t(blockIdx.x) * ld;
+// grid (rows, chunks): each block scans one slice of a row with 16-byte
+// loads and leaves (value, index) in part[chunk][row]; k_argmax_merge picks.
+constexpr int kArgmaxChunks = 16;
+__global__ void __launch_bounds__(256) k_argmax(const __nv_bfloat16* __restrict__ logits, int n,
+                                                int ld, int offset, float2* __restrict__ part,
+                                                int rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float s_v[8];
+  __shared__ int s_i[8];
+  const int row = blockIdx.x, chunk = blockIdx.y;
+  const __nv_bfloat16* p = logits + size_t(row) * ld;
+  const int per = ((n + kArgmaxChunks - 1) / kArgmaxChunks + 7) & ~7;
+  const int lo = chunk * per, hi = min(n, lo + per);
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float f = __bfloat162float(p[i]);
-    if (f > best || (f == best && i < bi)) {
-      best = f;
-      bi = i;
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) && ((ld & 7) == 0);
+  if (vec_ok) {
+    for (int i = lo + threadIdx.x * 8; i < hi; i += blockDim.x * 8) {
+      if (i + 8 <= hi) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p + i);
+        const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z),
+                     d = unpack_bf16x2(v.w);
+        const float f[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (f[j] > best) {  // ascending index inside a thread: first maximum wins
+            best = f[j];
+            bi = i + j;
+          }
+      } else {
+        for (int j = i; j < hi; ++j) {
+          const float f = __bfloat162float(p[j]);
+          if (f > best) {
+            best = f;
+            bi = j;
+          }
+        }
+      }
+    }
+  } else {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const float f = __bfloat162float(p[i]);
+      if (f > best || (f == best && i < bi)) {
+        best = f;
+        bi = i;
+      }
     }
   }
 #pragma unroll
@@ -247,10 +332,9 @@ __global__ void __launch_bounds__(1024) k_argmax(const __nv_bfloat16* __restrict
         bi = oi;
       }
     }
-    if (threadIdx.x == 0) {
-      idx[blockIdx.x] = bi + offset;
-      val[blockIdx.x] = best;
-    }
+    if (threadIdx.x == 0)
+      part[size_t(chunk) * rows + row] =
+          make_float2(best, __int_as_float(bi == 0x7fffffff ? bi : bi + offset));
   }
 }
 
@@ -304,6 +388,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
                         __nv_bfloat16* __restrict__ out, float* __restrict__ scratch, int nq,
                         int nkv, int max_blocks, float scale_log2) {
   extern __shared__ __align__(16) uint8_t smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int h = blockIdx.x, b = blockIdx.y, sp = blockIdx.z, nsplit = gridDim.z;
   const int G = nq / nkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -494,6 +580,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
 
 __global__ void __launch_bounds__(kHd) k_attn_merge(const float* __restrict__ scratch,
                                                     __nv_bfloat16* __restrict__ out, int nsplit) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t bh = blockIdx.x;  // batch*nq + head
   const float* base = scratch + bh * nsplit * (kHd + 2);
   const int d = threadIdx.x;
@@ -512,7 +600,9 @@ __global__ void __launch_bounds__(kHd) k_attn_merge(const float* __restrict__ sc
 // merge per-rank (value, index) pairs of a vocab-parallel arg max:
 // pairs [world][rows] as float2(value, index-as-int-bits)
 __global__ void k_argmax_merge(const float2* __restrict__ pairs, int world, int rows,
-                               int* __restrict__ idx) {
+                               int* __restrict__ idx, float* __restrict__ val) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   float best = -INFINITY;
@@ -526,6 +616,26 @@ __global__ void k_argmax_merge(const float2* __restrict__ pairs, int world, int 
     }
   }
   idx[r] = bi;
+  if (val) val[r] = best;
+}
+
+// One decode step forward on the device: position += 1, context = position + 1,
+// slot = block_table[b][position / bs] * bs + position % bs, next input id =
+// the token just sampled.
+__global__ void k_decode_advance(int* __restrict__ positions, int* __restrict__ ctx_lens,
+                                 int* __restrict__ slots, const int* __restrict__ block_tables,
+                                 int* __restrict__ ids, const int* __restrict__ sampled, int batch,
+                                 int max_blocks, int block_size) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  const int pos = positions[b] + 1;
+  positions[b] = pos;
+  ctx_lens[b] = pos + 1;
+  const int blk = pos / block_size < max_blocks ? block_tables[size_t(b) * max_blocks + pos / block_size] : -1;
+  slots[b] = blk >= 0 ? blk * block_size + pos % block_size : -1;
+  if (sampled) ids[b] = sampled[b];
 }
 
 }  // namespace bl
@@ -533,8 +643,8 @@ __global__ void k_argmax_merge(const float2* __restrict__ pairs, int world, int 
 using namespace bl;
 
 extern "C" int bl_rmsnorm(const void* x, const void* residual, const void* gamma, void* out,
-                          void* residual_out, int rows, int hidden, float eps, void* stream,
-                          char* err, size_t errlen) {
+                          void* residual_out, int rows, int hidden, float eps, const void* partials,
+                          int nsplit, size_t slab, void* stream, char* err, size_t errlen) {
   if (rows < 1 || hidden < 8 || (hidden & 7) || hidden / 8 > 512 * kNormMaxVpt) {
     set_err(err, errlen, "barlink: rmsnorm needs hidden %% 8 == 0 and hidden <= %d", 512 * kNormMaxVpt * 8);
     return -1;
@@ -542,23 +652,28 @@ extern "C" int bl_rmsnorm(const void* x, const void* residual, const void* gamma
   const int vpr = hidden / 8;
   int threads = (vpr + 31) / 32 * 32;
   if (threads > 512) threads = 512;
-  k_rmsnorm<<<rows, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_k(k_rmsnorm, dim3(rows), dim3(threads), 0, static_cast<cudaStream_t>(stream),
       static_cast<const uint4*>(x), static_cast<const uint4*>(residual),
       static_cast<const uint4*>(gamma), static_cast<uint4*>(out), static_cast<uint4*>(residual_out),
-      vpr, eps);
+      vpr, eps, static_cast<const float*>(partials), nsplit, slab);
   OPS_LAUNCH_CHECK("rmsnorm");
   return 0;
 }
 
-extern "C" int bl_rope_kv_write(void* qkv, const int* positions, const int* slots, void* k_cache,
-                                void* v_cache, int rows, int nq, int nkv, int hd, int block_size,
-                                float theta, void* stream, char* err, size_t errlen) {
+extern "C" int bl_rope_kv_write(void* qkv, const void* partials, int nsplit, size_t slab,
+                                const void* bias, const int* positions, const int* slots,
+                                void* k_cache, void* v_cache, int rows, int nq, int nkv, int hd,
+                                int block_size, float theta, void* stream, char* err,
+                                size_t errlen) {
   if (rows < 1 || hd < 16 || (hd & 15) || hd > 256) {
     set_err(err, errlen, "barlink: rope_kv_write needs head_dim in 16..256, multiple of 16");
     return -1;
   }
-  k_rope_kv_write<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__nv_bfloat16*>(qkv), positions, slots, static_cast<__nv_bfloat16*>(k_cache),
+  const int hpb = kRopeHeads * (hd / 2) <= 256 ? kRopeHeads : 256 / (hd / 2);
+  launch_k(k_rope_kv_write, dim3(rows, (nq + 2 * nkv + hpb - 1) / hpb), dim3(hpb * (hd / 2)), 0,
+           static_cast<cudaStream_t>(stream),
+      static_cast<__nv_bfloat16*>(qkv), static_cast<const float*>(partials), nsplit, slab,
+      static_cast<const __nv_bfloat16*>(bias), positions, slots, static_cast<__nv_bfloat16*>(k_cache),
       static_cast<__nv_bfloat16*>(v_cache), nq, nkv, hd, block_size, log2f(theta));
   OPS_LAUNCH_CHECK("rope_kv_write");
   return 0;
@@ -570,7 +685,7 @@ extern "C" int bl_rope(void* x, const int* positions, int rows, int heads, int h
     set_err(err, errlen, "barlink: rope needs head_dim divisible by 2*axes (axes 1 or 2)");
     return -1;
   }
-  k_rope<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_k(k_rope, dim3(rows), dim3(128), 0, static_cast<cudaStream_t>(stream),
       static_cast<__nv_bfloat16*>(x), positions, heads, hd, row_stride, log2f(theta), axes);
   OPS_LAUNCH_CHECK("rope");
   return 0;
@@ -582,7 +697,7 @@ extern "C" int bl_silu_mul(const void* gate_up, void* out, int rows, int inter, 
   int grid = int((total + 255) / 256);
   if (grid > 148 * 8) grid = 148 * 8;
   if (grid < 1) grid = 1;
-  k_silu_mul<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_k(k_silu_mul, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream),
       static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter,
       interleaved);
   OPS_LAUNCH_CHECK("silu_mul");
@@ -595,7 +710,7 @@ extern "C" int bl_embedding(const int* ids, const void* table, void* out, int ro
     set_err(err, errlen, "barlink: embedding needs hidden %% 8 == 0");
     return -1;
   }
-  k_embedding<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_k(k_embedding, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream),
       ids, static_cast<const uint4*>(table), static_cast<uint4*>(out), hidden / 8, vocab_lo,
       vocab_hi);
   OPS_LAUNCH_CHECK("embedding");
@@ -603,17 +718,38 @@ extern "C" int bl_embedding(const int* ids, const void* table, void* out, int ro
 }
 
 extern "C" int bl_argmax(const void* logits, int rows, int n, int ld, int offset, int* idx,
-                         float* val, void* stream, char* err, size_t errlen) {
-  k_argmax<<<rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(logits), n, ld, offset, idx, val);
+                         float* val, void* scratch, size_t scratch_bytes, void* stream, char* err,
+                         size_t errlen) {
+  if (!scratch || scratch_bytes < size_t(rows) * kArgmaxChunks * sizeof(float2)) {
+    set_err(err, errlen, "barlink: argmax needs %zu bytes of scratch",
+            size_t(rows) * kArgmaxChunks * sizeof(float2));
+    return -1;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  launch_k(k_argmax, dim3(rows, kArgmaxChunks), dim3(256), 0, st,
+           static_cast<const __nv_bfloat16*>(logits), n, ld, offset, static_cast<float2*>(scratch),
+           rows);
   OPS_LAUNCH_CHECK("argmax");
+  launch_k(k_argmax_merge, dim3((rows + 127) / 128), dim3(128), 0, st,
+           static_cast<const float2*>(scratch), kArgmaxChunks, rows, idx, val);
+  OPS_LAUNCH_CHECK("argmax_merge");
+  return 0;
+}
+
+extern "C" int bl_decode_advance(int* positions, int* ctx_lens, int* slots, const int* block_tables,
+                                 int* ids, const int* sampled, int batch, int max_blocks,
+                                 int block_size, void* stream, char* err, size_t errlen) {
+  launch_k(k_decode_advance, dim3((batch + 127) / 128), dim3(128), 0,
+           static_cast<cudaStream_t>(stream), positions, ctx_lens, slots, block_tables, ids, sampled,
+           batch, max_blocks, block_size);
+  OPS_LAUNCH_CHECK("decode_advance");
   return 0;
 }
 
 extern "C" int bl_argmax_merge(const void* pairs, int world, int rows, int* idx, void* stream,
                                char* err, size_t errlen) {
-  k_argmax_merge<<<(rows + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const float2*>(pairs), world, rows, idx);
+  launch_k(k_argmax_merge, dim3((rows + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream),
+      static_cast<const float2*>(pairs), world, rows, idx, static_cast<float*>(nullptr));
   OPS_LAUNCH_CHECK("argmax_merge");
   return 0;
 }
@@ -634,7 +770,8 @@ extern "C" int bl_paged_attn_decode(const void* q, int q_stride, const void* k_c
     return -1;
   }
   if (splits <= 0) {
-    const int want = (2 * sm_count() + batch * nkv - 1) / (batch * nkv);
+    // enough CTAs to fill the GPU once; more splits only add merge traffic
+    const int want = (sm_count() + batch * nkv - 1) / (batch * nkv);
     const int by_len = max_blocks / (2 * kAttnWarps) > 0 ? max_blocks / (2 * kAttnWarps) : 1;
     splits = want < by_len ? want : by_len;
     if (splits > 32) splits = 32;
@@ -656,14 +793,14 @@ extern "C" int bl_paged_attn_decode(const void* q, int q_stride, const void* k_c
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const float scale_log2 = scale * 1.4426950408889634f;
-  k_paged_attn_decode<<<dim3(nkv, batch, splits), kAttnWarps * 32, smem, st>>>(
+  launch_k(k_paged_attn_decode, dim3(nkv, batch, splits), dim3(kAttnWarps * 32), smem, st,
       static_cast<const __nv_bfloat16*>(q), q_stride, static_cast<const __nv_bfloat16*>(k_cache),
       static_cast<const __nv_bfloat16*>(v_cache), block_tables, ctx_lens,
       static_cast<__nv_bfloat16*>(out), static_cast<float*>(scratch), nq, nkv, max_blocks,
       scale_log2);
   OPS_LAUNCH_CHECK("paged_attn_decode");
   if (splits > 1) {
-    k_attn_merge<<<batch * nq, kHd, 0, st>>>(static_cast<const float*>(scratch),
+    launch_k(k_attn_merge, dim3(batch * nq), dim3(kHd), 0, st, static_cast<const float*>(scratch),
                                              static_cast<__nv_bfloat16*>(out), splits);
     OPS_LAUNCH_CHECK("attn_merge");
   }

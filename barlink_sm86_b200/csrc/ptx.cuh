@@ -69,9 +69,16 @@ __device__ __forceinline__ void st_volatile_v4(void* p, uint4 v) {
 }
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)::"memory");
   return t;
 }
+
+// programmatic dependent launch: let the next kernel of the stream start its
+// preamble now / wait until every earlier kernel has completed and flushed
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------
 // NVSwitch multimem (NVLS): the address is inside a multicast mapping

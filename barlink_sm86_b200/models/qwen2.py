@@ -162,23 +162,35 @@ class Qwen2Model:
         self.nq, self.nkv, self.hd = self.w.plan.nq, self.w.plan.nkv, cfg.head_dim
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
 
-    def _run_layers(self, ids, positions, attn_factory):
+    def _run_layers(self, ids, positions, attn_factory, split_k=False):
         """ids [T] int32 -> final normed hidden [T, hidden] (replicated on every rank)."""
         cfg, c, w = self.cfg, self.comm, self.w
         h = ops.embedding(ids, w.embed)
         res = torch.zeros_like(h)
+        split_k = split_k and h.is_cuda and c.world == 1
         pending = False  # h holds a partial sum that still needs the all-reduce
         for li, L in enumerate(w.layers):
             if pending:
                 normed, res = c.allreduce_rmsnorm(h, res, L["ln1"], cfg.eps)
             else:
                 normed, res = ops.rmsnorm(h, L["ln1"], cfg.eps, res)
-            qkv = ops.linear(normed, L["wqkv"], L["bqkv"])
-            a = attn_factory(li)(qkv)
-            h = ops.linear(a, L["wo"])
+            if split_k:
+                # decode: k-split linears leave fp32 slabs that the next kernel sums
+                qkv = ops.linear_split(normed, L["wqkv"])
+                if qkv.dtype == torch.float32:
+                    a = attn_factory(li)(qkv, L["bqkv"])
+                else:
+                    if L["bqkv"] is not None:
+                        qkv = qkv + L["bqkv"]
+                    a = attn_factory(li)(qkv, None)
+                h = ops.linear_split(a, L["wo"])
+            else:
+                qkv = ops.linear(normed, L["wqkv"], L["bqkv"])
+                a = attn_factory(li)(qkv, None)
+                h = ops.linear(a, L["wo"])
             normed, res = c.allreduce_rmsnorm(h, res, L["ln2"], cfg.eps)
             act = ops.linear(normed, L["wgu"], silu_mul=True)
-            h = ops.linear(act, L["wdown"])
+            h = ops.linear_split(act, L["wdown"]) if split_k else ops.linear(act, L["wdown"])
             pending = True
         if pending:
             normed, res = c.allreduce_rmsnorm(h, res, w.ln_f, cfg.eps)
@@ -198,11 +210,12 @@ class Qwen2Model:
         nq, nkv, hd = self.nq, self.nkv, self.hd
 
         def attn_factory(li):
-            def attn(qkv):
+            def attn(qkv, bias=None):
                 kc = cache.k[li] if cache is not None else None
                 vc = cache.v[li] if cache is not None else None
-                ops.rope_kv_write(qkv, positions, slots, kc, vc, nq, nkv, hd,
-                                  cache.block_size if cache is not None else 16, self.cfg.theta)
+                qkv = ops.rope_kv_write(qkv, positions, slots, kc, vc, nq, nkv, hd,
+                                        cache.block_size if cache is not None else 16, self.cfg.theta,
+                                        bias)
                 T = qkv.shape[0]
                 v3 = qkv.view(T, nq + 2 * nkv, hd)
                 o = ops.attention(v3[:, :nq], v3[:, nq:nq + nkv], v3[:, nq + nkv:], cu, cu, seq,
@@ -217,14 +230,14 @@ class Qwen2Model:
         nq, nkv, hd = self.nq, self.nkv, self.hd
 
         def attn_factory(li):
-            def attn(qkv):
-                ops.rope_kv_write(qkv, positions, slots, cache.k[li], cache.v[li], nq, nkv, hd,
-                                  cache.block_size, self.cfg.theta)
+            def attn(qkv, bias=None):
+                qkv = ops.rope_kv_write(qkv, positions, slots, cache.k[li], cache.v[li], nq, nkv, hd,
+                                        cache.block_size, self.cfg.theta, bias)
                 return ops.paged_attn_decode(qkv, cache.k[li], cache.v[li], cache.block_tables,
                                              ctx_lens, nq, nkv, hd, self.scale, splits)
             return attn
 
-        return self._run_layers(ids, positions, attn_factory)
+        return self._run_layers(ids, positions, attn_factory, split_k=True)
 
     def logits_local(self, hidden):
         return ops.linear(hidden, self.w.lm_head)
@@ -295,9 +308,17 @@ class DecodeEngine:
                                       self.attn_splits)
         nxt = self.m.next_tokens(hidden)
         self.out_ids.copy_(nxt)
-        self.ids.copy_(nxt)  # replays feed themselves unless the caller overwrites ids
-        self.positions.add_(1)
-        self._refresh()
+        if self.m.device.type == "cuda":
+            # one kernel: position, context length, KV slot and next input id
+            from .. import load_extension
+            ops._count()
+            load_extension().decode_advance(self.positions, self.ctx_lens, self.slots,
+                                            self.cache.block_tables, self.ids, self.out_ids,
+                                            self.cache.block_size)
+        else:
+            self.ids.copy_(nxt)  # replays feed themselves unless the caller overwrites ids
+            self.positions.add_(1)
+            self._refresh()
 
     def capture(self, warmup: int = 2):
         """Warm up (allocator, lazy attributes) and capture the step."""

@@ -35,6 +35,20 @@ def linear(x, weight, bias=None, residual=None, silu_mul=False, out=None):
     return ref.linear(x, weight, bias, residual, silu_mul)
 
 
+def linear_split(x, weight):
+    """Decode-path linear: when the shape wants a k-split, returns fp32 slabs
+    [splits, tokens, n] whose sum is x @ weight.T (the consumer -- `rmsnorm`,
+    `rope_kv_write`, the fused all-reduce -- adds them while reading, so the
+    GEMM has no reduction tail); otherwise the plain bf16 result."""
+    if x.is_cuda and x.dim() == 2 and x.shape[0] <= 128:
+        C = _C()
+        splits = C.gemm_splits(weight.shape[0], weight.shape[1], x.shape[0])
+        if splits > 1:
+            _count()
+            return C.linear_partial(x, weight, splits)
+    return linear(x, weight)
+
+
 def rmsnorm(x, gamma, eps, residual=None, out=None):
     """Returns (normed, residual); the residual tensor is updated in place on CUDA."""
     if x.is_cuda:
@@ -43,11 +57,15 @@ def rmsnorm(x, gamma, eps, residual=None, out=None):
     return ref.rmsnorm(x, gamma, eps, residual)
 
 
-def rope_kv_write(qkv, positions, slots, k_cache, v_cache, nq, nkv, hd, block_size, theta):
+def rope_kv_write(qkv, positions, slots, k_cache, v_cache, nq, nkv, hd, block_size, theta, bias=None):
+    """qkv: bf16 [rows, width] rotated in place, or fp32 split-K slabs of the
+    QKV linear (then `bias` is added and a new bf16 buffer is returned)."""
     if qkv.is_cuda:
         _count()
-        _C().rope_kv_write(qkv, positions, slots, k_cache, v_cache, nq, nkv, hd, block_size, theta)
-        return qkv
+        return _C().rope_kv_write(qkv, positions, slots, k_cache, v_cache, nq, nkv, hd, block_size,
+                                  theta, bias)
+    if bias is not None:
+        qkv = (qkv.float() + bias.float()).to(qkv.dtype)
     return ref.rope_kv_write(qkv, positions, slots, k_cache, v_cache, nq, nkv, hd, block_size, theta)
 
 

@@ -160,3 +160,75 @@ def test_paged_attention_decode(ext, nq, nkv, splits):
     got = ext.paged_attn_decode(qkv, kc, vc, bt, ctx, nq, nkv, hd, scale, splits)
     want = ref.paged_attn_decode(qkv, kc, vc, bt, ctx, nq, nkv, hd, scale)
     assert rel_l2(got, want) < 1e-2
+
+
+@pytest.mark.parametrize("tokens,n,k,splits", [(64, 4608, 3584, 4), (8, 3584, 18944, 5), (1, 512, 1024, 2),
+                                               (33, 640, 1024, 3)])
+def test_linear_split_slabs_sum_to_the_product(ext, tokens, n, k, splits):
+    from barlink_sm86_b200.ops import reference as ref
+    x, w = _bf(tokens, k, seed=21), _bf(n, k, seed=22, std=0.05)
+    slabs = ext.linear_partial(x, w, splits)
+    torch.cuda.synchronize()
+    assert ext.gemm_error_flag(0) == 0
+    assert slabs.shape == (splits, tokens, n) and slabs.dtype == torch.float32
+    want = x.float() @ w.float().t()
+    assert rel_l2(slabs.sum(0), want) < 1e-3
+
+
+def test_rmsnorm_and_rope_consume_slabs(ext):
+    from barlink_sm86_b200.ops import reference as ref
+    rows, hidden, S = 9, 3584, 4
+    g = torch.Generator(device="cuda").manual_seed(5)
+    slabs = torch.randn(S, rows, hidden, device="cuda", generator=g)
+    gamma, res = _bf(hidden, seed=6), _bf(rows, hidden, seed=7)
+    x = slabs.sum(0).to(torch.bfloat16)
+    want, want_res = ref.rmsnorm(x, gamma, 1e-6, res.clone())
+    got, got_res = ext.rmsnorm(slabs, gamma, 1e-6, res)
+    assert torch.equal(got_res, want_res)
+    assert rel_l2(got, want) < 5e-3
+    # rope + kv write from slabs with bias
+    nq, nkv, hd, bs = 7, 2, 128, 16
+    width = (nq + 2 * nkv) * hd
+    slabs = torch.randn(3, rows, width, device="cuda", generator=g)
+    bias = _bf(width, seed=8)
+    pos = torch.arange(rows, dtype=torch.int32, device="cuda") * 37
+    slots = torch.arange(rows, dtype=torch.int32, device="cuda") * 3 + 1
+    kc = torch.zeros(4, nkv, bs, hd, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    kc2, vc2 = kc.clone(), vc.clone()
+    q_in = (slabs.sum(0) + bias.float()).to(torch.bfloat16)
+    want = ref.rope_kv_write(q_in.clone(), pos, slots, kc2, vc2, nq, nkv, hd, bs, 1e6)
+    got = ext.rope_kv_write(slabs, pos, slots, kc, vc, nq, nkv, hd, bs, 1e6, bias)
+    assert rel_l2(got, want) < 5e-3
+    assert rel_l2(kc, kc2) < 5e-3
+    assert torch.equal(vc, vc2)
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("nq,nkv", [(4, 1), (6, 2)])
+def test_dense_attention(ext, causal, nq, nkv):
+    from barlink_sm86_b200.ops import reference as ref
+    hd = 128
+    lens_q = [70, 1, 129, 64]
+    lens_k = lens_q if causal else [70, 33, 200, 64]
+    cu_q = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32, device="cuda")
+    cu_k = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32, device="cuda")
+    q = _bf(sum(lens_q), nq, hd, seed=1)
+    k = _bf(sum(lens_k), nkv, hd, seed=2)
+    v = _bf(sum(lens_k), nkv, hd, seed=3)
+    scale = 1.0 / math.sqrt(hd)
+    got = ext.attn_fwd(q, k, v, cu_q, cu_k, max(lens_q), scale, causal)
+    want = ref.attention(q, k, v, cu_q.cpu(), cu_k.cpu(), scale, causal)
+    assert rel_l2(got, want) < 1e-2
+
+
+def test_dense_attention_on_fused_qkv_views(ext):
+    from barlink_sm86_b200.ops import reference as ref
+    T, nq, nkv, hd = 200, 4, 1, 128
+    qkv = _bf(T, (nq + 2 * nkv) * hd, seed=4)
+    v3 = qkv.view(T, nq + 2 * nkv, hd)
+    cu = torch.tensor([0, 120, 200], dtype=torch.int32, device="cuda")
+    scale = 1.0 / math.sqrt(hd)
+    got = ext.attn_fwd(v3[:, :nq], v3[:, nq:nq + nkv], v3[:, nq + nkv:], cu, cu, 120, scale, True)
+    want = ref.attention(v3[:, :nq], v3[:, nq:nq + nkv], v3[:, nq + nkv:], cu.cpu(), cu.cpu(), scale, True)
+    assert rel_l2(got, want) < 1e-2
