@@ -9,6 +9,8 @@
 // one launch per layer.
 #include <stdio.h>
 
+#include <mutex>
+
 #include "bl_ops.h"
 #include "heap.h"
 #include "launch.h"
@@ -804,5 +806,67 @@ extern "C" int bl_paged_attn_decode(const void* q, int q_stride, const void* k_c
                                              static_cast<__nv_bfloat16*>(out), splits);
     OPS_LAUNCH_CHECK("attn_merge");
   }
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// arg max for callers that may not allocate (see bl_noalloc.h)
+// ---------------------------------------------------------------------------
+#include "bl_noalloc.h"
+
+namespace bl {
+// Partial (value, index) pairs of k_argmax: [kArgmaxChunks][rows].  Part of
+// the library image, so no call ever has to allocate it.  In host code this
+// name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float2 g_argmax_scratch[BL_ARGMAX_NOALLOC_MAX_ROWS * kArgmaxChunks];
+
+constexpr int kNoallocMaxDevices = 64;
+static float2* g_argmax_scratch_addr[kNoallocMaxDevices];  // per device, filled on first use
+static std::mutex g_argmax_scratch_mu;
+}  // namespace bl
+
+extern "C" int bl_argmax_noalloc(const void* logits, int rows, int n, int ld, int offset, int* idx,
+                                 float* val, void* stream, char* err, size_t errlen) {
+  if (!logits || !idx || rows < 1 || n < 1 || ld < n) {
+    set_err(err, errlen, "barlink: argmax_noalloc needs logits, idx, rows >= 1, n >= 1 and ld >= n");
+    return -1;
+  }
+  if (rows > BL_ARGMAX_NOALLOC_MAX_ROWS) {
+    set_err(err, errlen,
+            "barlink: argmax_noalloc handles at most %d rows per call (%d given); split the batch or "
+            "use bl_argmax with a scratch buffer of your own",
+            BL_ARGMAX_NOALLOC_MAX_ROWS, rows);
+    return -1;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kNoallocMaxDevices) {
+    set_err(err, errlen, "barlink: argmax_noalloc cannot tell the current device: %s",
+            e != cudaSuccess ? cudaGetErrorString(e) : "ordinal out of range");
+    return -1;
+  }
+  float2* scratch = nullptr;
+  {
+    // once per device, with that device current: the array's address there
+    std::lock_guard<std::mutex> g(g_argmax_scratch_mu);
+    if (!g_argmax_scratch_addr[dev]) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_argmax_scratch);
+      if (e != cudaSuccess || !p) {
+        set_err(err, errlen, "barlink: argmax_noalloc could not resolve its scratch array on device %d: %s",
+                dev, cudaGetErrorString(e));
+        return -1;
+      }
+      g_argmax_scratch_addr[dev] = static_cast<float2*>(p);
+    }
+    scratch = g_argmax_scratch_addr[dev];
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // plain launches: this path must not depend on how the caller's other kernels were launched
+  k_argmax<<<dim3(rows, kArgmaxChunks), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(logits), n, ld,
+                                                     offset, scratch, rows);
+  OPS_LAUNCH_CHECK("argmax_noalloc");
+  k_argmax_merge<<<(rows + 127) / 128, 128, 0, st>>>(scratch, kArgmaxChunks, rows, idx, val);
+  OPS_LAUNCH_CHECK("argmax_noalloc merge");
   return 0;
 }
