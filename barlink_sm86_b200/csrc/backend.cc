@@ -49,6 +49,15 @@ BarlinkBackend::BarlinkBackend(int rank, int size, c10::intrusive_ptr<c10d::Back
   }
 }
 
+void BarlinkBackend::drain_sends() {
+  for (auto& e : inflight_) {
+    cudaEventSynchronize(e.first);
+    cudaEventDestroy(e.first);
+  }
+  cudaGetLastError();
+  inflight_.clear();
+}
+
 c10::intrusive_ptr<c10d::Work> BarlinkBackend::done(c10d::OpType op, std::vector<at::Tensor> outs) {
   return c10::make_intrusive<DoneWork>(getRank(), op, std::move(outs));
 }
@@ -226,8 +235,22 @@ void BarlinkBackend::send_cuda(const at::Tensor& t, int dst) {
     const size_t len = std::min(chunk, bytes - off);
     BL_CALL(bl_send_into_peer(c, p + off, len, dst, st, err, errlen));
   }
-  // the caller may overwrite or free the tensor once we return in stream order
-  bl_join_sends(c, st);
+  // Sends run on the link's own stream so that a recv queued behind them can
+  // make progress (several sends outstanding before the first recv would
+  // otherwise deadlock a pair).  The buffer is kept alive here until that
+  // stream has read it; any later collective joins the stream.
+  if (void* ss = bl_send_stream(c)) {
+    while (!inflight_.empty() && cudaEventQuery(inflight_.front().first) == cudaSuccess) {
+      cudaEventDestroy(inflight_.front().first);
+      inflight_.pop_front();
+    }
+    cudaGetLastError();
+    cudaEvent_t ev;
+    if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) == cudaSuccess) {
+      cudaEventRecord(ev, static_cast<cudaStream_t>(ss));
+      inflight_.emplace_back(ev, src);
+    }
+  }
 }
 
 void BarlinkBackend::recv_cuda(at::Tensor& t, int src) {

@@ -17,6 +17,10 @@
 #include <torch/csrc/distributed/c10d/Work.hpp>
 #include <torch/torch.h>
 
+#include <cuda_runtime.h>
+
+#include <deque>
+
 #include "bl_core.h"
 
 namespace blpg {
@@ -90,8 +94,9 @@ class BarlinkBackend : public c10d::Backend {
                                       int tag) override;
   c10::intrusive_ptr<c10d::Work> recvAnysource(std::vector<at::Tensor>& tensors, int tag) override;
 
-  void shutdown() override {}
-  void abort() override {}
+  void shutdown() override { drain_sends(); }
+  void abort() override { drain_sends(); }
+  ~BarlinkBackend() override { drain_sends(); }
 
   // counters for tests: how many ops took which path
   int64_t n_zero_copy = 0, n_staged = 0, n_cpu = 0, n_local = 0;
@@ -107,8 +112,12 @@ class BarlinkBackend : public c10d::Backend {
   c10d::Backend& cpu(const char* what);
   blCtx* link();
 
+  void drain_sends();
+
   c10::intrusive_ptr<c10d::Backend> cpu_;
   bool use_link_;
+  // tensors handed to send() whose copy on the send stream may still be running
+  std::deque<std::pair<cudaEvent_t, at::Tensor>> inflight_;
 };
 
 }  // namespace blpg

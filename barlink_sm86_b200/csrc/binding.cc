@@ -318,7 +318,10 @@ void send_into(const at::Tensor& t, int peer) {
   void* st = stream_of(t);
   py::gil_scoped_release nogil;
   BL_CHECK(bl_send_into_peer(c, t.data_ptr(), t.nbytes(), peer, st, err, errlen));
-  bl_join_sends(c, st);
+}
+void join_sends() {
+  blCtx* c = ctx_or_throw();
+  bl_join_sends(c, at::cuda::getCurrentCUDAStream().stream());
 }
 void recv_into(const at::Tensor& t, int peer) {
   blCtx* c = ctx_or_throw();
@@ -789,6 +792,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("eps"), py::arg("normed_out") = py::none(), py::arg("residual_out") = py::none());
   m.def("send_into", &send_into, py::arg("t"), py::arg("peer_rank"));
   m.def("recv_into", &recv_into, py::arg("t"), py::arg("peer_rank"));
+  m.def("join_sends", &join_sends);
   m.def("verify", &verify);
   m.def("readback", &readback);
   m.def("pool_move", &pool_move, py::arg("out"), py::arg("src"));

@@ -130,6 +130,8 @@ int bl_recv_into_peer(blCtx* ctx, void* outPtr, size_t bytes, int peerRank, void
  * waits for every send issued so far (call it before overwriting a sent
  * buffer). */
 int bl_join_sends(blCtx* ctx, void* stream);
+/* the stream sends run on (cudaStream_t), or null */
+void* bl_send_stream(blCtx* ctx);
 
 /* ---- proofs and diagnostics ------------------------------------------- */
 uint64_t bl_verify(blCtx* ctx, char* err, size_t errlen);

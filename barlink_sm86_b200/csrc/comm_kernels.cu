@@ -937,8 +937,18 @@ static int check_health(blCtx* ctx, char* err, size_t errlen) {
 
 template <typename K>
 static int launch_local(blCtx* ctx, K kernel, CollArgs base, const PerRank* pr, int grid_x,
-                        int threads, char* err, size_t errlen) {
+                        int threads, char* err, size_t errlen, bool join_sends = true) {
   if (ctx->peer_mode) {
+    // collectives are ordered after every send issued so far
+    if (join_sends && ctx->send_pending) {
+      cudaStream_t cs = static_cast<cudaStream_t>(pr[0].stream);
+      cudaStreamCaptureStatus cst = cudaStreamCaptureStatusNone;
+      if (cudaStreamIsCapturing(cs, &cst) == cudaSuccess && cst == cudaStreamCaptureStatusNone) {
+        cudaStreamWaitEvent(cs, ctx->ev_send, 0);
+        ctx->send_pending = false;
+      }
+      cudaGetLastError();
+    }
     CollArgs a = base;
     a.pack.c = ctx->comm_for(ctx->rank);
     a.pack.emu = nullptr;
@@ -1517,12 +1527,12 @@ extern "C" int bl_send_into_peer(blCtx* ctx, const void* inPtr, size_t bytes, in
   // outstanding before the first recv would otherwise deadlock a pair).
   if (no_side || stream_capturing(caller)) {
     pr.stream = caller;
-    if (launch_local(ctx, k_p2p_send, a, &pr, grid, kThreads, err, errlen) != 0) return -1;
+    if (launch_local(ctx, k_p2p_send, a, &pr, grid, kThreads, err, errlen, false) != 0) return -1;
   } else {
     RT_TRY(cudaEventRecord(ctx->ev_caller, caller), "event record");
     RT_TRY(cudaStreamWaitEvent(ctx->send_stream, ctx->ev_caller, 0), "stream wait");
     pr.stream = ctx->send_stream;
-    if (launch_local(ctx, k_p2p_send, a, &pr, grid, kThreads, err, errlen) != 0) return -1;
+    if (launch_local(ctx, k_p2p_send, a, &pr, grid, kThreads, err, errlen, false) != 0) return -1;
     RT_TRY(cudaEventRecord(ctx->ev_send, ctx->send_stream), "event record");
     ctx->send_pending = true;
   }
@@ -1542,13 +1552,15 @@ extern "C" int bl_recv_into_peer(blCtx* ctx, void* outPtr, size_t bytes, int pee
   pr.out = outPtr;
   pr.stream = stream;
   const int grid = pick_grid(ctx, a.nvec, kThreads, 64);
-  if (launch_local(ctx, k_p2p_recv, a, &pr, grid, kThreads, err, errlen) != 0) return -1;
+  if (launch_local(ctx, k_p2p_recv, a, &pr, grid, kThreads, err, errlen, false) != 0) return -1;
   ctx->stats[BL_STAT_P2P]++;
   return 0;
 }
 
 // make later work on `stream` wait for sends issued so far (used by the
 // binding before a tensor that was sent may be overwritten)
+extern "C" void* bl_send_stream(blCtx* ctx) { return ctx && ctx->peer_mode ? ctx->send_stream : nullptr; }
+
 extern "C" int bl_join_sends(blCtx* ctx, void* stream) {
   if (!ctx || !ctx->peer_mode) return 0;
   join_send_stream(ctx, static_cast<cudaStream_t>(stream));

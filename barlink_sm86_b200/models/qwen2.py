@@ -145,9 +145,10 @@ class PagedKV:
         self.block_tables = (torch.arange(n_blocks, dtype=torch.int32, device=device)
                              .view(batch, self.blocks_per_seq).contiguous())
 
-    def slots(self, positions_2d):
-        """positions [batch, s] -> flat slot ids [batch*s] (int32)."""
-        b = torch.arange(positions_2d.shape[0], device=positions_2d.device)[:, None]
+    def slots(self, positions_2d, seq_offset=0):
+        """positions [batch, s] -> flat slot ids [batch*s] (int32); the rows are
+        sequences seq_offset .. seq_offset + batch of the cache."""
+        b = torch.arange(positions_2d.shape[0], device=positions_2d.device)[:, None] + seq_offset
         blk = self.block_tables[b, (positions_2d // self.block_size).long()]
         return (blk * self.block_size + positions_2d % self.block_size).to(torch.int32).reshape(-1)
 
@@ -199,13 +200,14 @@ class Qwen2Model:
         return normed
 
     # ---- prefill: dense causal attention, optional KV write ----------------
-    def prefill(self, ids_2d, cache: Optional[PagedKV] = None, chunk_rows: int = 0):
-        """ids [batch, seq] -> final normed hidden [batch*seq, hidden]."""
+    def prefill(self, ids_2d, cache: Optional[PagedKV] = None, seq_offset: int = 0):
+        """ids [batch, seq] -> final normed hidden [batch*seq, hidden]; with a
+        cache, K/V of sequence i go to cache sequence seq_offset + i."""
         batch, seq = ids_2d.shape
         dev = ids_2d.device
         pos2d = torch.arange(seq, device=dev, dtype=torch.int32)[None, :].expand(batch, seq).contiguous()
         positions = pos2d.reshape(-1)
-        slots = cache.slots(pos2d) if cache is not None else None
+        slots = cache.slots(pos2d, seq_offset) if cache is not None else None
         cu = torch.arange(0, (batch + 1) * seq, seq, device=dev, dtype=torch.int32)
         nq, nkv, hd = self.nq, self.nkv, self.hd
 
@@ -295,10 +297,17 @@ class DecodeEngine:
         self.slots.copy_(blk * c.block_size + self.positions % c.block_size)
         self.ctx_lens.copy_(self.positions + 1)
 
-    def prefill(self, ids_2d):
-        hidden = self.m.prefill(ids_2d, self.cache)
+    def prefill(self, ids_2d, max_tokens: int = 8192):
+        """Run the prompts through the model (a few sequences at a time, at most
+        `max_tokens` tokens per pass) and return the first generated token."""
         seq = ids_2d.shape[1]
-        last = hidden.view(self.batch, seq, -1)[:, -1].contiguous()
+        per = max(1, max_tokens // seq)
+        lasts = []
+        for b0 in range(0, self.batch, per):
+            part = ids_2d[b0:b0 + per].contiguous()
+            hidden = self.m.prefill(part, self.cache, seq_offset=b0)
+            lasts.append(hidden.view(part.shape[0], seq, -1)[:, -1])
+        last = torch.cat(lasts, 0).contiguous()
         nxt = self.m.next_tokens(last)
         self.set_context(seq)
         return nxt

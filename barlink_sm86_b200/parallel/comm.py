@@ -35,6 +35,7 @@ class TPComm:
                     use_link = False
         self.use_link = use_link
         self.oneshot_max = load_extension().info()["oneshot_max"] if use_link else 0
+        self.max_chunk = load_extension().info()["max_chunk"] if use_link else 0
         self.ar_calls = 0
         self.ar_bytes = 0
 
@@ -43,7 +44,7 @@ class TPComm:
         """A communicator of one rank: every collective is a local no-op."""
         c = cls.__new__(cls)
         c.group, c.world, c.rank = None, 1, 0
-        c.use_link, c.oneshot_max, c.ar_calls, c.ar_bytes = False, 0, 0, 0
+        c.use_link, c.oneshot_max, c.ar_calls, c.ar_bytes, c.max_chunk = False, 0, 0, 0, 0
         return c
 
     # ---- collectives -----------------------------------------------------
@@ -55,8 +56,17 @@ class TPComm:
         self.ar_bytes += x.numel() * x.element_size()
         if self.use_link and x.is_cuda and x.is_contiguous() and (x.numel() * x.element_size()) % 16 == 0 \
                 and x.data_ptr() % 16 == 0:
-            _ops._count()
-            load_extension().allreduce_into(x, x)
+            nbytes = x.numel() * x.element_size()
+            if nbytes <= self.max_chunk:
+                _ops._count()
+                load_extension().allreduce_into(x, x)
+            else:
+                flat = x.view(-1)
+                step = (self.max_chunk // 16 * 16) // x.element_size()
+                for i in range(0, flat.numel(), step):
+                    _ops._count()
+                    part = flat[i:i + step]
+                    load_extension().allreduce_into(part, part)
             return x
         dist.all_reduce(x, group=self.group)
         return x

@@ -1,0 +1,272 @@
+# SPDX-License-Identifier: MIT
+"""One rank of the multi-GPU process-group test (started by test_pg_gpu.py).
+
+Same fixtures as the reference's distributed tests
+(torch_ext/tests/test_process_group.py:24-197, test_pg_p2p.py:42-245,
+test_pg_gather.py:24-62): rank-seeded data so that every rank can compute the
+expected result locally, and argument errors that must be raised before any
+traffic so that a failing check cannot desynchronise the ranks."""
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import barlink_sm86_b200 as bl  # noqa: E402
+from barlink_sm86_b200 import process_group as blpg  # noqa: E402
+
+rank, world, port = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3])
+os.environ["LOCAL_RANK"] = str(rank)
+os.environ.setdefault("BL_POOL_MB", "512")
+torch.cuda.set_device(rank)
+dev = torch.device("cuda", rank)
+blpg.init_process_group(init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
+C = bl.load_extension()
+info = bl.info()
+assert info["peer_mode"] and info["world"] == world and info["rank"] == rank, info
+
+
+def log(msg):
+    if rank == 0:
+        print("[pg] " + msg, flush=True)
+
+
+def seeded(r, n, dtype, lo=-3, hi=4):
+    g = torch.Generator(device="cpu").manual_seed(1000 + r)
+    return torch.randint(lo, hi, (n,), generator=g).to(dtype)
+
+
+def expect_sum(n, dtype):
+    acc = torch.zeros(n, dtype=torch.float64)
+    for r in range(world):
+        acc += seeded(r, n, torch.float64)
+    return acc.to(dtype)
+
+
+def host_barrier():
+    t = torch.zeros(1)
+    dist.all_reduce(t)  # CPU tensor: gloo companion
+
+
+# ---- proof of every path ------------------------------------------------------
+assert bl.verify() == 0
+log("verify ok (multicast=%s)" % info["multicast"])
+
+# ---- all_reduce: sizes, dtypes, algorithms ------------------------------------------
+for nbytes in (1024, 1 << 20, 32 << 20, (96 << 20) + 16):
+    n = nbytes // 4
+    t = seeded(rank, n, torch.float32).to(dev)
+    dist.all_reduce(t)
+    assert torch.equal(t.cpu(), expect_sum(n, torch.float32)), nbytes
+log("all_reduce sizes ok")
+for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.float64, torch.float8_e4m3fn,
+              torch.float8_e5m2):
+    n = 4096
+    t = seeded(rank, n, torch.float32).to(dtype).to(dev)
+    dist.all_reduce(t)
+    assert torch.equal(t.cpu().view(torch.uint8), expect_sum(n, torch.float32).to(dtype).view(torch.uint8)), dtype
+u = torch.arange(4096, dtype=torch.int64).mul(rank + 7).remainder(256).to(torch.uint8).to(dev)
+dist.all_reduce(u)
+want = sum(torch.arange(4096, dtype=torch.int64).mul(r + 7).remainder(256) for r in range(world)).remainder(256)
+assert torch.equal(u.cpu().long(), want)
+log("all_reduce dtypes ok")
+algos = ["oneshot", "twoshot"] + (["nvls"] if info["multicast"] else [])
+for algo in algos:
+    for nbytes in (16, 10240, 256 << 10, 4 << 20):
+        n = nbytes // 2
+        x = seeded(rank, n, torch.bfloat16).to(dev)
+        out = torch.empty_like(x)
+        bl.allreduce_into(out, x, algo)
+        assert torch.equal(out.cpu(), expect_sum(n, torch.bfloat16)), (algo, nbytes)
+log("all_reduce algorithms ok: %s" % algos)
+
+# staged paths: odd size, unaligned view, non-contiguous
+t = seeded(rank, 1001, torch.float32).to(dev)
+dist.all_reduce(t)
+assert torch.equal(t.cpu(), expect_sum(1001, torch.float32))
+base = seeded(rank, 4100, torch.float16).to(dev)
+v = base[1:4098]
+dist.all_reduce(v)
+assert torch.equal(v.cpu(), expect_sum(4100, torch.float16)[1:4098])
+m = seeded(rank, 64 * 64, torch.float32).view(64, 64).to(dev)
+mt = m.t()
+dist.all_reduce(mt)
+assert torch.equal(mt.cpu(), expect_sum(64 * 64, torch.float32).view(64, 64).t())
+be = blpg.backend_of()
+assert be.n_staged >= 3 and be.n_zero_copy > 0
+log("staged fallbacks ok (zero-copy %d, staged %d)" % (be.n_zero_copy, be.n_staged))
+
+# reuse loop on the decode message size, bitwise check every 50
+n = 5120
+for it in range(300):
+    t = (seeded(rank, n, torch.float32) + it).to(torch.bfloat16).to(dev) if it % 50 == 0 else t
+    if it % 50 == 0:
+        keep = t.clone()
+    dist.all_reduce(t)
+    if it % 50 == 0:
+        want = sum((seeded(r, n, torch.float32) + it).to(torch.bfloat16).float() for r in range(world)).to(torch.bfloat16)
+        assert torch.equal(t.cpu(), want), it
+assert bl.status()["code"] == 0
+log("soak ok")
+
+# ---- gather / scatter / broadcast / barrier ----------------------------------------
+n = 2560
+mine = seeded(rank, n, torch.bfloat16).to(dev)
+out = torch.empty(world * n, dtype=torch.bfloat16, device=dev)
+dist.all_gather_into_tensor(out, mine)
+assert torch.equal(out.cpu(), torch.cat([seeded(r, n, torch.bfloat16) for r in range(world)]))
+lst = [torch.empty(333, dtype=torch.float32, device=dev) for _ in range(world)]
+dist.all_gather(lst, seeded(rank, 333, torch.float32).to(dev))
+for r in range(world):
+    assert torch.equal(lst[r].cpu(), seeded(r, 333, torch.float32))
+big = seeded(rank, world * 4096, torch.float32).to(dev)
+part = torch.empty(4096, dtype=torch.float32, device=dev)
+dist.reduce_scatter_tensor(part, big)
+assert torch.equal(part.cpu(), expect_sum(world * 4096, torch.float32)[rank * 4096:(rank + 1) * 4096])
+for root in range(world):
+    t = seeded(rank, 9999, torch.float32).to(dev)
+    dist.broadcast(t, src=root)
+    assert torch.equal(t.cpu(), seeded(root, 9999, torch.float32))
+dist.barrier()
+log("gather/scatter/broadcast/barrier ok")
+
+# groups of one member are local no-ops and leave the world group intact
+subs = [dist.new_group([r]) for r in range(world)]
+t = torch.full((8,), float(rank), device=dev)
+dist.all_reduce(t, group=subs[rank])
+assert torch.all(t == float(rank))
+t = torch.ones(64, device=dev)
+dist.all_reduce(t)
+assert torch.all(t == world)
+log("size-1 groups ok")
+
+# ---- p2p ---------------------------------------------------------------------------------
+peer = rank ^ 1
+if peer < world:
+    for nbytes in (1024, 64 << 10, 8 << 20, 1000):
+        n = nbytes // 4
+        a = seeded(rank, n, torch.float32).to(dev)
+        b = torch.empty(n, dtype=torch.float32, device=dev)
+        reqs = [dist.isend(a, peer), dist.irecv(b, peer)]
+        for r in reqs:
+            r.wait()
+        assert torch.equal(b.cpu(), seeded(peer, n, torch.float32)), nbytes
+    # three sends outstanding before the first recv
+    outs = [seeded(rank, 2048, torch.float32).add(i).to(dev) for i in range(3)]
+    ins = [torch.empty(2048, dtype=torch.float32, device=dev) for _ in range(3)]
+    for o in outs:
+        dist.send(o, peer)
+    for i in ins:
+        dist.recv(i, peer)
+    for i, t in enumerate(ins):
+        assert torch.equal(t.cpu(), seeded(peer, 2048, torch.float32).add(i))
+    # ping-pong
+    t = torch.zeros(2560, device=dev)
+    for it in range(20):
+        if rank < peer:
+            t.fill_(it)
+            dist.send(t, peer)
+            dist.recv(t, peer)
+            assert torch.all(t == it + 0.5)
+        else:
+            dist.recv(t, peer)
+            t.add_(0.5)
+            dist.send(t, peer)
+    log("p2p ok")
+
+# ---- fused all-reduce + residual + RMSNorm ------------------------------------------------
+from barlink_sm86_b200.ops import reference as ref  # noqa: E402
+for rows, hidden in ((1, 3584), (8, 3584), (64, 3584), (3, 5120)):
+    g = torch.Generator(device="cpu").manual_seed(77)
+    parts = [torch.randn(rows, hidden, generator=g).to(torch.bfloat16) for _ in range(world)]
+    res = torch.randn(rows, hidden, generator=g).to(torch.bfloat16)
+    gamma = (1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16)
+    normed, new_res = bl.allreduce_rmsnorm(parts[rank].to(dev), res.to(dev), gamma.to(dev), 1e-6)
+    want_n, want_r = ref.allreduce_rmsnorm(parts, res, gamma, 1e-6)
+    assert torch.equal(new_res.cpu(), want_r)
+    assert ((normed.cpu().float() - want_n.float()).norm() / want_n.float().norm()) < 5e-3
+log("allreduce_rmsnorm ok")
+
+# ---- CUDA graph capture and replay ----------------------------------------------------------
+x = torch.zeros(5120, dtype=torch.bfloat16, device=dev)
+y = torch.empty_like(x)
+s = torch.cuda.Stream()
+s.wait_stream(torch.cuda.current_stream())
+with torch.cuda.stream(s):
+    bl.allreduce_into(y, x)
+torch.cuda.current_stream().wait_stream(s)
+torch.cuda.synchronize()
+g = torch.cuda.CUDAGraph()
+with torch.cuda.graph(g):
+    bl.allreduce_into(y, x)
+    bl.allreduce_into(y, y, "twoshot")
+for it in range(10):
+    x.fill_(float(rank + it))
+    g.replay()
+    torch.cuda.synchronize()
+    want = float(sum(r + it for r in range(world)) * world)
+    assert torch.all(y.float() == want), (it, y[:4], want)
+log("graph replay ok")
+
+# ---- argument errors come before any traffic ------------------------------------------------
+for bad in (lambda: dist.all_reduce(torch.ones(4, device=dev), op=dist.ReduceOp.MIN),
+            lambda: dist.all_reduce(torch.ones(4, dtype=torch.int64, device=dev)),
+            lambda: dist.send(torch.ones(4, device=dev), rank)):
+    try:
+        bad()
+        raise SystemExit("expected an error")
+    except (RuntimeError, ValueError):
+        pass
+t = torch.ones(16, device=dev)
+dist.all_reduce(t)
+assert torch.all(t == world)
+log("error paths ok")
+
+# ---- a wait that runs out: status, no trap, link usable again after reset ----------------------
+host_barrier()
+torch.cuda.synchronize()
+bl.set_wait_timeout_ms(200)
+if rank == 0 and world >= 2:
+    t = torch.zeros(64, device=dev)
+    bl.recv_into(t, 1)  # rank 1 never sends this message
+    torch.cuda.synchronize()
+    st = bl.status()
+    assert st["code"] == 1 and st["from_rank"] == 1, st
+    try:
+        bl.allreduce_into(t, t)
+        raise SystemExit("expected the poisoned link to refuse")
+    except RuntimeError:
+        pass
+host_barrier()
+bl.reset()
+bl.set_wait_timeout_ms(2000)
+host_barrier()
+t = torch.ones(64, device=dev)
+dist.all_reduce(t)
+assert torch.all(t == world) and bl.status()["code"] == 0
+log("bounded wait + reset ok")
+
+# ---- latency (device-timed, max over ranks is taken by the caller's log) -------------------------
+for nbytes in (10240, 65536, 262144, 1 << 20):
+    t = torch.zeros(nbytes // 2, dtype=torch.bfloat16, device=dev)
+    for _ in range(10):
+        dist.all_reduce(t)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(50):
+        bl.allreduce_into(t, t)
+    e1.record()
+    torch.cuda.synchronize()
+    us = torch.tensor([e0.elapsed_time(e1) / 50 * 1e3])
+    dist.all_reduce(us, op=dist.ReduceOp.MAX)
+    log("all_reduce %7d B: %.1f us (direct call, max over ranks)" % (nbytes, us.item()))
+
+host_barrier()
+dist.destroy_process_group()
+bl.shutdown()
+print("[pg] rank %d done" % rank, flush=True)

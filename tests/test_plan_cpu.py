@@ -1,0 +1,93 @@
+# SPDX-License-Identifier: MIT
+"""Sharding rules, CPU oracles and package plumbing (no GPU)."""
+import pytest
+import torch
+
+from barlink_sm86_b200.parallel import head_plan, interleave_gate_up, shard_cols, shard_rows
+from barlink_sm86_b200.ops import reference as ref
+
+
+def test_head_plan_even_split():
+    p = head_plan(28, 4, 2, 1)
+    assert p.kv_heads == [2, 3] and p.q_heads == list(range(14, 28))
+    p = head_plan(28, 4, 4, 3)
+    assert p.kv_heads == [3] and p.q_heads == list(range(21, 28))
+
+
+def test_head_plan_replicates_kv_heads_when_fewer_than_ranks():
+    seen = []
+    for r in range(8):
+        p = head_plan(28, 4, 8, r)
+        assert p.nq == 4 and p.nkv == 1 and p.kv_heads == [r // 2]
+        for h in p.q_heads:
+            if h >= 0:
+                assert h // 7 == r // 2  # a query head stays with its KV head
+                seen.append(h)
+    assert sorted(seen) == list(range(28))  # every head exactly once, the rest are empty slots
+
+
+def test_head_plan_rejects_impossible_splits():
+    with pytest.raises(ValueError):
+        head_plan(28, 4, 3, 0)
+    with pytest.raises(ValueError):
+        head_plan(10, 4, 2, 0)
+
+
+def test_shards_reassemble():
+    w = torch.arange(24.).view(6, 4)
+    assert torch.equal(torch.cat([shard_rows(w, 3, r) for r in range(3)], 0), w)
+    assert torch.equal(torch.cat([shard_cols(w, 2, r) for r in range(2)], 1), w)
+    g, u = torch.zeros(3, 2), torch.ones(3, 2)
+    gu = interleave_gate_up(g, u)
+    assert torch.equal(gu[0::2], g) and torch.equal(gu[1::2], u)
+
+
+def test_reference_linear_silu_matches_separate_ops():
+    x, g, u = torch.randn(5, 16), torch.randn(8, 16), torch.randn(8, 16)
+    got = ref.linear(x, interleave_gate_up(g, u), silu_mul=True)
+    want = torch.nn.functional.silu(x @ g.t()) * (x @ u.t())
+    assert torch.allclose(got, want, atol=1e-5)
+
+
+def test_reference_paged_attention_matches_dense():
+    torch.manual_seed(0)
+    nq, nkv, hd, bs = 4, 2, 16, 16
+    ctx = torch.tensor([5, 33])
+    kc, vc = torch.randn(6, nkv, bs, hd), torch.randn(6, nkv, bs, hd)
+    bt = torch.tensor([[0, 1, 2], [3, 4, 5]], dtype=torch.int32)
+    q = torch.randn(2, nq * hd)
+    out = ref.paged_attn_decode(q, kc, vc, bt, ctx, nq, nkv, hd, 0.25)
+    for b in range(2):
+        n = int(ctx[b])
+        k = kc[bt[b].long()].permute(1, 0, 2, 3).reshape(nkv, -1, hd)[:, :n]
+        v = vc[bt[b].long()].permute(1, 0, 2, 3).reshape(nkv, -1, hd)[:, :n]
+        qq = q[b].view(nq, 1, hd)
+        dense = ref.attention(qq.permute(1, 0, 2), k.permute(1, 0, 2), v.permute(1, 0, 2),
+                              [0, 1], [0, n], 0.25, False)
+        assert torch.allclose(out[b], dense.reshape(-1), atol=1e-5)
+
+
+def test_reference_rope_is_a_rotation_and_2d_splits_axes():
+    x = torch.randn(7, 3, 32)
+    pos = torch.arange(7, dtype=torch.int32)
+    y = ref.rope(x, pos, 1e4)
+    assert torch.allclose(y.norm(dim=-1), x.norm(dim=-1), atol=1e-4)
+    assert torch.allclose(y[0], x[0], atol=1e-6)  # position 0 is the identity
+    pos2 = torch.stack([pos, torch.zeros_like(pos)], 1)
+    y2 = ref.rope(x, pos2, 1e4, axes=2)
+    assert torch.allclose(y2[..., 16:], x[..., 16:], atol=1e-6)  # second axis at position 0
+
+
+def test_w8_quantisation_round_trip():
+    w = torch.randn(32, 64) * 0.02
+    wq, s = ref.quantize_w8(w)
+    assert wq.dtype == torch.int8 and s.dtype == torch.bfloat16
+    back = wq.float() * s.float()[:, None]
+    assert (back - w).abs().max() <= s.float().max() * 0.51 + 1e-3
+
+
+def test_package_imports_without_a_gpu():
+    import barlink_sm86_b200 as bl
+    assert callable(bl.init) and callable(bl.allreduce_into) and callable(bl.copy_large)
+    import barlink_sm86 as old
+    assert old.init is bl.init
