@@ -286,18 +286,24 @@ std::tuple<at::Tensor, at::Tensor> allreduce_rmsnorm(const at::Tensor& x,
   blCtx* c = ctx_or_throw();
   check_cuda_contig(x, "x");
   check_cuda_contig(gamma, "gamma");
-  TORCH_CHECK(x.dim() >= 1 && gamma.numel() == x.size(-1) && gamma.scalar_type() == x.scalar_type(),
-              "barlink: gamma must match the last dim and dtype of x");
-  const int code = blpg::dtype_code(x.scalar_type());
+  const bool from_slabs = x.scalar_type() == at::kFloat && gamma.scalar_type() != at::kFloat;
+  TORCH_CHECK(x.dim() >= 1 && gamma.numel() == x.size(-1) &&
+                  (from_slabs ? x.dim() == 3 : gamma.scalar_type() == x.scalar_type()),
+              "barlink: gamma must match the last dim (and, unless x is fp32 split-K slabs "
+              "[splits, rows, hidden], the dtype) of x");
+  const int code = blpg::dtype_code(gamma.scalar_type());
   const int hidden = int(x.size(-1));
-  const int rows = int(x.numel() / hidden);
-  at::Tensor normed = normed_out ? *normed_out : at::empty_like(x);
-  at::Tensor res = residual_out ? *residual_out : at::empty_like(x);
+  const int nsplit = from_slabs ? int(x.size(0)) : 0;
+  const int rows = int(x.numel() / hidden / (from_slabs ? nsplit : 1));
+  auto oopt = x.options().dtype(gamma.scalar_type());
+  at::Tensor normed = normed_out ? *normed_out : at::empty({rows, hidden}, oopt);
+  at::Tensor res = residual_out ? *residual_out : at::empty({rows, hidden}, oopt);
   const void* rin = nullptr;
   if (residual) {
     check_cuda_contig(*residual, "residual");
-    TORCH_CHECK(residual->sizes() == x.sizes() && residual->scalar_type() == x.scalar_type(),
-                "barlink: residual must match x");
+    TORCH_CHECK(residual->numel() == int64_t(rows) * hidden &&
+                    residual->scalar_type() == gamma.scalar_type(),
+                "barlink: residual must be [rows, hidden] of the output dtype");
     rin = residual->data_ptr();
   }
   c10::cuda::CUDAGuard guard(x.device());
@@ -305,8 +311,8 @@ std::tuple<at::Tensor, at::Tensor> allreduce_rmsnorm(const at::Tensor& x,
   {
     py::gil_scoped_release nogil;
     BL_CHECK(bl_allreduce_rmsnorm_peer(c, x.data_ptr(), rin, gamma.data_ptr(), res.data_ptr(),
-                                       normed.data_ptr(), rows, hidden, float(eps), code, st, err,
-                                       errlen));
+                                       normed.data_ptr(), rows, hidden, float(eps), code, nsplit,
+                                       size_t(rows) * hidden, st, err, errlen));
   }
   return {normed, res};
 }

@@ -116,11 +116,13 @@ int bl_broadcast_peer(blCtx* ctx, void* ptr, size_t bytes, int root, void* strea
                       size_t errlen);
 int bl_barrier_peer(blCtx* ctx, void* stream, char* err, size_t errlen);
 /* out = all-reduce(in) + residual (written to residual_out), then RMSNorm
- * with weight gamma into normed_out.  rows x hidden elements of dtype. */
+ * with weight gamma into normed_out.  rows x hidden elements of dtype.
+ * nsplit > 0: in is instead nsplit fp32 slabs (slab elements apart) left by a
+ * split-K linear; their sum, rounded to dtype, is this rank's contribution. */
 int bl_allreduce_rmsnorm_peer(blCtx* ctx, const void* inPtr, const void* residualIn,
                               const void* gamma, void* residualOut, void* normedOut, int rows,
-                              int hidden, float eps, int dtype, void* stream, char* err,
-                              size_t errlen);
+                              int hidden, float eps, int dtype, int nsplit, size_t slab, void* stream,
+                              char* err, size_t errlen);
 /* byte move; the k-th send to a peer pairs with that peer's k-th recv */
 int bl_send_into_peer(blCtx* ctx, const void* inPtr, size_t bytes, int peerRank, void* stream,
                       char* err, size_t errlen);

@@ -46,6 +46,8 @@ struct CollArgs {
   unsigned long long* bad;
   unsigned seed;
   int iters;
+  int nsplit;    // fused norm: `in` is nsplit fp32 slabs (slab elements apart) to be summed first
+  size_t slab;
 };
 
 // ---------------------------------------------------------------------------
@@ -373,6 +375,27 @@ __global__ void __launch_bounds__(kThreads) k_lamport(CollArgs a) {
     __shared__ float s_part[kThreads / 32];
     __shared__ float s_rstd;
     const int vpr = a.vec_per_row;
+    // the row-parallel linear before this kernel may have left k-split slabs:
+    // their sum, rounded to the storage type, is this rank's contribution
+    const float* slabs = a.nsplit > 0 ? static_cast<const float*>(a.in[y]) : nullptr;
+    auto load_in = [&](size_t g) -> uint4 {
+      if (!slabs) return scrub(in[g]);
+      float acc[E::N];
+#pragma unroll
+      for (int j = 0; j < E::N; ++j) acc[j] = 0.f;
+      for (int sp = 0; sp < a.nsplit; ++sp) {
+        const float4* p = reinterpret_cast<const float4*>(slabs + size_t(sp) * a.slab + g * E::N);
+#pragma unroll
+        for (int j = 0; j < E::N / 4; ++j) {
+          const float4 f = __ldcg(p + j);
+          acc[4 * j] += f.x;
+          acc[4 * j + 1] += f.y;
+          acc[4 * j + 2] += f.z;
+          acc[4 * j + 3] += f.w;
+        }
+      }
+      return scrub(E::pack(acc));
+    };
     const uint4* res_in = static_cast<const uint4*>(a.aux_in[y]);
     uint4* res_out = static_cast<uint4*>(a.aux_out[y]);
     const uint4* gamma = static_cast<const uint4*>(a.gamma[y]);
@@ -380,7 +403,8 @@ __global__ void __launch_bounds__(kThreads) k_lamport(CollArgs a) {
     for (int row = blockIdx.x; row < a.rows; row += gridDim.x)
       for (int i = threadIdx.x; i < vpr; i += blockDim.x) {
         const size_t g = size_t(row) * vpr + i;
-        uint4 v = scrub(in[g]);
+        uint4 v = load_in(g);
+        if (slabs) st_v4(c.base[rank] + cur_off + size_t(rank) * c.lamport_slice + g * 16, v);
 #pragma unroll 1
         for (int k = 1; k < world; ++k) {
           int p = rank + k;
@@ -407,7 +431,9 @@ __global__ void __launch_bounds__(kThreads) k_lamport(CollArgs a) {
           for (int r = 0; r < world; ++r) {
             uint4 v;
             if (r == rank) {
-              v = scrub(in[g]);
+              // with slabs, my own contribution was parked in my inbox slot by this same thread
+              v = slabs ? ld_volatile_v4(c.base[rank] + cur_off + size_t(rank) * c.lamport_slice + g * 16)
+                        : scrub(in[g]);
             } else if (!poll_vec(c, c.base[rank] + cur_off + size_t(r) * c.lamport_slice + g * 16,
                                  v, r)) {
               ok = false;
@@ -1309,7 +1335,7 @@ extern "C" int bl_barrier_peer(blCtx* ctx, void* stream, char* err, size_t errle
 }
 
 static int norm_local(blCtx* ctx, const PerRank* pr, int rows, int hidden, float eps, int dtype,
-                      char* err, size_t errlen) {
+                      int nsplit, size_t slab, char* err, size_t errlen) {
   if (check_health(ctx, err, errlen) != 0) return -1;
   const int esz = dtype == BL_DTYPE_FP32 ? 4 : 2;
   if (dtype != BL_DTYPE_BF16 && dtype != BL_DTYPE_FP16 && dtype != BL_DTYPE_FP32) {
@@ -1340,6 +1366,12 @@ static int norm_local(blCtx* ctx, const PerRank* pr, int rows, int hidden, float
   a.rows = rows;
   a.vec_per_row = int(row_bytes / 16);
   a.eps = eps;
+  a.nsplit = nsplit;
+  a.slab = slab;
+  if (nsplit > 0 && dtype == BL_DTYPE_FP32) {
+    set_err(err, errlen, "barlink: slab input to allreduce_rmsnorm needs a 16-bit output type");
+    return -1;
+  }
   int grid = rows < 64 ? rows : 64;
   if (!ctx->peer_mode && grid > 8) grid = 8;
   int rc = -1;
@@ -1366,8 +1398,8 @@ static int norm_local(blCtx* ctx, const PerRank* pr, int rows, int hidden, float
 
 extern "C" int bl_allreduce_rmsnorm_peer(blCtx* ctx, const void* inPtr, const void* residualIn,
                                          const void* gamma, void* residualOut, void* normedOut,
-                                         int rows, int hidden, float eps, int dtype, void* stream,
-                                         char* err, size_t errlen) {
+                                         int rows, int hidden, float eps, int dtype, int nsplit,
+                                         size_t slab, void* stream, char* err, size_t errlen) {
   if (!ctx || !ctx->peer_mode) {
     set_err(err, errlen, "barlink: allreduce_rmsnorm needs an SPMD context (init_peer)");
     return -1;
@@ -1379,7 +1411,7 @@ extern "C" int bl_allreduce_rmsnorm_peer(blCtx* ctx, const void* inPtr, const vo
   pr.aux_out = residualOut;
   pr.gamma = gamma;
   pr.stream = stream;
-  return norm_local(ctx, &pr, rows, hidden, eps, dtype, err, errlen);
+  return norm_local(ctx, &pr, rows, hidden, eps, dtype, nsplit, slab, err, errlen);
 }
 
 // Single-process form of the SPMD collectives: one pointer per arena.  With
@@ -1410,7 +1442,7 @@ extern "C" int bl_sp_collective(blCtx* ctx, int kind, const void* const* in, voi
     case 1: return staged_local(ctx, 1, pr, bytes, 0, dtype, 0, err, errlen);
     case 2: return staged_local(ctx, 2, pr, bytes, 0, BL_DTYPE_U8, 0, err, errlen);
     case 3: return staged_local(ctx, 3, pr, bytes, 0, BL_DTYPE_U8, root, err, errlen);
-    case 4: return norm_local(ctx, pr, rows, hidden, eps, dtype, err, errlen);
+    case 4: return norm_local(ctx, pr, rows, hidden, eps, dtype, 0, 0, err, errlen);
     case 5: {
       if (check_health(ctx, err, errlen) != 0) return -1;
       CollArgs a;

@@ -168,7 +168,7 @@ class Qwen2Model:
         cfg, c, w = self.cfg, self.comm, self.w
         h = ops.embedding(ids, w.embed)
         res = torch.zeros_like(h)
-        split_k = split_k and h.is_cuda and c.world == 1
+        split_k = split_k and h.is_cuda
         pending = False  # h holds a partial sum that still needs the all-reduce
         for li, L in enumerate(w.layers):
             if pending:

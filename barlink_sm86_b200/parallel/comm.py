@@ -105,7 +105,11 @@ class TPComm:
         otherwise all-reduce followed by the add+norm kernel."""
         if self.world == 1:
             return _ops.rmsnorm(x, gamma, eps, residual)
-        nbytes = x.numel() * x.element_size()
+        slabs = x.dtype == torch.float32 and x.dim() == 3 and gamma.dtype != torch.float32
+        nbytes = (x[0].numel() * gamma.element_size()) if slabs else x.numel() * x.element_size()
+        if slabs and not (self.use_link and x.is_cuda and nbytes <= self.oneshot_max):
+            x = x.sum(0).to(gamma.dtype)  # no fused path for this size: fold the k-split slabs here
+            slabs = False
         if self.use_link and x.is_cuda and nbytes <= self.oneshot_max and x.is_contiguous():
             self.ar_calls += 1
             self.ar_bytes += nbytes

@@ -189,6 +189,17 @@ for rows, hidden in ((1, 3584), (8, 3584), (64, 3584), (3, 5120)):
     want_n, want_r = ref.allreduce_rmsnorm(parts, res, gamma, 1e-6)
     assert torch.equal(new_res.cpu(), want_r)
     assert ((normed.cpu().float() - want_n.float()).norm() / want_n.float().norm()) < 5e-3
+# the same with this rank's contribution given as k-split fp32 slabs of a linear
+for rows, hidden, S in ((8, 3584, 4), (64, 3584, 5)):
+    g = torch.Generator(device="cpu").manual_seed(78)
+    slabs = [torch.randn(S, rows, hidden, generator=g) for _ in range(world)]
+    parts = [s_.sum(0).to(torch.bfloat16) for s_ in slabs]
+    res = torch.randn(rows, hidden, generator=g).to(torch.bfloat16)
+    gamma = (1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16)
+    normed, new_res = bl.allreduce_rmsnorm(slabs[rank].to(dev), res.to(dev), gamma.to(dev), 1e-6)
+    want_n, want_r = ref.allreduce_rmsnorm(parts, res, gamma, 1e-6)
+    assert (new_res.cpu().float() - want_r.float()).abs().max() <= 0.07, "slab sum differs"
+    assert ((normed.cpu().float() - want_n.float()).norm() / want_n.float().norm()) < 8e-3
 log("allreduce_rmsnorm ok")
 
 # ---- CUDA graph capture and replay ----------------------------------------------------------
