@@ -450,7 +450,7 @@ int gemm_error_flag(int dev) {
 at::Tensor linear(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
                   const c10::optional<at::Tensor>& residual, bool silu_mul,
                   c10::optional<at::Tensor> out_opt, int force_swap, int bn, int splits,
-                  bool dynamic_weights, c10::optional<at::Tensor> trace) {
+                  bool dynamic_weights, c10::optional<at::Tensor> trace, int gate_tokens) {
   check_bf16(w, "weight");
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
               "barlink: x must be a 2-D bfloat16 CUDA tensor with unit inner stride");
@@ -498,6 +498,7 @@ at::Tensor linear(const at::Tensor& x, const at::Tensor& w, const c10::optional<
   a.n_counters = int(s.counters.numel());
   a.err_flag = s.err_flag.data_ptr();
   a.dynamic_weights = dynamic_weights ? 1 : 0;
+  if (gate_tokens > 0) BL_CHECK(bl_tp_gate(ctx_or_throw(), gate_tokens, &a, err, errlen));
   if (trace) {
     TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == at::kLong && trace->numel() >= 8 * 296,
                 "barlink: trace must be an int64 CUDA tensor of at least 2368 entries");
@@ -516,7 +517,7 @@ int gemm_splits(int n, int k, int tokens) { return bl_gemm_splits(n, k, tokens);
 // Split-K linear without a reduction: returns fp32 slabs [splits, tokens, n] that
 // the next kernel (rmsnorm / rope_kv_write / the fused all-reduce) sums as it reads.
 at::Tensor linear_partial(const at::Tensor& x, const at::Tensor& w, int splits,
-                          c10::optional<at::Tensor> out_opt) {
+                          c10::optional<at::Tensor> out_opt, int gate_tokens) {
   check_bf16(w, "weight");
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
               "barlink: x must be a 2-D bfloat16 CUDA tensor with unit inner stride");
@@ -544,12 +545,89 @@ at::Tensor linear_partial(const at::Tensor& x, const at::Tensor& w, int splits,
   a.partial_splits = splits;
   a.splits = splits;
   a.err_flag = s.err_flag.data_ptr();
+  if (gate_tokens > 0) BL_CHECK(bl_tp_gate(ctx_or_throw(), gate_tokens, &a, err, errlen));
   void* st = at::cuda::getCurrentCUDAStream(dev).stream();
   {
     py::gil_scoped_release nogil;
     BL_CHECK(bl_gemm_bf16(&a, st, err, errlen));
   }
   return out;
+}
+
+// Row-parallel linear fused with the reduce-scatter: partial rows of x @ w.T go
+// straight into the inbox of each token's owner (inbox: fp32 arena tensor of
+// world*splits*tokens/world*n elements at the same offset on every rank).
+// Returns (units, splits) for tp_rs_finish.
+std::tuple<int, int> tp_gemm_rs(const at::Tensor& x, const at::Tensor& w, const at::Tensor& inbox) {
+  blCtx* c = ctx_or_throw();
+  check_bf16(w, "weight");
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
+              "barlink: x must be a 2-D bfloat16 CUDA tensor with unit inner stride");
+  TORCH_CHECK(w.dim() == 2 && w.size(1) == x.size(1), "barlink: weight must be [n, k_local]");
+  const int tokens = int(x.size(0)), k = int(x.size(1)), n = int(w.size(0));
+  TORCH_CHECK(tokens <= 256, "barlink: the fused reduce-scatter linear is the decode path (<= 256 tokens)");
+  int splits = 1;
+  const int units = bl_tp_units(n, k, tokens, &splits);
+  const int64_t off = bl_pool_offset(c, 0, inbox.data_ptr());
+  TORCH_CHECK(off >= 0 && inbox.scalar_type() == at::kFloat &&
+                  inbox.numel() >= int64_t(bl_world(c)) * splits * (tokens / bl_world(c)) * n,
+              "barlink: inbox must be a float32 arena tensor (empty()) of at least world*splits*tokens/world*n elements");
+  const int dev = x.device().index();
+  c10::cuda::CUDAGuard guard(x.device());
+  Scratch& s = scratch_for(dev);
+  blPeerSink ps;
+  BL_CHECK(bl_tp_peer_sink(c, size_t(off), tokens, &ps, err, errlen));
+  blGemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.a = w.data_ptr(); a.ra = n; a.lda = k;
+  a.b = x.data_ptr(); a.rb = tokens; a.ldb = int(x.stride(0));
+  a.k = k;
+  a.ldo = n;
+  a.swap = 1;
+  a.peer = &ps;
+  a.partial_splits = splits;
+  a.splits = splits;
+  a.err_flag = s.err_flag.data_ptr();
+  void* st = at::cuda::getCurrentCUDAStream(dev).stream();
+  {
+    py::gil_scoped_release nogil;
+    BL_CHECK(bl_gemm_bf16(&a, st, err, errlen));
+  }
+  return {units, splits};
+}
+
+// Reduce my tokens from the inbox, add the residual (updated in place), norm,
+// and all-gather the normed rows into `gather` (bf16 arena tensor [tokens, n]).
+void tp_rs_finish(const at::Tensor& inbox, const at::Tensor& gather, const at::Tensor& residual,
+                  const at::Tensor& gamma, double eps, int tokens, int splits, int units,
+                  bool add_residual) {
+  blCtx* c = ctx_or_throw();
+  check_bf16(gamma, "gamma");
+  check_bf16(residual, "residual");
+  check_bf16(gather, "gather");
+  const int n = int(gamma.numel());
+  const int64_t ioff = bl_pool_offset(c, 0, inbox.data_ptr());
+  const int64_t goff = bl_pool_offset(c, 0, gather.data_ptr());
+  TORCH_CHECK(ioff >= 0 && goff >= 0, "barlink: inbox and gather must be arena tensors (empty())");
+  TORCH_CHECK(gather.numel() >= int64_t(tokens) * n, "barlink: gather must hold tokens x n elements");
+  TORCH_CHECK(residual.numel() == int64_t(tokens / bl_world(c)) * n,
+              "barlink: residual holds this rank's tokens: [tokens/world, n]");
+  blRsFinishArgs a;
+  memset(&a, 0, sizeof(a));
+  a.inbox_off = size_t(ioff);
+  a.tokens = tokens;
+  a.n = n;
+  a.splits = splits;
+  a.units = units;
+  a.residual_in = add_residual ? residual.data_ptr() : nullptr;
+  a.residual_out = residual.data_ptr();
+  a.gamma = gamma.data_ptr();
+  a.eps = float(eps);
+  a.gather_off = size_t(goff);
+  c10::cuda::CUDAGuard guard(gather.device());
+  void* st = at::cuda::getCurrentCUDAStream(gather.device().index()).stream();
+  py::gil_scoped_release nogil;
+  BL_CHECK(bl_rs_finish(c, &a, st, err, errlen));
 }
 
 std::tuple<at::Tensor, at::Tensor> rmsnorm(const at::Tensor& x, const at::Tensor& gamma, double eps,
@@ -812,7 +890,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("linear", &linear, py::arg("x"), py::arg("weight"), py::arg("bias") = py::none(),
         py::arg("residual") = py::none(), py::arg("silu_mul") = false, py::arg("out") = py::none(),
         py::arg("force_swap") = -1, py::arg("bn") = 0, py::arg("splits") = 0,
-        py::arg("dynamic_weights") = false, py::arg("trace") = py::none());
+        py::arg("dynamic_weights") = false, py::arg("trace") = py::none(), py::arg("gate_tokens") = 0);
   m.def("gemm_error_flag", &gemm_error_flag, py::arg("device") = 0);
   m.def("rmsnorm", &rmsnorm, py::arg("x"), py::arg("gamma"), py::arg("eps"),
         py::arg("residual") = py::none(), py::arg("out") = py::none());
@@ -822,7 +900,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("block_size") = 16, py::arg("theta") = 1e6, py::arg("bias") = py::none(),
         py::arg("out") = py::none());
   m.def("linear_partial", &linear_partial, py::arg("x"), py::arg("weight"), py::arg("splits") = 0,
-        py::arg("out") = py::none());
+        py::arg("out") = py::none(), py::arg("gate_tokens") = 0);
+  m.def("tp_gemm_rs", &tp_gemm_rs, py::arg("x"), py::arg("weight"), py::arg("inbox"));
+  m.def("tp_rs_finish", &tp_rs_finish, py::arg("inbox"), py::arg("gather"), py::arg("residual"),
+        py::arg("gamma"), py::arg("eps"), py::arg("tokens"), py::arg("splits"), py::arg("units"),
+        py::arg("add_residual") = true);
   m.def("gemm_splits", &gemm_splits, py::arg("n"), py::arg("k"), py::arg("tokens"));
   m.def("rope", &rope, py::arg("x"), py::arg("positions"), py::arg("heads"), py::arg("hd"),
         py::arg("theta") = 1e4, py::arg("axes") = 1);

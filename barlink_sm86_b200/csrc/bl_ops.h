@@ -21,6 +21,15 @@
 extern "C" {
 #endif
 
+/* Where the row-parallel linear fused with the reduce-scatter sends its output:
+ * the inbox of each token's owner (fp32 [src rank][split][tokens_per_rank][n])
+ * and that owner's arrival word for this rank, both as mapped in this process. */
+typedef struct blPeerSink {
+  void* inbox[BL_MAX_RANKS];
+  void* flag[BL_MAX_RANKS];
+  int world, rank, tokens_per_rank;
+} blPeerSink;
+
 /* D[i, j] = sum_k A[i, k] * B[j, k]; A [ra x k] pitch lda, B [rb x k] pitch
  * ldb, bf16, K-major.  swap = 0: out[i, j]; swap = 1: out[j, i] (A = weight
  * rows, B = tokens: the decode orientation).  out is bf16 with pitch ldo.
@@ -57,6 +66,16 @@ typedef struct blGemmArgs {
   void* partial_out;
   size_t partial_stride;
   int partial_splits;
+  /* fused reduce-scatter (swap orientation only): partial rows go to peers */
+  const blPeerSink* peer;
+  /* fused all-gather in front: wait for gate_n words at gate_flags to reach
+   * *gate_cum + gate_add before the first activation tile is requested */
+  const void* gate_flags;
+  void* gate_cum;
+  void* gate_ticket;
+  unsigned gate_add;
+  int gate_n;
+  unsigned long long gate_timeout_ns;
   void* trace; /* debug: u64[8 * grid] global-timer stamps per CTA, or null */
 } blGemmArgs;
 int bl_gemm_bf16(const blGemmArgs* a, void* stream, char* err, size_t errlen);
@@ -149,51 +168,39 @@ int bl_decode_advance(int* positions, int* ctx_lens, int* slots, const int* bloc
                       const int* sampled, int batch, int max_blocks, int block_size, void* stream,
                       char* err, size_t errlen);
 
-/* ---- fused GEMM + collective (tensor-parallel linears) ------------------- */
-/* Row-parallel linear fused with reduce-scatter over tokens: every rank
- * multiplies its K-shard, the epilogue pushes each finished tile straight
- * into the inbox of the rank that owns those tokens; the owner then sums the
- * world partials (+ residual), optionally RMS-normalises, and (gather = 1)
- * pushes its finished rows to every rank's all-gather buffer.  All buffers
- * named *_off are offsets into the symmetric arena. */
-typedef struct blGemmRsArgs {
-  const void* x;      /* [tokens x k_local] bf16 */
-  int tokens, ldx;
-  const void* w;      /* [n x k_local] bf16 */
-  int n, k_local;
-  size_t inbox_off;   /* arena: [world][tokens_per_rank x n] bf16 partials */
-  void* err_flag;
-  void* ws; size_t ws_bytes; void* counters; int n_counters;
-} blGemmRsArgs;
-int bl_gemm_rs(blCtx* ctx, const blGemmRsArgs* a, void* stream, char* err, size_t errlen);
-/* second half: reduce my token slice from the inbox, add residual, norm,
- * write residual_out (local) and push normed rows into gather_off of every
- * rank (or only locally when gather = 0). */
+/* ---- fused GEMM + collective (tensor-parallel linears) -------------------
+ * Decode with T tokens on `world` ranks, T % world == 0: token m belongs to
+ * rank m / (T / world).
+ *
+ *  1. row-parallel linear + reduce-scatter: bl_gemm_bf16 in swap orientation
+ *     with `peer` filled by bl_tp_peer_sink -- every k-split of every tile
+ *     stores its fp32 partial rows into the owners' inboxes over NVLink and
+ *     bumps their arrival counters;
+ *  2. bl_rs_finish on every rank: wait for `units` arrivals from each rank,
+ *     sum world x splits partial rows of my tokens (rank order, split order),
+ *     add the residual of my tokens, RMS-normalise, and store the normed rows
+ *     into every rank's all-gather buffer (+ arrival counter);
+ *  3. all-gather + column-parallel linear: bl_gemm_bf16 whose activation
+ *     operand is the all-gather buffer and whose gate_* fields come from
+ *     bl_tp_gate: the weight tiles stream while it waits for the rows.
+ * Offsets are into the symmetric arena (bl_pool_offset). */
+int bl_tp_peer_sink(blCtx* ctx, size_t inbox_off, int tokens, blPeerSink* out, char* err,
+                    size_t errlen);
+int bl_tp_gate(blCtx* ctx, int tokens, blGemmArgs* a, char* err, size_t errlen);
 typedef struct blRsFinishArgs {
-  size_t inbox_off;
-  int tokens, n;           /* full token count (padded to world), hidden */
-  const void* residual_in; /* [tokens_per_rank x n] local rows or null */
-  void* residual_out;      /* [tokens_per_rank x n] */
-  const void* gamma;       /* null: no norm, gather the sum itself */
+  size_t inbox_off;        /* fp32 [world][splits][tokens/world][n] in my arena */
+  int tokens, n, splits;
+  int units;               /* arrivals expected from each rank: tiles x splits of step 1 */
+  const void* residual_in; /* bf16 [tokens/world][n], my tokens, or null */
+  void* residual_out;      /* bf16 [tokens/world][n] (may alias residual_in) */
+  const void* gamma;       /* bf16 [n] */
   float eps;
-  size_t gather_off;       /* arena: [tokens x n] bf16, filled on every rank */
-  int gather;
+  size_t gather_off;       /* bf16 [tokens][n] in every rank's arena */
 } blRsFinishArgs;
 int bl_rs_finish(blCtx* ctx, const blRsFinishArgs* a, void* stream, char* err, size_t errlen);
-/* Column-parallel linear fused with the all-gather: waits (per source rank)
- * for the rows that bl_rs_finish pushed, then runs the GEMM on them. */
-typedef struct blAgGemmArgs {
-  size_t gather_off;  /* arena: [tokens x k] bf16 */
-  int tokens, k;
-  const void* w;      /* [n_local x k] */
-  int n_local;
-  const void* bias;
-  void* out; int ldo;
-  int silu_mul;
-  void* err_flag;
-  void* ws; size_t ws_bytes; void* counters; int n_counters;
-} blAgGemmArgs;
-int bl_ag_gemm(blCtx* ctx, const blAgGemmArgs* a, void* stream, char* err, size_t errlen);
+/* tiles x splits that bl_gemm_bf16 will use for a peer-sink linear (the
+ * `units` of bl_rs_finish and the slab count the inbox must hold) */
+int bl_tp_units(int n, int k_local, int tokens, int* splits_out);
 
 #ifdef __cplusplus
 }

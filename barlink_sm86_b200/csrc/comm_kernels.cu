@@ -19,7 +19,9 @@
 
 #include <type_traits>
 
+#include "bl_ops.h"
 #include "heap.h"
+#include "launch.h"
 #include "ptx.cuh"
 
 namespace bl {
@@ -383,16 +385,11 @@ __global__ void __launch_bounds__(kThreads) k_lamport(CollArgs a) {
       float acc[E::N];
 #pragma unroll
       for (int j = 0; j < E::N; ++j) acc[j] = 0.f;
-      for (int sp = 0; sp < a.nsplit; ++sp) {
-        const float4* p = reinterpret_cast<const float4*>(slabs + size_t(sp) * a.slab + g * E::N);
+      if constexpr (E::N == 8) {
+        float a8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        sum_slabs8(slabs + g * 8, a.slab, a.nsplit, a8);
 #pragma unroll
-        for (int j = 0; j < E::N / 4; ++j) {
-          const float4 f = __ldcg(p + j);
-          acc[4 * j] += f.x;
-          acc[4 * j + 1] += f.y;
-          acc[4 * j + 2] += f.z;
-          acc[4 * j + 3] += f.w;
-        }
+        for (int j = 0; j < 8; ++j) acc[j] = a8[j];
       }
       return scrub(E::pack(acc));
     };
@@ -832,6 +829,121 @@ __global__ void k_copy_vec(const uint4* src, uint4* dst, size_t nvec) {
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
        i += size_t(gridDim.x) * blockDim.x)
     dst[i] = ld_volatile_v4(src + i);
+}
+
+// ---------------------------------------------------------------------------
+// second half of the fused row-parallel linear: reduce my tokens' partial rows
+// that every rank's GEMM epilogue stored into my inbox, add the residual,
+// RMS-normalise and all-gather the result by storing it into every rank's
+// gather buffer.  One block per local token.
+// ---------------------------------------------------------------------------
+struct RsFinishArgs {
+  Comm c;
+  size_t inbox_off, gather_off;
+  int tpr, n, splits, units;
+  const uint4* residual_in;
+  uint4* residual_out;
+  const uint4* gamma;
+  float eps;
+};
+
+__global__ void __launch_bounds__(kThreads) k_rs_finish(RsFinishArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const Comm& c = a.c;
+  const int rank = c.rank, world = c.world;
+  __shared__ int s_ok;
+  __shared__ float s_part[kThreads / 32];
+  __shared__ float s_rstd;
+  uint32_t* s = sig_of(c, rank);
+  const uint32_t cum = ld_volatile_u32(&s[sig_aux(P_GEMM_RS)]);
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < world)
+    if (!wait_flag(c, s + sig_flag(P_GEMM_RS, 0, threadIdx.x), cum + uint32_t(a.units), P_GEMM_RS,
+                   threadIdx.x))
+      s_ok = 0;
+  __syncthreads();
+  const int lm = blockIdx.x;
+  const int vpr = a.n / 8;
+  constexpr int kMaxVpt = 4;
+  float x[kMaxVpt][8];
+  float ss = 0.f;
+  const float* inbox = reinterpret_cast<const float*>(c.base[rank] + a.inbox_off);
+  if (s_ok) {
+#pragma unroll
+    for (int k = 0; k < kMaxVpt; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < vpr) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        // world x splits partial rows, summed in (rank, split) order
+        sum_slabs8(inbox + size_t(lm) * a.n + i * 8, size_t(a.tpr) * a.n, world * a.splits, acc);
+        using E = Elem<BL_DTYPE_BF16>;
+        uint4 packed = E::pack(acc);  // the linear's output, rounded as an unfused linear would
+        if (a.residual_in) {
+          E::unpack(packed, acc);
+          acc_add<BL_DTYPE_BF16>(acc, a.residual_in[size_t(lm) * vpr + i]);
+          packed = E::pack(acc);
+        }
+        a.residual_out[size_t(lm) * vpr + i] = packed;
+        E::unpack(packed, x[k]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += x[k][j] * x[k][j];
+      }
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? s_part[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) s_rstd = rsqrtf(t / float(a.n) + a.eps);
+  }
+  __syncthreads();
+  const float rstd = s_rstd;
+  const int token = rank * a.tpr + lm;
+  if (s_ok) {
+#pragma unroll
+    for (int k = 0; k < kMaxVpt; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < vpr) {
+        using E = Elem<BL_DTYPE_BF16>;
+        float gmm[8], o[8];
+        E::unpack(a.gamma[i], gmm);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = x[k][j] * rstd;
+        uint4 t = E::pack(o);
+        E::unpack(t, o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] *= gmm[j];
+        const uint4 res = E::pack(o);
+        const size_t off = a.gather_off + (size_t(token) * vpr + i) * 16;
+        for (int kk = 0; kk < world; ++kk) {
+          int p = rank + kk;
+          if (p >= world) p -= world;
+          st_v4(c.base[p] + off, res);
+        }
+      }
+    }
+  }
+  // my row is in every rank's gather buffer: tell them
+  __syncthreads();
+  if (threadIdx.x < world && s_ok) {
+    __threadfence_system();
+    red_release_sys_add(sig_of(c, threadIdx.x) + sig_flag(P_AG_GEMM, 0, rank), 1u);
+  }
+  // the last block moves the arrival expectation forward
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t t = atomicAdd(&s[sig_ticket(P_GEMM_RS)], 1u);
+    if (t == gridDim.x - 1) {
+      s[sig_ticket(P_GEMM_RS)] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(&s[sig_aux(P_GEMM_RS)]) = cum + uint32_t(a.units);
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -1755,5 +1867,112 @@ extern "C" int bl_probe_signal(blCtx* ctx, unsigned long long* res, int iters, v
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
   cudaFreeHost(h);
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// fused tensor-parallel linears: host side
+// ---------------------------------------------------------------------------
+extern "C" int bl_tp_units(int n, int k_local, int tokens, int* splits_out) {
+  const int tiles = (n + 127) / 128;
+  const int kblocks = (k_local + 63) / 64;
+  (void)tokens;
+  const int splits = pick_splits(tiles, kblocks, sm_count(), 0);
+  if (splits_out) *splits_out = splits;
+  return tiles * splits;
+}
+
+extern "C" int bl_tp_peer_sink(blCtx* ctx, size_t inbox_off, int tokens, blPeerSink* out, char* err,
+                               size_t errlen) {
+  if (!ctx || !ctx->peer_mode || !out) {
+    set_err(err, errlen, "barlink: fused TP linears need an SPMD context (init_peer)");
+    return -1;
+  }
+  if (tokens < ctx->world || tokens % ctx->world) {
+    set_err(err, errlen, "barlink: fused reduce-scatter needs a token count that is a multiple of the %d ranks (got %d)",
+            ctx->world, tokens);
+    return -1;
+  }
+  if (inbox_off >= ctx->user_bytes || (inbox_off & 15u)) {
+    set_err(err, errlen, "barlink: inbox offset %zu is not inside the arena's user zone", inbox_off);
+    return -1;
+  }
+  if (check_health(ctx, err, errlen) != 0) return -1;
+  memset(out, 0, sizeof(*out));
+  out->world = ctx->world;
+  out->rank = ctx->rank;
+  out->tokens_per_rank = tokens / ctx->world;
+  for (int r = 0; r < ctx->world; ++r) {
+    char* base = reinterpret_cast<char*>(ctx->arena[r].va);
+    out->inbox[r] = base + inbox_off;
+    out->flag[r] = reinterpret_cast<uint32_t*>(base + ctx->layout.sig_off) + sig_flag(P_GEMM_RS, 0, ctx->rank);
+  }
+  return 0;
+}
+
+extern "C" int bl_tp_gate(blCtx* ctx, int tokens, blGemmArgs* a, char* err, size_t errlen) {
+  if (!ctx || !ctx->peer_mode || !a) {
+    set_err(err, errlen, "barlink: fused TP linears need an SPMD context (init_peer)");
+    return -1;
+  }
+  if (tokens < ctx->world || tokens % ctx->world) {
+    set_err(err, errlen, "barlink: fused all-gather needs a token count that is a multiple of the %d ranks (got %d)",
+            ctx->world, tokens);
+    return -1;
+  }
+  uint32_t* s = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(ctx->arena[ctx->rank].va) +
+                                            ctx->layout.sig_off);
+  a->gate_flags = s + sig_flag(P_AG_GEMM, 0, 0);
+  a->gate_cum = s + sig_aux(P_AG_GEMM);
+  a->gate_ticket = s + sig_ticket(P_AG_GEMM);
+  a->gate_add = unsigned(tokens / ctx->world);
+  a->gate_n = ctx->world;
+  a->gate_timeout_ns = uint64_t(ctx->timeout_ms) * 1000000ull;
+  return 0;
+}
+
+extern "C" int bl_rs_finish(blCtx* ctx, const blRsFinishArgs* a, void* stream, char* err,
+                            size_t errlen) {
+  if (!ctx || !ctx->peer_mode || !a) {
+    set_err(err, errlen, "barlink: rs_finish needs an SPMD context (init_peer)");
+    return -1;
+  }
+  if (check_health(ctx, err, errlen) != 0) return -1;
+  if (a->tokens % ctx->world || a->n % 8 || a->n / 8 > kThreads * 4 || a->splits < 1 || !a->gamma ||
+      !a->residual_out) {
+    set_err(err, errlen, "barlink: rs_finish needs tokens %% world == 0, n %% 8 == 0, n <= %d, gamma and residual_out",
+            kThreads * 32);
+    return -1;
+  }
+  const int tpr = a->tokens / ctx->world;
+  const size_t inbox_bytes = size_t(ctx->world) * a->splits * tpr * a->n * 4;
+  const size_t gather_bytes = size_t(a->tokens) * a->n * 2;
+  if (a->inbox_off + inbox_bytes > ctx->user_bytes || a->gather_off + gather_bytes > ctx->user_bytes) {
+    set_err(err, errlen, "barlink: rs_finish buffers do not fit the arena's user zone");
+    return -1;
+  }
+  RsFinishArgs k;
+  k.c = ctx->comm_for(ctx->rank);
+  k.inbox_off = a->inbox_off;
+  k.gather_off = a->gather_off;
+  k.tpr = tpr;
+  k.n = a->n;
+  k.splits = a->splits;
+  k.units = a->units;
+  k.residual_in = static_cast<const uint4*>(a->residual_in);
+  k.residual_out = static_cast<uint4*>(a->residual_out);
+  k.gamma = static_cast<const uint4*>(a->gamma);
+  k.eps = a->eps;
+  int threads = (a->n / 8 + 31) / 32 * 32;
+  if (threads > kThreads) threads = kThreads;
+  if (threads < 64) threads = 64;
+  cudaError_t e = launch_k(k_rs_finish, dim3(tpr), dim3(threads), 0, static_cast<cudaStream_t>(stream), k);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_err(err, errlen, "barlink: rs_finish launch failed: %s", cudaGetErrorString(e));
+    return -1;
+  }
+  ctx->stats[BL_STAT_OPS]++;
+  ctx->stats[BL_STAT_FUSED_NORM]++;
   return 0;
 }

@@ -47,6 +47,17 @@ struct GemmShape {
   uint32_t* counters;       // [tiles] arrival counters, zero between launches
   uint32_t* err;            // set to 1 when a wait inside the kernel ran out
   unsigned long long* trace; // debug: 8 global-timer stamps per CTA, or nullptr
+  // All-gather fused in front of the GEMM: the activation operand lives in this
+  // rank's arena and peers store their rows into it.  Before the first
+  // activation tile is requested, each of gate_n flag words must have reached
+  // *gate_cum + gate_add (peers add 1 per finished row block with a release at
+  // system scope); the last CTA to finish moves *gate_cum forward.
+  const uint32_t* gate_flags;
+  uint32_t* gate_cum;
+  uint32_t* gate_ticket;
+  uint32_t gate_add;
+  int gate_n;
+  unsigned long long gate_timeout_ns;
 };
 
 template <int BN, int CPS = 1>
@@ -146,16 +157,42 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
       }
       pdl_wait();
       if (tr) tr[2] = globaltimer_ns();
+      if (g.gate_flags) {
+        const uint32_t want = *reinterpret_cast<volatile uint32_t*>(g.gate_cum) + g.gate_add;
+        const uint64_t t0 = globaltimer_ns();
+        for (int f = 0; f < g.gate_n; ++f) {
+          uint32_t polls = 0;
+          while (int32_t(ld_acquire_sys(g.gate_flags + f) - want) < 0) {
+            if ((++polls & 63u) == 0u && globaltimer_ns() - t0 > g.gate_timeout_ns) {
+              *s_abort = 1;  // peers never delivered their rows: give up, nothing was requested yet
+              break;
+            }
+          }
+          if (*s_abort) break;
+        }
+        // the rows were written by other GPUs and are read next by the TMA unit
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
       int stage = 0;
       uint32_t phase = 0;
       int armed = 0;
-      bool ok = true;
+      bool ok = !*s_abort;
+      if (!ok && pre > 0) {
+        // weight tiles of the first lap are in flight with half of their bytes
+        // expected: complete the stages with the activation tiles anyway so
+        // that the copies land before the CTA leaves
+        ok = true;
+      }
       for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
         const int tile = u / g.splits, sp = u - tile * g.splits;
         const int ta = tile / g.tiles_b, tb = tile - ta * g.tiles_b;
         const int kb0 = sp * kb_per;
         const int kb1 = min(g.kblocks, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb) {
+          if (*s_abort && armed >= pre) {
+            ok = false;
+            break;
+          }
           const uint32_t sa = ring + stage * S::kStageBytes;
           const bool early = armed < pre;  // weight tile of this stage is already on its way
           if (!early) {
@@ -277,6 +314,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
         }
         tc_fence_before_sync();
         mbar_arrive(&tempty_bar[acc]);
+        sink.unit_done(et);
       } else {
         // partial tile -> workspace [unit][row][col] (each thread owns a row)
         float4* wp = reinterpret_cast<float4*>(g.ws + (size_t(u) * kTileA + row) * BN);
@@ -350,6 +388,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
     tmem_dealloc(tmem_base, S::kTmemCols);
   }
   if (threadIdx.x == 0 && *s_abort && g.err) *g.err = 1u;
+  if (threadIdx.x == 0 && g.gate_flags) {
+    __threadfence();
+    const uint32_t t = atomicAdd(g.gate_ticket, 1u);
+    if (t == gridDim.x - 1) {
+      *g.gate_ticket = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(g.gate_cum) = *g.gate_cum + g.gate_add;
+    }
+  }
 }
 
 }  // namespace bl

@@ -33,6 +33,7 @@ struct LocalSink {
   const __nv_bfloat16* residual;
   int ldo, ra, rb, swap, epi;
 
+  __device__ __forceinline__ void unit_done(int) const {}
   __device__ __forceinline__ void operator()(int ta, int tb, int /*split*/, int row, int c0,
                                              const float (&v)[32], int ncols) const {
     const int i = ta * kTileA + row;
@@ -144,6 +145,7 @@ struct PartialSink {
   size_t slab;         // elements per split
   int ldo, ra, rb, swap;
 
+  __device__ __forceinline__ void unit_done(int) const {}
   __device__ __forceinline__ void operator()(int ta, int tb, int split, int row, int c0,
                                              const float (&v)[32], int ncols) const {
     const int i = ta * kTileA + row;
@@ -169,6 +171,46 @@ struct PartialSink {
     }
   }
 };
+
+// Epilogue of the row-parallel linear fused with the reduce-scatter: token m
+// belongs to rank m / tpr; every k-split stores its fp32 partial row straight
+// into that rank's inbox [src rank][split][local token][feature] over NVLink
+// and, once a tile is out, bumps the owners' arrival counters with a release at
+// system scope.  No collective library call, no local staging.
+template <int BN>
+struct PeerSlabSink {
+  float* inbox[kMaxRanks];      // each owner's inbox as mapped here
+  uint32_t* flag[kMaxRanks];    // each owner's arrival word for this source rank
+  int world, rank, tpr, n, splits, tokens;
+
+  __device__ __forceinline__ void operator()(int ta, int tb, int split, int row, int c0,
+                                             const float (&v)[32], int ncols) const {
+    const int i = ta * kTileA + row;  // feature
+    const int j0 = tb * BN + c0;      // first token of this chunk
+    if (i >= n) return;
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      const int m = j0 + c;
+      if (c < ncols && m < tokens) {
+        const int owner = m / tpr, lm = m - owner * tpr;
+        float* dst = inbox[owner] + ((size_t(rank) * splits + split) * tpr + lm) * n + i;
+        asm volatile("st.global.f32 [%0], %1;" ::"l"(dst), "f"(v[c]) : "memory");
+      }
+    }
+  }
+  __device__ __forceinline__ void unit_done(int et) const {
+    __threadfence_system();
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (et < world) red_release_sys_add(flag[et], 1u);
+  }
+};
+
+template <int BN, int CPS>
+__global__ void __launch_bounds__(kGemmThreads, CPS)
+    k_gemm_peer(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                GemmShape g, PeerSlabSink<BN> sink, uint64_t hint_a, uint64_t hint_b) {
+  gemm_body<BN, CPS>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
+}
 
 template <int BN, int CPS>
 __global__ void __launch_bounds__(kGemmThreads, CPS)
@@ -304,7 +346,7 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
   int slots = sms * S::kCtasPerSm * wave / 100;
   if (slots < 1) slots = 1;
   g.splits = pick_splits(tiles, g.kblocks, slots, splits_want);
-  const bool partial = a.partial_out != nullptr;
+  const bool partial = a.partial_out != nullptr || a.peer != nullptr;
   if (partial) {
     if (a.partial_splits < 1 || g.splits > a.partial_splits) g.splits = a.partial_splits;
     // the caller sized the slabs for exactly partial_splits; fewer is not allowed
@@ -320,6 +362,12 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
     if (!a.ws || a.ws_bytes < need || !a.counters || a.n_counters < tiles) g.splits = 1;
   }
   g.direct = 0;
+  g.gate_flags = static_cast<const uint32_t*>(a.gate_flags);
+  g.gate_cum = static_cast<uint32_t*>(a.gate_cum);
+  g.gate_ticket = static_cast<uint32_t*>(a.gate_ticket);
+  g.gate_add = a.gate_add;
+  g.gate_n = a.gate_n;
+  g.gate_timeout_ns = a.gate_timeout_ns ? a.gate_timeout_ns : 2000000000ull;
   g.ab_fmt = 1;
   g.weights_in_a = a.dynamic_weights ? 2 : (a.swap ? 1 : 0);
   g.ws = static_cast<float*>(a.ws);
@@ -331,7 +379,34 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
   // weights stream through L2 once, activations are re-read by every CTA
   const uint64_t hint_w = kHintEvictFirst, hint_x = kHintEvictLast;
   cudaError_t e;
-  if (partial) {
+  if (a.peer) {
+    g.direct = 1;
+    const blPeerSink& ps_in = *a.peer;
+    PeerSlabSink<BN> ps;
+    for (int r = 0; r < kMaxRanks; ++r) {
+      ps.inbox[r] = static_cast<float*>(ps_in.inbox[r]);
+      ps.flag[r] = static_cast<uint32_t*>(ps_in.flag[r]);
+    }
+    ps.world = ps_in.world;
+    ps.rank = ps_in.rank;
+    ps.tpr = ps_in.tokens_per_rank;
+    ps.n = a.ra;
+    ps.splits = g.splits;
+    ps.tokens = a.rb;
+    static bool attr_q = false;
+    if (!attr_q) {
+      e = cudaFuncSetAttribute(k_gemm_peer<BN, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               S::kBytes);
+      if (e != cudaSuccess) {
+        set_err(err, errlen, "barlink: cannot raise shared memory to %d B: %s", S::kBytes,
+                cudaGetErrorString(e));
+        return -1;
+      }
+      attr_q = true;
+    }
+    e = launch_k(k_gemm_peer<BN, CPS>, dim3(grid), dim3(kGemmThreads), size_t(S::kBytes), st, ta, tb,
+                 g, ps, hint_w, hint_x);
+  } else if (partial) {
     g.direct = 1;
     PartialSink<BN> ps;
     ps.out = static_cast<float*>(a.partial_out);
@@ -397,7 +472,7 @@ extern "C" int bl_gemm_splits(int n, int k, int tokens) {
 }
 
 extern "C" int bl_gemm_bf16(const blGemmArgs* a, void* stream, char* err, size_t errlen) {
-  if (!a || !a->a || !a->b || (!a->out && !a->partial_out) || a->ra < 1 || a->rb < 1 || a->k < 8 || (a->k & 7)) {
+  if (!a || !a->a || !a->b || (!a->out && !a->partial_out && !a->peer) || a->ra < 1 || a->rb < 1 || a->k < 8 || (a->k & 7)) {
     set_err(err, errlen, "barlink: gemm needs non-null operands and K a multiple of 8");
     return -1;
   }

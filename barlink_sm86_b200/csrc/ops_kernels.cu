@@ -55,13 +55,7 @@ __global__ void __launch_bounds__(512) k_rmsnorm(const uint4* __restrict__ x,
         // x is the sum of the k-split slabs of the linear before this norm,
         // rounded to bf16 as that linear's output would have been
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        const float* pp = partials + (row * vpr + i) * 8;
-        for (int sp = 0; sp < nsplit; ++sp) {
-          const float4 u = __ldcg(reinterpret_cast<const float4*>(pp + sp * slab));
-          const float4 w = __ldcg(reinterpret_cast<const float4*>(pp + sp * slab) + 1);
-          acc[0] += u.x; acc[1] += u.y; acc[2] += u.z; acc[3] += u.w;
-          acc[4] += w.x; acc[5] += w.y; acc[6] += w.z; acc[7] += w.w;
-        }
+        sum_slabs8(partials + (row * vpr + i) * 8, slab, nsplit, acc);
         a = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
                        pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
       } else {

@@ -314,4 +314,25 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t v) {
   return __bfloat1622float2(h);
 }
 
+// acc[0..8) += sum over n slabs (stride elements apart) of the 8 floats at p,
+// in slab order; the loads of up to eight slabs are in flight together
+__device__ __forceinline__ void sum_slabs8(const float* p, size_t stride, int n, float (&acc)[8]) {
+  for (int s0 = 0; s0 < n; s0 += 8) {
+    float4 u[8][2];
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      if (s0 + q < n) {
+        const float4* v = reinterpret_cast<const float4*>(p + size_t(s0 + q) * stride);
+        u[q][0] = __ldcg(v);
+        u[q][1] = __ldcg(v + 1);
+      }
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      if (s0 + q < n) {
+        acc[0] += u[q][0].x; acc[1] += u[q][0].y; acc[2] += u[q][0].z; acc[3] += u[q][0].w;
+        acc[4] += u[q][1].x; acc[5] += u[q][1].y; acc[6] += u[q][1].z; acc[7] += u[q][1].w;
+      }
+  }
+}
+
 }  // namespace bl

@@ -241,6 +241,79 @@ class Qwen2Model:
 
         return self._run_layers(ids, positions, attn_factory, split_k=True)
 
+    # ---- decode with the fused tensor-parallel linears -------------------------
+    def fused_ok(self, tokens):
+        """Row-parallel GEMM->reduce-scatter and all-gather->column-parallel GEMM
+        need the link and a token count that splits over the ranks.  They are
+        selected with BL_FUSED_LINEAR=1; the default decode path is the k-split
+        GEMM followed by the one-hop fused all-reduce+RMSNorm, which measured
+        faster at decode sizes (the reduce-scatter/all-gather pair costs two
+        flag round trips per half layer, the one-shot all-reduce none)."""
+        import os
+        c = self.comm
+        return (c.world > 1 and c.use_link and tokens % c.world == 0 and tokens <= 256
+                and self.device.type == "cuda" and os.environ.get("BL_FUSED_LINEAR", "0") == "1")
+
+    def _fused_buffers(self, tokens):
+        key = ("fused", tokens)
+        if getattr(self, "_fbuf_key", None) != key:
+            from .. import load_extension
+            C = load_extension()
+            H, w = self.cfg.hidden, self.comm.world
+            smax = 1
+            for n, k in ((H, self.nq * self.hd), (H, self.w.inter_local)):
+                smax = max(smax, C.gemm_splits(n, k, tokens))
+            tpr = tokens // w
+            dev = self.device.index or 0
+            inbox = C.empty(4 * w * smax * tpr * H, 0, torch.float32)
+            gather = C.empty(2 * tokens * H, 0, torch.bfloat16).view(tokens, H)
+            inbox.zero_()
+            gather.zero_()
+            self._fbuf = (inbox, gather, torch.zeros(tpr, H, dtype=self.dtype, device=self.device))
+            self._fbuf_key = key
+        return self._fbuf
+
+    def decode_hidden_fused(self, ids, positions, slots, ctx_lens, cache: PagedKV, splits=0):
+        """Same result as decode_hidden; the residual stream is sharded by tokens:
+        o_proj/down push fp32 partial rows to each token's owner from the GEMM
+        epilogue, the owner reduces + adds the residual + normalises and stores
+        the normed rows into every rank's gather buffer, and the next GEMM waits
+        for those rows while its weights are already streaming."""
+        from .. import load_extension
+        C = load_extension()
+        cfg, c, w = self.cfg, self.comm, self.w
+        T = ids.shape[0]
+        tpr = T // c.world
+        nq, nkv, hd = self.nq, self.nkv, self.hd
+        inbox, gather, res = self._fused_buffers(T)
+        h0 = ops.embedding(ids, w.embed)
+        res.copy_(h0[c.rank * tpr:(c.rank + 1) * tpr])
+        x, _ = ops.rmsnorm(h0, w.layers[0]["ln1"], cfg.eps)
+        gate = 0
+        for li, L in enumerate(w.layers):
+            qkv = ops.linear_split(x, L["wqkv"], gate_tokens=gate)
+            if qkv.dtype == torch.float32:
+                qkv = ops.rope_kv_write(qkv, positions, slots, cache.k[li], cache.v[li], nq, nkv, hd,
+                                        cache.block_size, cfg.theta, L["bqkv"])
+            else:
+                if L["bqkv"] is not None:
+                    qkv = qkv + L["bqkv"]
+                qkv = ops.rope_kv_write(qkv, positions, slots, cache.k[li], cache.v[li], nq, nkv, hd,
+                                        cache.block_size, cfg.theta)
+            a = ops.paged_attn_decode(qkv, cache.k[li], cache.v[li], cache.block_tables, ctx_lens,
+                                      nq, nkv, hd, self.scale, splits)
+            ops._count(2)
+            units, S = C.tp_gemm_rs(a, L["wo"], inbox)
+            C.tp_rs_finish(inbox, gather, res, L["ln2"], cfg.eps, T, S, units)
+            act = ops.linear(gather, L["wgu"], silu_mul=True, gate_tokens=T)
+            nxt = w.layers[li + 1]["ln1"] if li + 1 < len(w.layers) else w.ln_f
+            ops._count(2)
+            units, S = C.tp_gemm_rs(act, L["wdown"], inbox)
+            C.tp_rs_finish(inbox, gather, res, nxt, cfg.eps, T, S, units)
+            x, gate = gather, T
+            c.ar_calls += 2
+        return gather, T
+
     def logits_local(self, hidden):
         return ops.linear(hidden, self.w.lm_head)
 
@@ -313,9 +386,15 @@ class DecodeEngine:
         return nxt
 
     def _step_body(self):
-        hidden = self.m.decode_hidden(self.ids, self.positions, self.slots, self.ctx_lens, self.cache,
-                                      self.attn_splits)
-        nxt = self.m.next_tokens(hidden)
+        if self.m.fused_ok(self.batch):
+            hidden, gate = self.m.decode_hidden_fused(self.ids, self.positions, self.slots,
+                                                      self.ctx_lens, self.cache, self.attn_splits)
+            logits = ops.linear(hidden, self.m.w.lm_head, gate_tokens=gate)
+            nxt = self.m.comm.argmax_vocab_parallel(logits, self.m.w.vocab_local)
+        else:
+            hidden = self.m.decode_hidden(self.ids, self.positions, self.slots, self.ctx_lens,
+                                          self.cache, self.attn_splits)
+            nxt = self.m.next_tokens(hidden)
         self.out_ids.copy_(nxt)
         if self.m.device.type == "cuda":
             # one kernel: position, context length, KV slot and next input id

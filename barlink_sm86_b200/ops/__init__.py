@@ -26,16 +26,18 @@ def _count(n=1):
     launch_count += n
 
 
-def linear(x, weight, bias=None, residual=None, silu_mul=False, out=None):
+def linear(x, weight, bias=None, residual=None, silu_mul=False, out=None, gate_tokens=0):
+    """gate_tokens > 0: x is the all-gather buffer of the fused tensor-parallel
+    path; the kernel waits for the peers' rows before it reads x."""
     if x.is_cuda:
         _count()
         x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
-        y = _C().linear(x2, weight, bias, residual, silu_mul, out)
+        y = _C().linear(x2, weight, bias, residual, silu_mul, out, gate_tokens=gate_tokens)
         return y if x.dim() == 2 else y.view(*x.shape[:-1], y.shape[-1])
     return ref.linear(x, weight, bias, residual, silu_mul)
 
 
-def linear_split(x, weight):
+def linear_split(x, weight, gate_tokens=0):
     """Decode-path linear: when the shape wants a k-split, returns fp32 slabs
     [splits, tokens, n] whose sum is x @ weight.T (the consumer -- `rmsnorm`,
     `rope_kv_write`, the fused all-reduce -- adds them while reading, so the
@@ -45,8 +47,8 @@ def linear_split(x, weight):
         splits = C.gemm_splits(weight.shape[0], weight.shape[1], x.shape[0])
         if splits > 1:
             _count()
-            return C.linear_partial(x, weight, splits)
-    return linear(x, weight)
+            return C.linear_partial(x, weight, splits, None, gate_tokens)
+    return linear(x, weight, gate_tokens=gate_tokens)
 
 
 def rmsnorm(x, gamma, eps, residual=None, out=None):

@@ -47,8 +47,16 @@ def generate(model):
     return torch.stack(seq, 1)
 
 
+os.environ["BL_FUSED_LINEAR"] = "1"
+assert tp.fused_ok(B), "the fused TP linears should be available for this shape"
 tok_tp = generate(tp)
+os.environ["BL_FUSED_LINEAR"] = "0"
+tok_unfused = generate(tp)
 tok_1 = generate(one)
+m_fu = (tok_tp == tok_unfused).float().mean().item()
+if rank == 0:
+    print("[tp] fused vs all-reduce path token match %.0f%%" % (m_fu * 100), flush=True)
+assert m_fu >= 0.7, m_fu
 gathered = [torch.empty_like(tok_tp) for _ in range(world)]
 dist.all_gather(gathered, tok_tp)
 for g in gathered:
