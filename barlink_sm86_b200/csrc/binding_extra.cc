@@ -132,9 +132,133 @@ at::Tensor attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& 
   return out;
 }
 
+void check_bf16x(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == at::kBFloat16, "barlink: ", name,
+              " must be a contiguous bfloat16 CUDA tensor");
+}
+
+struct W8Scratch {
+  at::Tensor ws, counters, err_flag;
+};
+W8Scratch& w8_scratch(int dev) {
+  static std::map<int, W8Scratch> m;
+  auto it = m.find(dev);
+  if (it != m.end()) return it->second;
+  auto o = at::TensorOptions().device(at::kCUDA, dev);
+  W8Scratch s;
+  s.ws = at::empty({int64_t(64) << 20}, o.dtype(at::kByte));
+  s.counters = at::zeros({16384}, o.dtype(at::kInt));
+  s.err_flag = at::zeros({4}, o.dtype(at::kInt));
+  return m.emplace(dev, s).first->second;
+}
+
+// y = x @ (wq * scale[:, None]).T (+ bias): bf16 activations, int8 per-channel
+// weights widened to bf16 inside the tcgen05 main loop (<= 256 tokens); more
+// tokens widen the weight once and use the bf16 GEMM.
+at::Tensor w8a16_linear(const at::Tensor& x, const at::Tensor& wq, const at::Tensor& scale,
+                        const c10::optional<at::Tensor>& bias, bool silu_mul, int splits) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
+              "barlink: x must be a 2-D bfloat16 CUDA tensor with unit inner stride");
+  TORCH_CHECK(wq.is_cuda() && wq.is_contiguous() && wq.scalar_type() == at::kChar && wq.dim() == 2 &&
+                  wq.size(1) == x.size(1),
+              "barlink: wq must be a contiguous int8 [n, k] CUDA tensor with k = x.shape[1]");
+  check_bf16x(scale, "scale");
+  const int m = int(x.size(0)), k = int(x.size(1)), n = int(wq.size(0));
+  TORCH_CHECK(scale.numel() == n, "barlink: scale must have one entry per output channel");
+  const int dev = x.device().index();
+  c10::cuda::CUDAGuard guard(x.device());
+  void* st = at::cuda::getCurrentCUDAStream(dev).stream();
+  at::Tensor out = at::empty({m, silu_mul ? n / 2 : n}, x.options());
+  if (m == 0) return out;
+  if (m > 256) {
+    at::Tensor w = at::empty({n, k}, x.options());
+    BL_CHECK(bl_w8_dequant(wq.data_ptr(), scale.data_ptr(), w.data_ptr(), n, k, st, err, errlen));
+    py::object lin = py::module_::import("barlink_sm86_b200").attr("load_extension")().attr("linear");
+    return lin(x, w, bias ? py::cast(*bias) : py::none(), py::none(), silu_mul).cast<at::Tensor>();
+  }
+  W8Scratch& s = w8_scratch(dev);
+  blW8A16Args a;
+  memset(&a, 0, sizeof(a));
+  a.x = x.data_ptr();
+  a.m = m;
+  a.ldx = int(x.stride(0));
+  a.wq = wq.data_ptr();
+  a.n = n;
+  a.k = k;
+  a.scale = scale.data_ptr();
+  if (bias) {
+    check_bf16x(*bias, "bias");
+    TORCH_CHECK(bias->numel() == n, "barlink: bias must have n entries");
+    a.bias = bias->data_ptr();
+  }
+  a.out = out.data_ptr();
+  a.ldo = silu_mul ? n / 2 : n;
+  a.silu_mul = silu_mul ? 1 : 0;
+  a.splits = splits;
+  a.ws = s.ws.data_ptr();
+  a.ws_bytes = size_t(s.ws.nbytes());
+  a.counters = s.counters.data_ptr();
+  a.n_counters = int(s.counters.numel());
+  a.err_flag = s.err_flag.data_ptr();
+  {
+    py::gil_scoped_release nogil;
+    BL_CHECK(bl_w8a16_linear(&a, st, err, errlen));
+  }
+  return out;
+}
+
+int w8_error_flag(int dev) { return w8_scratch(dev).err_flag.cpu()[0].item<int>(); }
+
+// the reference's pair (binding.cpp:434-490 there)
+std::vector<at::Tensor> w8a16_quant_act(const at::Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 2 && x.scalar_type() == at::kBFloat16,
+              "barlink w8a16_quant_act: x must be a contiguous 2-D bfloat16 CUDA tensor");
+  const int m = int(x.size(0)), k = int(x.size(1));
+  TORCH_CHECK(k % 8 == 0, "barlink w8a16_quant_act: K % 8 must be 0");
+  at::Tensor xq = at::empty({m, k}, x.options().dtype(at::kChar));
+  at::Tensor xs = at::empty({m}, x.options().dtype(at::kFloat));
+  c10::cuda::CUDAGuard guard(x.device());
+  void* st = at::cuda::getCurrentCUDAStream(x.device().index()).stream();
+  if (m > 0) BL_CHECK(bl_w8a16_quant_act(x.data_ptr(), m, k, xq.data_ptr(), xs.data_ptr(), st, err, errlen));
+  return {xq, xs};
+}
+
+at::Tensor w8a16_gemm(const at::Tensor& xq, const at::Tensor& xs, const at::Tensor& wq_t,
+                      const at::Tensor& sw_t, int64_t N, int64_t K, int64_t S) {
+  TORCH_CHECK(xq.is_cuda() && xq.is_contiguous() && xq.dim() == 2 && xq.scalar_type() == at::kChar,
+              "barlink w8a16_gemm: xq must be contiguous int8 [M, K]");
+  const int m = int(xq.size(0));
+  TORCH_CHECK(xq.size(1) == K && K % 128 == 0, "barlink w8a16_gemm: K must match xq and be a multiple of 128");
+  TORCH_CHECK(wq_t.is_contiguous() && wq_t.scalar_type() == at::kChar && wq_t.numel() == N * K &&
+                  sw_t.is_contiguous() && sw_t.scalar_type() == at::kFloat && sw_t.numel() == (K / 128) * N,
+              "barlink w8a16_gemm: wq_t int8 [K/16, N, 16] and sw_t float32 [K/128, N], contiguous");
+  TORCH_CHECK(xs.is_contiguous() && xs.scalar_type() == at::kFloat && xs.numel() == m,
+              "barlink w8a16_gemm: xs must be float32 [M]");
+  TORCH_CHECK(m <= 16, "barlink w8a16_gemm: M > 16 is not supported by this decode kernel (use w8a16_linear)");
+  at::Tensor out = at::empty({m, N}, xq.options().dtype(at::kBFloat16));
+  at::Tensor ws;
+  void* wsp = nullptr;
+  if (S > 1) {
+    ws = at::empty({S, m, N}, xq.options().dtype(at::kFloat));
+    wsp = ws.data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(xq.device());
+  void* st = at::cuda::getCurrentCUDAStream(xq.device().index()).stream();
+  if (m > 0)
+    BL_CHECK(bl_w8a16_gemm(xq.data_ptr(), xs.data_ptr(), wq_t.data_ptr(), sw_t.data_ptr(), out.data_ptr(),
+                           m, int(N), int(K), int(S), wsp, st, err, errlen));
+  return out;
+}
+
 }  // namespace
 
 void bind_extra(py::module_& m) {
+  m.def("w8a16_linear", &w8a16_linear, py::arg("x"), py::arg("wq"), py::arg("scale"),
+        py::arg("bias") = py::none(), py::arg("silu_mul") = false, py::arg("splits") = 0);
+  m.def("w8_error_flag", &w8_error_flag, py::arg("device") = 0);
+  m.def("w8a16_quant_act", &w8a16_quant_act);
+  m.def("w8a16_gemm", &w8a16_gemm, py::arg("xq"), py::arg("xs"), py::arg("wq_t"), py::arg("sw_t"),
+        py::arg("N"), py::arg("K"), py::arg("S"));
   m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("cu_q"),
         py::arg("cu_k"), py::arg("max_q"), py::arg("scale"), py::arg("causal"));
   m.def("sp_collective", &sp_collective, py::arg("kind"), py::arg("ins") = std::vector<at::Tensor>{},

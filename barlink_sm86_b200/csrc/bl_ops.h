@@ -103,8 +103,18 @@ typedef struct blW8A16Args {
   void* counters;
   int n_counters;
   void* err_flag;
+  /* split-K slabs instead of a reduced output (see blGemmArgs.partial_out); the
+   * per-channel scale is applied to every slab */
+  void* partial_out;
+  size_t partial_stride;
+  int partial_splits;
 } blW8A16Args;
+/* returns -2 (and launches nothing) for more than 256 tokens */
 int bl_w8a16_linear(const blW8A16Args* a, void* stream, char* err, size_t errlen);
+/* out[n x k] bf16 = wq[n x k] int8 * scale[n]: the prefill path widens once and
+ * then uses the bf16 GEMM */
+int bl_w8_dequant(const void* wq, const void* scale, void* out, int n, int k, void* stream, char* err,
+                  size_t errlen);
 /* reference-compatible pair (w8a16.cu:165-212): per-token int8 activation
  * quantisation and the int8 x int8 GEMM with group-128 weight scales */
 int bl_w8a16_quant_act(const void* x, int m, int k, void* xq, void* xs, void* stream, char* err,

@@ -60,15 +60,21 @@ struct GemmShape {
   unsigned long long gate_timeout_ns;
 };
 
-template <int BN, int CPS = 1>
+// W8: the A operand (weight rows) is int8 in global memory; its 128x64-byte raw
+// tile lands in a third region of the stage and four extra warps widen it to
+// bf16 into the swizzled A region before the MMA warp may use the stage.
+template <int BN, int CPS = 1, bool W8 = false>
 struct GemmSmem {
   static constexpr int kStageA = kTileA * kTileK * 2;
   static constexpr int kStageB = BN * kTileK * 2;
-  static constexpr int kStageBytes = kStageA + kStageB;
+  static constexpr int kStageRaw = W8 ? kTileA * kTileK : 0;
+  static constexpr int kStageBytes = kStageA + kStageB + kStageRaw;
+  static constexpr int kTxBytes = (W8 ? kStageRaw : kStageA) + kStageB;  // bytes TMA delivers per stage
+  static constexpr int kThreads = kGemmThreads + (W8 ? 128 : 0);
   // narrow tiles (decode): 4 stages so that two CTAs share an SM -- the same
   // bytes in flight per SM, but a CTA of the next kernel can move in and
   // prefetch weights while one of this kernel is still in its epilogue
-  static constexpr int kStages = (CPS == 2) ? 4 : (BN <= 64 ? 8 : (BN <= 128 ? 6 : 4));
+  static constexpr int kStages = W8 ? (BN <= 64 ? 6 : 4) : (CPS == 2) ? 4 : (BN <= 64 ? 8 : (BN <= 128 ? 6 : 4));
   static constexpr int kCtasPerSm = CPS;
   static constexpr int kBarBytes = 1024;
   // + 1024 so that the tile ring can be aligned to the swizzle atom
@@ -82,18 +88,31 @@ struct GemmSmem {
 // called by each of the 128 epilogue threads (row_in_tile = TMEM lane) once per
 // 32-column chunk of a finished tile; all 32 threads of a warp call it together.
 
-template <int BN, int CPS, class Sink>
+// four int8 in one word -> two bf16x2 words, exactly (|v| <= 128 fits bf16's 8 bits)
+__device__ __forceinline__ void s8x4_to_bf16x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t u = w ^ 0x80808080u;  // biased to 0..255
+  const float bias = 8388608.f + 128.f;
+  const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - bias;
+  const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - bias;
+  const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - bias;
+  const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - bias;
+  lo = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
+  hi = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+}
+
+template <int BN, int CPS, bool W8, class Sink>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUtensorMap* tmap_b,
                                           const GemmShape& g, const Sink& sink, uint64_t hint_a,
                                           uint64_t hint_b) {
-  using S = GemmSmem<BN, CPS>;
+  using S = GemmSmem<BN, CPS, W8>;
   extern __shared__ uint8_t smem_raw[];
   // barriers first, then the 1024-aligned stage ring
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem_raw);
   uint64_t* empty_bar = full_bar + S::kStages;
   uint64_t* tfull_bar = empty_bar + S::kStages;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* ready_bar = tempty_bar + 2;  // W8: stage widened to bf16
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ready_bar + S::kStages);
   volatile uint32_t* s_abort = tmem_slot + 1;
   uint32_t* s_last = tmem_slot + 2;
   const uint32_t ring = (smem_u32(smem_raw) + S::kBarBytes + 1023u) & ~1023u;
@@ -112,6 +131,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
     for (int s = 0; s < S::kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
+      mbar_init(&ready_bar[s], 128);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
@@ -146,10 +166,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
         const int kb0 = sp * kb_per;
         const int kb1 = min(g.kblocks, kb0 + kb_per);
         for (int kb = kb0; kb < kb1 && pre < S::kStages; ++kb, ++pre) {
-          mbar_expect_tx(&full_bar[pre], S::kStageBytes);
+          mbar_expect_tx(&full_bar[pre], S::kTxBytes);
           const uint32_t sa = ring + pre * S::kStageBytes;
           if (g.weights_in_a)
-            tma_load_2d_hint_s(sa, tmap_a, smem_u32(&full_bar[pre]), kb * kTileK, ta * kTileA, hint_a);
+            tma_load_2d_hint_s(sa + (W8 ? S::kStageA + S::kStageB : 0), tmap_a,
+                               smem_u32(&full_bar[pre]), kb * kTileK, ta * kTileA, hint_a);
           else
             tma_load_2d_hint_s(sa + S::kStageA, tmap_b, smem_u32(&full_bar[pre]), kb * kTileK,
                                tb * BN, hint_b);
@@ -200,11 +221,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
               ok = false;
               break;
             }
-            mbar_expect_tx(&full_bar[stage], S::kStageBytes);
+            mbar_expect_tx(&full_bar[stage], S::kTxBytes);
           }
           if (!early || !g.weights_in_a)
-            tma_load_2d_hint_s(sa, tmap_a, smem_u32(&full_bar[stage]), kb * kTileK, ta * kTileA,
-                               hint_a);
+            tma_load_2d_hint_s(sa + (W8 ? S::kStageA + S::kStageB : 0), tmap_a,
+                               smem_u32(&full_bar[stage]), kb * kTileK, ta * kTileA, hint_a);
           if (!early || g.weights_in_a)
             tma_load_2d_hint_s(sa + S::kStageA, tmap_b, smem_u32(&full_bar[stage]), kb * kTileK,
                                tb * BN, hint_b);
@@ -250,7 +271,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait_bounded(&full_bar[stage], phase, s_abort)) {
+          if (!mbar_wait_bounded(W8 ? &ready_bar[stage] : &full_bar[stage], phase, s_abort)) {
             ok = false;
             break;
           }
@@ -272,6 +293,53 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
           }
         }
         if (ok) umma_commit(&tfull_bar[acc]);
+      }
+    }
+  } else if (W8 && warp >= 6) {
+    // ------------------------ int8 -> bf16 widening -----------------------
+    // thread = tile row: 64 int8 in, 8 swizzled 16-byte chunks of bf16 out
+    const int row = threadIdx.x - kGemmThreads;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      const int tile = u / g.splits, sp = u - tile * g.splits;
+      const int kb0 = sp * kb_per;
+      const int kb1 = min(g.kblocks, kb0 + kb_per);
+      (void)tile;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait_bounded(&full_bar[stage], phase, s_abort)) {
+          ok = false;
+          break;
+        }
+        const uint32_t sa = ring + stage * S::kStageBytes;
+        const uint32_t src = sa + S::kStageA + S::kStageB + row * kTileK;
+        const uint32_t dst = sa + row * 128;
+#pragma unroll
+        for (int qd = 0; qd < 4; ++qd) {
+          uint32_t w0, w1, w2, w3;
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
+                       : "r"(src + qd * 16));
+          uint32_t o0, o1, o2, o3, o4, o5, o6, o7;
+          s8x4_to_bf16x4(w0, o0, o1);
+          s8x4_to_bf16x4(w1, o2, o3);
+          s8x4_to_bf16x4(w2, o4, o5);
+          s8x4_to_bf16x4(w3, o6, o7);
+          const int c0 = qd * 2, c1 = qd * 2 + 1;
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + (((c0 ^ (row & 7))) << 4)),
+                       "r"(o0), "r"(o1), "r"(o2), "r"(o3)
+                       : "memory");
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + (((c1 ^ (row & 7))) << 4)),
+                       "r"(o4), "r"(o5), "r"(o6), "r"(o7)
+                       : "memory");
+        }
+        fence_proxy_async_smem();  // the tensor core reads what these threads just wrote
+        mbar_arrive(&ready_bar[stage]);
+        if (++stage == S::kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
       }
     }
   } else {

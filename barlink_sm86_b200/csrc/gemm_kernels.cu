@@ -32,12 +32,28 @@ struct LocalSink {
   const __nv_bfloat16* bias;
   const __nv_bfloat16* residual;
   int ldo, ra, rb, swap, epi;
+  const __nv_bfloat16* scale;  // per output feature (W8A16), or null
 
   __device__ __forceinline__ void unit_done(int) const {}
   __device__ __forceinline__ void operator()(int ta, int tb, int /*split*/, int row, int c0,
-                                             const float (&v)[32], int ncols) const {
+                                             const float (&vin)[32], int ncols) const {
     const int i = ta * kTileA + row;
     const int j0 = tb * BN + c0;
+    float v[32];
+    if (scale) {
+      if (swap) {
+        const float sc = i < ra ? __bfloat162float(scale[i]) : 0.f;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c] = vin[c] * sc;
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          v[c] = (c < ncols && j0 + c < rb) ? vin[c] * __bfloat162float(scale[j0 + c]) : 0.f;
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = vin[c];
+    }
     if (!swap) {
       const int m = i;
       if (m >= ra) return;
@@ -132,7 +148,7 @@ template <int BN, int CPS>
 __global__ void __launch_bounds__(kGemmThreads, CPS)
     k_gemm(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
            GemmShape g, LocalSink<BN> sink, uint64_t hint_a, uint64_t hint_b) {
-  gemm_body<BN, CPS>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
+  gemm_body<BN, CPS, false>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
 }
 
 // Epilogue of the split-K decode path: every k-split stores its raw fp32
@@ -144,13 +160,29 @@ struct PartialSink {
   float* out;          // [splits][tokens][n]
   size_t slab;         // elements per split
   int ldo, ra, rb, swap;
+  const __nv_bfloat16* scale;  // per output feature (W8A16), or null
 
   __device__ __forceinline__ void unit_done(int) const {}
   __device__ __forceinline__ void operator()(int ta, int tb, int split, int row, int c0,
-                                             const float (&v)[32], int ncols) const {
+                                             const float (&vin)[32], int ncols) const {
     const int i = ta * kTileA + row;
     const int j0 = tb * BN + c0;
     float* base = out + size_t(split) * slab;
+    float v[32];
+    if (scale) {
+      if (swap) {
+        const float sc = i < ra ? __bfloat162float(scale[i]) : 0.f;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c] = vin[c] * sc;
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          v[c] = (c < ncols && j0 + c < rb) ? vin[c] * __bfloat162float(scale[j0 + c]) : 0.f;
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) v[c] = vin[c];
+    }
     if (swap) {
       if (i >= ra) return;  // i = feature, j = token: a warp stores 32 consecutive features
 #pragma unroll
@@ -209,7 +241,7 @@ template <int BN, int CPS>
 __global__ void __launch_bounds__(kGemmThreads, CPS)
     k_gemm_peer(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 GemmShape g, PeerSlabSink<BN> sink, uint64_t hint_a, uint64_t hint_b) {
-  gemm_body<BN, CPS>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
+  gemm_body<BN, CPS, false>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
 }
 
 template <int BN, int CPS>
@@ -217,7 +249,7 @@ __global__ void __launch_bounds__(kGemmThreads, CPS)
     k_gemm_partial(const __grid_constant__ CUtensorMap tmap_a,
                    const __grid_constant__ CUtensorMap tmap_b, GemmShape g, PartialSink<BN> sink,
                    uint64_t hint_a, uint64_t hint_b) {
-  gemm_body<BN, CPS>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
+  gemm_body<BN, CPS, false>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
 }
 
 // ---------------------------------------------------------------------------
@@ -226,7 +258,7 @@ __global__ void __launch_bounds__(kGemmThreads, CPS)
 struct TmapKey {
   const void* ptr;
   uint64_t rows, cols, ld;
-  uint32_t box_rows, esize;
+  uint32_t box_rows, esize;  // esize 1 = int8 rows of 64 bytes, unswizzled
   bool operator==(const TmapKey& o) const {
     return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld &&
            box_rows == o.box_rows && esize == o.esize;
@@ -268,14 +300,15 @@ int make_tmap_kmajor(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
   }
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {ld * esize};
-  cuuint32_t box[2] = {128u / esize, box_rows};
+  // 64 elements along K per box row: 128 swizzled bytes of bf16, or 64 plain bytes of int8
+  cuuint32_t box[2] = {64u, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
   CUresult r = d->cuTensorMapEncodeTiled(
       &m, esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
       const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      esize == 2 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     const char* s = nullptr;
     d->cuGetErrorString(r, &s);
@@ -415,6 +448,7 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
     ps.ra = a.ra;
     ps.rb = a.rb;
     ps.swap = a.swap;
+    ps.scale = nullptr;
     static bool attr_p = false;
     if (!attr_p) {
       e = cudaFuncSetAttribute(k_gemm_partial<BN, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -438,6 +472,7 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
     sink.rb = a.rb;
     sink.swap = a.swap;
     sink.epi = (a.bias ? 1 : 0) | (a.residual ? 2 : 0) | (a.silu_mul ? 4 : 0);
+    sink.scale = nullptr;
     static bool attr_set = false;
     if (!attr_set) {
       e = cudaFuncSetAttribute(k_gemm<BN, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -460,9 +495,180 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
   return 0;
 }
 
+// ---------------------------------------------------------------------------
+// W8A16: int8 per-channel weights widened to bf16 inside the main loop
+// ---------------------------------------------------------------------------
+template <int BN>
+__global__ void __launch_bounds__(GemmSmem<BN, 1, true>::kThreads, 1)
+    k_gemm_w8(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+              GemmShape g, LocalSink<BN> sink, uint64_t hint_a, uint64_t hint_b) {
+  gemm_body<BN, 1, true>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
+}
+template <int BN>
+__global__ void __launch_bounds__(GemmSmem<BN, 1, true>::kThreads, 1)
+    k_gemm_w8_partial(const __grid_constant__ CUtensorMap tmap_a,
+                      const __grid_constant__ CUtensorMap tmap_b, GemmShape g, PartialSink<BN> sink,
+                      uint64_t hint_a, uint64_t hint_b) {
+  gemm_body<BN, 1, true>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
+}
+
+__global__ void k_w8_dequant(const int8_t* __restrict__ wq, const __nv_bfloat16* __restrict__ scale,
+                             __nv_bfloat16* __restrict__ out, int n, int k) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t total = size_t(n) * k / 8;
+  for (size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+       t += size_t(gridDim.x) * blockDim.x) {
+    const size_t e = t * 8;
+    const int row = int(e / k);
+    const float sc = __bfloat162float(scale[row]);
+    const uint2 w = *reinterpret_cast<const uint2*>(wq + e);
+    uint32_t a, b, c, d;
+    s8x4_to_bf16x4(w.x, a, b);
+    s8x4_to_bf16x4(w.y, c, d);
+    const float2 f0 = unpack_bf16x2(a), f1 = unpack_bf16x2(b), f2 = unpack_bf16x2(c),
+                 f3 = unpack_bf16x2(d);
+    *reinterpret_cast<uint4*>(out + e) =
+        make_uint4(pack_bf16x2(f0.x * sc, f0.y * sc), pack_bf16x2(f1.x * sc, f1.y * sc),
+                   pack_bf16x2(f2.x * sc, f2.y * sc), pack_bf16x2(f3.x * sc, f3.y * sc));
+  }
+}
+
+template <int BN>
+static int launch_w8(const blW8A16Args& a, cudaStream_t st, char* err, size_t errlen) {
+  using S = GemmSmem<BN, 1, true>;
+  CUtensorMap ta, tb;
+  if (make_tmap_kmajor(a.wq, a.n, a.k, a.k, kTileA, 1, &ta, err, errlen) != 0) return -1;
+  if (make_tmap_kmajor(a.x, a.m, a.k, a.ldx, BN, 2, &tb, err, errlen) != 0) return -1;
+  GemmShape g;
+  memset(&g, 0, sizeof(g));
+  g.ra = a.n;
+  g.rb = a.m;
+  g.k = a.k;
+  g.tiles_a = (a.n + kTileA - 1) / kTileA;
+  g.tiles_b = (a.m + BN - 1) / BN;
+  g.kblocks = (a.k + kTileK - 1) / kTileK;
+  const int tiles = g.tiles_a * g.tiles_b;
+  const int sms = sm_count();
+  const bool partial = a.partial_out != nullptr;
+  g.splits = partial ? a.partial_splits : pick_splits(tiles, g.kblocks, sms, a.splits);
+  if (!partial && g.splits > 1) {
+    const size_t need = size_t(tiles) * g.splits * BN * kTileA * sizeof(float);
+    if (!a.ws || a.ws_bytes < need || !a.counters || a.n_counters < tiles) g.splits = 1;
+  }
+  if (partial) {
+    const int per = (g.kblocks + g.splits - 1) / g.splits;
+    if (g.splits < 1 || (g.kblocks + per - 1) / per != g.splits) {
+      set_err(err, errlen, "barlink: %d k-splits do not divide %d k-blocks into non-empty parts", g.splits,
+              g.kblocks);
+      return -1;
+    }
+  }
+  g.ab_fmt = 1;
+  g.direct = partial ? 1 : 0;
+  g.weights_in_a = 1;
+  g.ws = static_cast<float*>(a.ws);
+  g.counters = static_cast<uint32_t*>(a.counters);
+  g.err = static_cast<uint32_t*>(a.err_flag);
+  g.gate_timeout_ns = 2000000000ull;
+  const int units = tiles * g.splits;
+  const int grid = units < sms ? units : sms;
+  cudaError_t e;
+  if (partial) {
+    PartialSink<BN> ps;
+    ps.out = static_cast<float*>(a.partial_out);
+    ps.slab = a.partial_stride;
+    ps.ldo = a.ldo;
+    ps.ra = a.n;
+    ps.rb = a.m;
+    ps.swap = 1;
+    ps.scale = static_cast<const __nv_bfloat16*>(a.scale);
+    static bool attr = false;
+    if (!attr) {
+      e = cudaFuncSetAttribute(k_gemm_w8_partial<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+      if (e != cudaSuccess) {
+        set_err(err, errlen, "barlink: cannot raise shared memory to %d B: %s", S::kBytes, cudaGetErrorString(e));
+        return -1;
+      }
+      attr = true;
+    }
+    e = launch_k(k_gemm_w8_partial<BN>, dim3(grid), dim3(S::kThreads), size_t(S::kBytes), st, ta, tb, g, ps,
+                 kHintEvictFirst, kHintEvictLast);
+  } else {
+    LocalSink<BN> sink;
+    sink.out = static_cast<__nv_bfloat16*>(a.out);
+    sink.bias = static_cast<const __nv_bfloat16*>(a.bias);
+    sink.residual = nullptr;
+    sink.ldo = a.ldo;
+    sink.ra = a.n;
+    sink.rb = a.m;
+    sink.swap = 1;
+    sink.epi = (a.bias ? 1 : 0) | (a.silu_mul ? 4 : 0);
+    sink.scale = static_cast<const __nv_bfloat16*>(a.scale);
+    static bool attr = false;
+    if (!attr) {
+      e = cudaFuncSetAttribute(k_gemm_w8<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+      if (e != cudaSuccess) {
+        set_err(err, errlen, "barlink: cannot raise shared memory to %d B: %s", S::kBytes, cudaGetErrorString(e));
+        return -1;
+      }
+      attr = true;
+    }
+    e = launch_k(k_gemm_w8<BN>, dim3(grid), dim3(S::kThreads), size_t(S::kBytes), st, ta, tb, g, sink,
+                 kHintEvictFirst, kHintEvictLast);
+  }
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_err(err, errlen, "barlink: W8A16 launch failed: %s", cudaGetErrorString(e));
+    return -1;
+  }
+  return 0;
+}
+
 }  // namespace bl
 
 using namespace bl;
+
+extern "C" int bl_w8a16_linear(const blW8A16Args* a, void* stream, char* err, size_t errlen) {
+  if (!a || !a->x || !a->wq || !a->scale || (!a->out && !a->partial_out) || a->m < 1 || a->n < 1 ||
+      a->k < 16 || (a->k & 15)) {
+    set_err(err, errlen, "barlink: w8a16_linear needs x, wq, scale, an output, and K a multiple of 16");
+    return -1;
+  }
+  if (a->m > 256) {
+    set_err(err, errlen, "barlink: the in-mainloop W8A16 kernel takes at most 256 tokens; dequantise (bl_w8_dequant) and use the bf16 GEMM for prefill");
+    return -2;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int bn = a->m <= 16 ? 16 : a->m <= 32 ? 32 : a->m <= 64 ? 64 : a->m <= 128 ? 128 : 256;
+  switch (bn) {
+    case 16: return launch_w8<16>(*a, st, err, errlen);
+    case 32: return launch_w8<32>(*a, st, err, errlen);
+    case 64: return launch_w8<64>(*a, st, err, errlen);
+    case 128: return launch_w8<128>(*a, st, err, errlen);
+    default: return launch_w8<256>(*a, st, err, errlen);
+  }
+}
+
+extern "C" int bl_w8_dequant(const void* wq, const void* scale, void* out, int n, int k, void* stream,
+                             char* err, size_t errlen) {
+  if (!wq || !scale || !out || n < 1 || k < 8 || (k & 7)) {
+    set_err(err, errlen, "barlink: w8_dequant needs K a multiple of 8");
+    return -1;
+  }
+  const size_t total = size_t(n) * k / 8;
+  int grid = int((total + 255) / 256);
+  if (grid > 148 * 16) grid = 148 * 16;
+  cudaError_t e = launch_k(k_w8_dequant, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                           static_cast<const int8_t*>(wq), static_cast<const __nv_bfloat16*>(scale),
+                           static_cast<__nv_bfloat16*>(out), n, k);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_err(err, errlen, "barlink: w8_dequant launch failed: %s", cudaGetErrorString(e));
+    return -1;
+  }
+  return 0;
+}
 
 extern "C" int bl_gemm_splits(int n, int k, int tokens) {
   if (tokens > 128) return 1;

@@ -1,0 +1,72 @@
+# SPDX-License-Identifier: MIT
+"""W8A16: the tcgen05 kernel that widens int8 weights in its main loop, and the
+reference-compatible quant_act/gemm pair, against fp64 statements on the
+quantised operands (the reference's criterion: rel-L2 < 2e-2,
+torch_ext/tests/test_w8a16.py:45-49 there)."""
+import pytest
+import torch
+
+from conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def _quant(n, k, seed):
+    from barlink_sm86_b200.ops import reference as ref
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    w = torch.randn(n, k, device="cuda", generator=g) * 0.02
+    return ref.quantize_w8(w)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 512, 3072), (3, 5120, 5120), (16, 1024, 8704), (64, 27648 // 8 * 2, 5120),
+                                   (64, 5120, 3456), (200, 640, 512)])
+def test_w8a16_linear(ext, m, n, k):
+    from barlink_sm86_b200.ops import reference as ref
+    wq, scale = _quant(n, k, 1)
+    x = torch.randn(m, k, device="cuda", generator=torch.Generator("cuda").manual_seed(2)).to(torch.bfloat16)
+    got = ext.w8a16_linear(x, wq, scale)
+    torch.cuda.synchronize()
+    assert ext.w8_error_flag(0) == 0
+    want = (x.double() @ wq.double().t()) * scale.double()[None, :]
+    assert rel_l2(got, want) < 1e-2, (m, n, k)
+    assert rel_l2(got, ref.w8a16_linear(x, wq, scale)) < 1e-2
+
+
+def test_w8a16_linear_epilogues_and_splits(ext):
+    from barlink_sm86_b200.ops import reference as ref
+    m, n, k = 8, 1024, 4096
+    wq, scale = _quant(n, k, 3)
+    x = torch.randn(m, k, device="cuda", generator=torch.Generator("cuda").manual_seed(4)).to(torch.bfloat16)
+    bias = torch.randn(n, device="cuda").to(torch.bfloat16)
+    assert rel_l2(ext.w8a16_linear(x, wq, scale, bias), ref.w8a16_linear(x, wq, scale, bias)) < 1e-2
+    assert rel_l2(ext.w8a16_linear(x, wq, scale, None, True), ref.w8a16_linear(x, wq, scale, None, True)) < 2e-2
+    a = ext.w8a16_linear(x, wq, scale, None, False, 4)
+    b = ext.w8a16_linear(x, wq, scale, None, False, 4)
+    assert torch.equal(a, b)
+    assert rel_l2(a, ref.w8a16_linear(x, wq, scale)) < 1e-2
+
+
+def test_w8a16_prefill_path(ext):
+    from barlink_sm86_b200.ops import reference as ref
+    wq, scale = _quant(768, 1024, 5)
+    x = torch.randn(600, 1024, device="cuda").to(torch.bfloat16)
+    assert rel_l2(ext.w8a16_linear(x, wq, scale), ref.w8a16_linear(x, wq, scale)) < 1.5e-2
+
+
+@pytest.mark.parametrize("M", [1, 3, 16])
+@pytest.mark.parametrize("S", [1, 4, 7])
+def test_reference_api_pair(ext, M, S):
+    N, K = 1536, 3072
+    g = torch.Generator(device="cuda").manual_seed(6)
+    wq = torch.randint(-127, 128, (N, K), device="cuda", generator=g, dtype=torch.int32).to(torch.int8)
+    sw = torch.rand(K // 128, N, device="cuda", generator=g) * 0.01 + 0.001
+    wq_t = wq.view(N, K // 16, 16).permute(1, 0, 2).contiguous()
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    xq, xs = ext.w8a16_quant_act(x)
+    amax = x.float().abs().amax(1)
+    assert torch.allclose(xs, (amax / 127).clamp_min(1e-12), rtol=1e-6)
+    assert (xq.float() * xs[:, None] - x.float()).abs().max() <= xs.max() * 0.51
+    y = ext.w8a16_gemm(xq, xs, wq_t, sw, N, K, S)
+    part = (xq.double().view(M, K // 128, 128)[:, :, None, :] * wq.double().view(N, K // 128, 128).permute(1, 0, 2)[None]).sum(-1)
+    want = (part * sw.double()[None]).sum(1) * xs.double()[:, None]
+    assert rel_l2(y, want) < 2e-2
