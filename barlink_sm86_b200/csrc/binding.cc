@@ -450,12 +450,20 @@ int gemm_error_flag(int dev) {
 at::Tensor linear(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
                   const c10::optional<at::Tensor>& residual, bool silu_mul,
                   c10::optional<at::Tensor> out_opt, int force_swap, int bn, int splits,
-                  bool dynamic_weights, c10::optional<at::Tensor> trace, int gate_tokens) {
+                  bool dynamic_weights, c10::optional<at::Tensor> trace, int gate_tokens, int tiled_n,
+                  int tiled_k) {
   check_bf16(w, "weight");
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
               "barlink: x must be a 2-D bfloat16 CUDA tensor with unit inner stride");
-  TORCH_CHECK(w.dim() == 2 && w.size(1) == x.size(1), "barlink: weight must be [n, k] with k = x.shape[1]");
-  const int tokens = int(x.size(0)), k = int(x.size(1)), n = int(w.size(0));
+  const bool tiled = tiled_n > 0;
+  if (tiled) {
+    TORCH_CHECK(tiled_k == x.size(1) && size_t(w.nbytes()) >= bl_tiled_weight_bytes(tiled_n, tiled_k) &&
+                    (reinterpret_cast<uintptr_t>(w.data_ptr()) & 15u) == 0,
+                "barlink: tiled weight buffer does not match (n, k) = (", tiled_n, ", ", tiled_k, ")");
+  } else {
+    TORCH_CHECK(w.dim() == 2 && w.size(1) == x.size(1), "barlink: weight must be [n, k] with k = x.shape[1]");
+  }
+  const int tokens = int(x.size(0)), k = int(x.size(1)), n = tiled ? tiled_n : int(w.size(0));
   const int n_out = silu_mul ? n / 2 : n;
   at::Tensor out = out_opt ? *out_opt : at::empty({tokens, n_out}, x.options());
   TORCH_CHECK(out.is_contiguous() && out.size(0) == tokens && out.size(1) == n_out &&
@@ -498,6 +506,7 @@ at::Tensor linear(const at::Tensor& x, const at::Tensor& w, const c10::optional<
   a.n_counters = int(s.counters.numel());
   a.err_flag = s.err_flag.data_ptr();
   a.dynamic_weights = dynamic_weights ? 1 : 0;
+  a.weight_tiled = tiled ? 1 : 0;
   if (gate_tokens > 0) BL_CHECK(bl_tp_gate(ctx_or_throw(), gate_tokens, &a, err, errlen));
   if (trace) {
     TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == at::kLong && trace->numel() >= 8 * 296,
@@ -514,15 +523,32 @@ at::Tensor linear(const at::Tensor& x, const at::Tensor& w, const c10::optional<
 
 int gemm_splits(int n, int k, int tokens) { return bl_gemm_splits(n, k, tokens); }
 
+// [n, k] bf16 -> flat buffer of 16 KiB tiles in the swizzled shared-memory image
+at::Tensor tile_weight(const at::Tensor& w) {
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.stride(1) == 1,
+              "barlink: tile_weight needs a 2-D bfloat16 CUDA tensor with unit inner stride");
+  const int n = int(w.size(0)), k = int(w.size(1));
+  at::Tensor out = at::empty({int64_t(bl_tiled_weight_bytes(n, k) / 2)}, w.options());
+  c10::cuda::CUDAGuard guard(w.device());
+  BL_CHECK(bl_tile_weight(w.data_ptr(), n, k, int(w.stride(0)), out.data_ptr(), stream_of(w), err, errlen));
+  return out;
+}
+
 // Split-K linear without a reduction: returns fp32 slabs [splits, tokens, n] that
 // the next kernel (rmsnorm / rope_kv_write / the fused all-reduce) sums as it reads.
 at::Tensor linear_partial(const at::Tensor& x, const at::Tensor& w, int splits,
-                          c10::optional<at::Tensor> out_opt, int gate_tokens) {
+                          c10::optional<at::Tensor> out_opt, int gate_tokens, int tiled_n, int tiled_k) {
   check_bf16(w, "weight");
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
               "barlink: x must be a 2-D bfloat16 CUDA tensor with unit inner stride");
-  TORCH_CHECK(w.dim() == 2 && w.size(1) == x.size(1), "barlink: weight must be [n, k] with k = x.shape[1]");
-  const int tokens = int(x.size(0)), k = int(x.size(1)), n = int(w.size(0));
+  const bool tiled = tiled_n > 0;
+  if (tiled) {
+    TORCH_CHECK(tiled_k == x.size(1) && size_t(w.nbytes()) >= bl_tiled_weight_bytes(tiled_n, tiled_k),
+                "barlink: tiled weight buffer does not match (n, k)");
+  } else {
+    TORCH_CHECK(w.dim() == 2 && w.size(1) == x.size(1), "barlink: weight must be [n, k] with k = x.shape[1]");
+  }
+  const int tokens = int(x.size(0)), k = int(x.size(1)), n = tiled ? tiled_n : int(w.size(0));
   TORCH_CHECK(tokens >= 1 && tokens <= 256, "barlink: linear_partial is the decode path (1..256 tokens)");
   if (splits <= 0) splits = bl_gemm_splits(n, k, tokens);
   at::Tensor out = out_opt ? *out_opt
@@ -545,6 +571,7 @@ at::Tensor linear_partial(const at::Tensor& x, const at::Tensor& w, int splits,
   a.partial_splits = splits;
   a.splits = splits;
   a.err_flag = s.err_flag.data_ptr();
+  a.weight_tiled = tiled ? 1 : 0;
   if (gate_tokens > 0) BL_CHECK(bl_tp_gate(ctx_or_throw(), gate_tokens, &a, err, errlen));
   void* st = at::cuda::getCurrentCUDAStream(dev).stream();
   {
@@ -558,13 +585,17 @@ at::Tensor linear_partial(const at::Tensor& x, const at::Tensor& w, int splits,
 // straight into the inbox of each token's owner (inbox: fp32 arena tensor of
 // world*splits*tokens/world*n elements at the same offset on every rank).
 // Returns (units, splits) for tp_rs_finish.
-std::tuple<int, int> tp_gemm_rs(const at::Tensor& x, const at::Tensor& w, const at::Tensor& inbox) {
+std::tuple<int, int> tp_gemm_rs(const at::Tensor& x, const at::Tensor& w, const at::Tensor& inbox,
+                                int tiled_n, int tiled_k) {
   blCtx* c = ctx_or_throw();
   check_bf16(w, "weight");
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
               "barlink: x must be a 2-D bfloat16 CUDA tensor with unit inner stride");
-  TORCH_CHECK(w.dim() == 2 && w.size(1) == x.size(1), "barlink: weight must be [n, k_local]");
-  const int tokens = int(x.size(0)), k = int(x.size(1)), n = int(w.size(0));
+  const bool tiled = tiled_n > 0;
+  if (!tiled) {
+    TORCH_CHECK(w.dim() == 2 && w.size(1) == x.size(1), "barlink: weight must be [n, k_local]");
+  }
+  const int tokens = int(x.size(0)), k = int(x.size(1)), n = tiled ? tiled_n : int(w.size(0));
   TORCH_CHECK(tokens <= 256, "barlink: the fused reduce-scatter linear is the decode path (<= 256 tokens)");
   int splits = 1;
   const int units = bl_tp_units(n, k, tokens, &splits);
@@ -585,6 +616,7 @@ std::tuple<int, int> tp_gemm_rs(const at::Tensor& x, const at::Tensor& w, const 
   a.ldo = n;
   a.swap = 1;
   a.peer = &ps;
+  a.weight_tiled = tiled ? 1 : 0;
   a.partial_splits = splits;
   a.splits = splits;
   a.err_flag = s.err_flag.data_ptr();
@@ -890,7 +922,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("linear", &linear, py::arg("x"), py::arg("weight"), py::arg("bias") = py::none(),
         py::arg("residual") = py::none(), py::arg("silu_mul") = false, py::arg("out") = py::none(),
         py::arg("force_swap") = -1, py::arg("bn") = 0, py::arg("splits") = 0,
-        py::arg("dynamic_weights") = false, py::arg("trace") = py::none(), py::arg("gate_tokens") = 0);
+        py::arg("dynamic_weights") = false, py::arg("trace") = py::none(), py::arg("gate_tokens") = 0,
+        py::arg("tiled_n") = 0, py::arg("tiled_k") = 0);
   m.def("gemm_error_flag", &gemm_error_flag, py::arg("device") = 0);
   m.def("rmsnorm", &rmsnorm, py::arg("x"), py::arg("gamma"), py::arg("eps"),
         py::arg("residual") = py::none(), py::arg("out") = py::none());
@@ -900,8 +933,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("block_size") = 16, py::arg("theta") = 1e6, py::arg("bias") = py::none(),
         py::arg("out") = py::none());
   m.def("linear_partial", &linear_partial, py::arg("x"), py::arg("weight"), py::arg("splits") = 0,
-        py::arg("out") = py::none(), py::arg("gate_tokens") = 0);
-  m.def("tp_gemm_rs", &tp_gemm_rs, py::arg("x"), py::arg("weight"), py::arg("inbox"));
+        py::arg("out") = py::none(), py::arg("gate_tokens") = 0, py::arg("tiled_n") = 0,
+        py::arg("tiled_k") = 0);
+  m.def("tile_weight", &tile_weight, py::arg("weight"));
+  m.def("tp_gemm_rs", &tp_gemm_rs, py::arg("x"), py::arg("weight"), py::arg("inbox"),
+        py::arg("tiled_n") = 0, py::arg("tiled_k") = 0);
   m.def("tp_rs_finish", &tp_rs_finish, py::arg("inbox"), py::arg("gather"), py::arg("residual"),
         py::arg("gamma"), py::arg("eps"), py::arg("tokens"), py::arg("splits"), py::arg("units"),
         py::arg("add_residual") = true);

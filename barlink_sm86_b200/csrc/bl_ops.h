@@ -76,9 +76,18 @@ typedef struct blGemmArgs {
   unsigned gate_add;
   int gate_n;
   unsigned long long gate_timeout_ns;
+  /* the weight operand (A when swap, else B) is a buffer made by bl_tile_weight
+   * (lda/ldb of that operand are ignored) */
+  int weight_tiled;
   void* trace; /* debug: u64[8 * grid] global-timer stamps per CTA, or null */
 } blGemmArgs;
 int bl_gemm_bf16(const blGemmArgs* a, void* stream, char* err, size_t errlen);
+/* Weights in 16 KiB tiles [ceil(n/128)][ceil(k/64)][128 x 128 B], each tile in the
+ * swizzled shared-memory image: one bulk copy per tile instead of 128 row requests.
+ * dst must be 16-byte aligned and bl_tiled_weight_bytes(n, k) long. */
+size_t bl_tiled_weight_bytes(int n, int k);
+int bl_tile_weight(const void* src, int n, int k, int ld, void* dst, void* stream, char* err,
+                   size_t errlen);
 /* k-splits the decode heuristic picks for n output features, k inputs and
  * `tokens` rows (1 = no split) */
 int bl_gemm_splits(int n, int k, int tokens);

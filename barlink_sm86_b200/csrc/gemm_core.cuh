@@ -47,6 +47,12 @@ struct GemmShape {
   uint32_t* counters;       // [tiles] arrival counters, zero between launches
   uint32_t* err;            // set to 1 when a wait inside the kernel ran out
   unsigned long long* trace; // debug: 8 global-timer stamps per CTA, or nullptr
+  // Pre-tiled weights: the weight matrix is stored as [row block of 128][k block of 64]
+  // tiles of 16 KiB, each already in the swizzled shared-memory image, so a tile is
+  // ONE bulk copy instead of 128 row requests.  0 = none, 1 = operand A, 2 = operand B.
+  int tiled;
+  const uint8_t* tiled_base;
+  int tiled_kblocks;        // k blocks per row block in the tiled matrix
   // All-gather fused in front of the GEMM: the activation operand lives in this
   // rank's arena and peers store their rows into it.  Before the first
   // activation tile is requested, each of gate_n flag words must have reached
@@ -68,17 +74,25 @@ struct GemmSmem {
   static constexpr int kStageA = kTileA * kTileK * 2;
   static constexpr int kStageB = BN * kTileK * 2;
   static constexpr int kStageRaw = W8 ? kTileA * kTileK : 0;
-  static constexpr int kStageBytes = kStageA + kStageB + kStageRaw;
-  static constexpr int kTxBytes = (W8 ? kStageRaw : kStageA) + kStageB;  // bytes TMA delivers per stage
-  static constexpr int kThreads = kGemmThreads + (W8 ? 128 : 0);
+  // bf16: a stage is [A 16 KiB][B]; W8: a stage is [B][raw int8 A 8 KiB] and the
+  // widened A tiles live in a short ring of their own behind the stages, so
+  // that many raw stages (= bytes in flight from HBM) fit
+  static constexpr int kStageBytes = W8 ? kStageB + kStageRaw : kStageA + kStageB;
+  static constexpr int kOffB = W8 ? 0 : kStageA;
+  static constexpr int kOffRaw = kStageB;
+  static constexpr int kA16Stages = W8 ? 3 : 0;
+  static constexpr int kTxBytes = kStageBytes;  // bytes TMA delivers per stage
+  static constexpr int kConvThreads = W8 ? 256 : 0;
+  static constexpr int kThreads = kGemmThreads + kConvThreads;
   // narrow tiles (decode): 4 stages so that two CTAs share an SM -- the same
   // bytes in flight per SM, but a CTA of the next kernel can move in and
   // prefetch weights while one of this kernel is still in its epilogue
-  static constexpr int kStages = W8 ? (BN <= 64 ? 6 : 4) : (CPS == 2) ? 4 : (BN <= 64 ? 8 : (BN <= 128 ? 6 : 4));
+  static constexpr int kStages = W8 ? (BN <= 16 ? 16 : BN <= 32 ? 14 : BN <= 64 ? 10 : BN <= 128 ? 7 : 4)
+                                    : (CPS == 2) ? 4 : (BN <= 64 ? 8 : (BN <= 128 ? 6 : 4));
   static constexpr int kCtasPerSm = CPS;
   static constexpr int kBarBytes = 1024;
   // + 1024 so that the tile ring can be aligned to the swizzle atom
-  static constexpr int kBytes = kStages * kStageBytes + kBarBytes + 1024;
+  static constexpr int kBytes = kStages * kStageBytes + kA16Stages * kStageA + kBarBytes + 1024;
   static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
 };
 
@@ -111,8 +125,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
   uint64_t* empty_bar = full_bar + S::kStages;
   uint64_t* tfull_bar = empty_bar + S::kStages;
   uint64_t* tempty_bar = tfull_bar + 2;
-  uint64_t* ready_bar = tempty_bar + 2;  // W8: stage widened to bf16
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ready_bar + S::kStages);
+  uint64_t* ready_bar = tempty_bar + 2;  // W8: a widened A tile is ready / free again
+  uint64_t* afree_bar = ready_bar + 4;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(afree_bar + 4);
   volatile uint32_t* s_abort = tmem_slot + 1;
   uint32_t* s_last = tmem_slot + 2;
   const uint32_t ring = (smem_u32(smem_raw) + S::kBarBytes + 1023u) & ~1023u;
@@ -127,11 +142,42 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
   const int units = tiles * g.splits;
   const int kb_per = (g.kblocks + g.splits - 1) / g.splits;
 
+  // operand loads of one stage: 2-D tensor copies, or bulk copies of pre-tiled weights
+  auto load_a = [&](uint32_t dst, uint32_t bar, int kb, int ta) {
+    if (!W8 && g.tiled == 1)
+      bulk_load_s(dst, g.tiled_base + (size_t(ta) * g.tiled_kblocks + kb) * S::kStageA, S::kStageA, bar,
+                  hint_a);
+    else
+      tma_load_2d_hint_s(dst, tmap_a, bar, kb * kTileK, ta * kTileA, hint_a);
+  };
+  auto load_b = [&](uint32_t dst, uint32_t bar, int kb, int tb) {
+    if (!W8 && g.tiled == 2) {
+      if constexpr (BN <= kTileA) {
+        const int r0 = tb * BN;
+        bulk_load_s(dst,
+                    g.tiled_base + (size_t(r0 / kTileA) * g.tiled_kblocks + kb) * S::kStageA +
+                        size_t(r0 % kTileA) * 128,
+                    BN * 128, bar, hint_b);
+      } else {
+#pragma unroll
+        for (int h = 0; h < BN / kTileA; ++h)
+          bulk_load_s(dst + h * S::kStageA,
+                      g.tiled_base + (size_t(tb * (BN / kTileA) + h) * g.tiled_kblocks + kb) * S::kStageA,
+                      S::kStageA, bar, hint_b);
+      }
+    } else {
+      tma_load_2d_hint_s(dst, tmap_b, bar, kb * kTileK, tb * BN, hint_b);
+    }
+  };
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
-      mbar_init(&ready_bar[s], 128);
+    }
+    for (int s = 0; s < 4; ++s) {
+      mbar_init(&ready_bar[s], S::kConvThreads > 0 ? S::kConvThreads : 1);
+      mbar_init(&afree_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
@@ -169,11 +215,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
           mbar_expect_tx(&full_bar[pre], S::kTxBytes);
           const uint32_t sa = ring + pre * S::kStageBytes;
           if (g.weights_in_a)
-            tma_load_2d_hint_s(sa + (W8 ? S::kStageA + S::kStageB : 0), tmap_a,
-                               smem_u32(&full_bar[pre]), kb * kTileK, ta * kTileA, hint_a);
+            load_a(sa + (W8 ? S::kOffRaw : 0), smem_u32(&full_bar[pre]), kb, ta);
           else
-            tma_load_2d_hint_s(sa + S::kStageA, tmap_b, smem_u32(&full_bar[pre]), kb * kTileK,
-                               tb * BN, hint_b);
+            load_b(sa + S::kOffB, smem_u32(&full_bar[pre]), kb, tb);
         }
       }
       pdl_wait();
@@ -224,11 +268,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
             mbar_expect_tx(&full_bar[stage], S::kTxBytes);
           }
           if (!early || !g.weights_in_a)
-            tma_load_2d_hint_s(sa + (W8 ? S::kStageA + S::kStageB : 0), tmap_a,
-                               smem_u32(&full_bar[stage]), kb * kTileK, ta * kTileA, hint_a);
+            load_a(sa + (W8 ? S::kOffRaw : 0), smem_u32(&full_bar[stage]), kb, ta);
           if (!early || g.weights_in_a)
-            tma_load_2d_hint_s(sa + S::kStageA, tmap_b, smem_u32(&full_bar[stage]), kb * kTileK,
-                               tb * BN, hint_b);
+            load_b(sa + S::kOffB, smem_u32(&full_bar[stage]), kb, tb);
           ++armed;
           if (++stage == S::kStages) {
             stage = 0;
@@ -256,8 +298,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
     // ------------------------------ MMA issuer ----------------------------
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_f16(kTileA, BN, g.ab_fmt);
-      int stage = 0;
-      uint32_t phase = 0;
+      int stage = 0, astage = 0;
+      uint32_t phase = 0, aphase = 0;
       uint32_t tphase[2] = {0, 0};
       int it = 0;
       bool ok = true;
@@ -271,15 +313,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait_bounded(W8 ? &ready_bar[stage] : &full_bar[stage], phase, s_abort)) {
+          if (!mbar_wait_bounded(W8 ? &ready_bar[astage] : &full_bar[stage], W8 ? aphase : phase,
+                                 s_abort)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
           if (tr && kb == kb0 && it == 0) tr[3] = globaltimer_ns();
           const uint32_t sa = ring + stage * S::kStageBytes;
-          const uint64_t da = umma_desc_k_sw128(sa);
-          const uint64_t db = umma_desc_k_sw128(sa + S::kStageA);
+          const uint64_t da =
+              umma_desc_k_sw128(W8 ? ring + S::kStages * S::kStageBytes + astage * S::kStageA : sa);
+          const uint64_t db = umma_desc_k_sw128(sa + S::kOffB);
 #pragma unroll
           for (int k = 0; k < kTileK / 16; ++k) {
             // +32 bytes along K inside the swizzle atom = +2 in the address field
@@ -287,6 +331,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
                         (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);
+          if (W8) {
+            umma_commit(&afree_bar[astage]);
+            if (++astage == S::kA16Stages) {
+              astage = 0;
+              aphase ^= 1u;
+            }
+          }
           if (++stage == S::kStages) {
             stage = 0;
             phase ^= 1u;
@@ -297,10 +348,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
     }
   } else if (W8 && warp >= 6) {
     // ------------------------ int8 -> bf16 widening -----------------------
-    // thread = tile row: 64 int8 in, 8 swizzled 16-byte chunks of bf16 out
-    const int row = threadIdx.x - kGemmThreads;
-    int stage = 0;
-    uint32_t phase = 0;
+    // two threads per tile row: 32 int8 in, 4 swizzled 16-byte chunks of bf16 out
+    const int ct = threadIdx.x - kGemmThreads;
+    const int row = ct >> 1, half = ct & 1;
+    int stage = 0, astage = 0;
+    uint32_t phase = 0, aphase = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
       const int tile = u / g.splits, sp = u - tile * g.splits;
@@ -308,15 +360,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
       const int kb1 = min(g.kblocks, kb0 + kb_per);
       (void)tile;
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait_bounded(&full_bar[stage], phase, s_abort)) {
+        if (!mbar_wait_bounded(&full_bar[stage], phase, s_abort) ||
+            !mbar_wait_bounded(&afree_bar[astage], aphase ^ 1u, s_abort)) {
           ok = false;
           break;
         }
-        const uint32_t sa = ring + stage * S::kStageBytes;
-        const uint32_t src = sa + S::kStageA + S::kStageB + row * kTileK;
-        const uint32_t dst = sa + row * 128;
+        const uint32_t src = ring + stage * S::kStageBytes + S::kOffRaw + row * kTileK + half * 32;
+        const uint32_t dst = ring + S::kStages * S::kStageBytes + astage * S::kStageA + row * 128;
 #pragma unroll
-        for (int qd = 0; qd < 4; ++qd) {
+        for (int qd = 0; qd < 2; ++qd) {
           uint32_t w0, w1, w2, w3;
           asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                        : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
@@ -326,7 +378,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
           s8x4_to_bf16x4(w1, o2, o3);
           s8x4_to_bf16x4(w2, o4, o5);
           s8x4_to_bf16x4(w3, o6, o7);
-          const int c0 = qd * 2, c1 = qd * 2 + 1;
+          const int c0 = half * 4 + qd * 2, c1 = c0 + 1;
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + (((c0 ^ (row & 7))) << 4)),
                        "r"(o0), "r"(o1), "r"(o2), "r"(o3)
                        : "memory");
@@ -335,7 +387,11 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
                        : "memory");
         }
         fence_proxy_async_smem();  // the tensor core reads what these threads just wrote
-        mbar_arrive(&ready_bar[stage]);
+        mbar_arrive(&ready_bar[astage]);
+        if (++astage == S::kA16Stages) {
+          astage = 0;
+          aphase ^= 1u;
+        }
         if (++stage == S::kStages) {
           stage = 0;
           phase ^= 1u;

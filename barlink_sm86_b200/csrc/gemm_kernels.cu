@@ -252,6 +252,34 @@ __global__ void __launch_bounds__(kGemmThreads, CPS)
   gemm_body<BN, CPS, false>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
 }
 
+// Re-layout of a weight matrix [n x k] (row pitch ld) into 16 KiB tiles
+// [ceil(n/128)][ceil(k/64)][128 rows x 128 bytes], each tile in the 128-byte
+// swizzled shared-memory image (16-byte chunk c of row r sits at chunk c ^ (r & 7)).
+// Rows and columns beyond the matrix are zero.
+__global__ void k_tile_weight(const __nv_bfloat16* __restrict__ src, uint4* __restrict__ dst, int n, int k,
+                              int ld, int tkb, size_t total_chunks) {
+  for (size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x; t < total_chunks;
+       t += size_t(gridDim.x) * blockDim.x) {
+    const size_t tile = t >> 10;           // 1024 chunks per tile
+    const int in_tile = int(t & 1023);
+    const int r = in_tile >> 3, cpos = in_tile & 7;
+    const int c = cpos ^ (r & 7);          // logical chunk stored at this position
+    const int rb = int(tile / tkb), kb = int(tile % tkb);
+    const int row = rb * 128 + r, col = kb * 64 + c * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < n && col < k) {
+      if (col + 8 <= k && ((size_t(row) * ld + col) & 7) == 0) {
+        v = *reinterpret_cast<const uint4*>(src + size_t(row) * ld + col);
+      } else {
+        __nv_bfloat16 tmp[8];
+        for (int j = 0; j < 8; ++j) tmp[j] = col + j < k ? src[size_t(row) * ld + col + j] : __float2bfloat16(0.f);
+        v = *reinterpret_cast<uint4*>(tmp);
+      }
+    }
+    dst[t] = v;
+  }
+}
+
 // ---------------------------------------------------------------------------
 // tensor map cache
 // ---------------------------------------------------------------------------
@@ -363,8 +391,12 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
                        size_t errlen) {
   using S = GemmSmem<BN, CPS>;
   CUtensorMap ta, tb;
-  if (make_tmap_kmajor(a.a, a.ra, a.k, a.lda, kTileA, 2, &ta, err, errlen) != 0) return -1;
-  if (make_tmap_kmajor(a.b, a.rb, a.k, a.ldb, BN, 2, &tb, err, errlen) != 0) return -1;
+  // a pre-tiled weight operand needs no tensor map (the other operand's map stands in)
+  const bool a_tiled = a.weight_tiled && a.swap, b_tiled = a.weight_tiled && !a.swap;
+  if (!b_tiled && make_tmap_kmajor(a.b, a.rb, a.k, a.ldb, BN, 2, &tb, err, errlen) != 0) return -1;
+  if (!a_tiled && make_tmap_kmajor(a.a, a.ra, a.k, a.lda, kTileA, 2, &ta, err, errlen) != 0) return -1;
+  if (a_tiled) ta = tb;
+  if (b_tiled) tb = ta;
   GemmShape g;
   g.ra = a.ra;
   g.rb = a.rb;
@@ -395,6 +427,9 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
     if (!a.ws || a.ws_bytes < need || !a.counters || a.n_counters < tiles) g.splits = 1;
   }
   g.direct = 0;
+  g.tiled = a_tiled ? 1 : b_tiled ? 2 : 0;
+  g.tiled_base = static_cast<const uint8_t*>(a_tiled ? a.a : a.b);
+  g.tiled_kblocks = (a.k + kTileK - 1) / kTileK;
   g.gate_flags = static_cast<const uint32_t*>(a.gate_flags);
   g.gate_cum = static_cast<uint32_t*>(a.gate_cum);
   g.gate_ticket = static_cast<uint32_t*>(a.gate_ticket);
@@ -665,6 +700,30 @@ extern "C" int bl_w8_dequant(const void* wq, const void* scale, void* out, int n
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_err(err, errlen, "barlink: w8_dequant launch failed: %s", cudaGetErrorString(e));
+    return -1;
+  }
+  return 0;
+}
+
+extern "C" size_t bl_tiled_weight_bytes(int n, int k) {
+  return size_t((n + kTileA - 1) / kTileA) * size_t((k + kTileK - 1) / kTileK) * (kTileA * kTileK * 2);
+}
+
+extern "C" int bl_tile_weight(const void* src, int n, int k, int ld, void* dst, void* stream, char* err,
+                              size_t errlen) {
+  if (!src || !dst || n < 1 || k < 1 || (reinterpret_cast<uintptr_t>(dst) & 15u)) {
+    set_err(err, errlen, "barlink: tile_weight needs a source, and a destination aligned to 16 bytes");
+    return -1;
+  }
+  const int tkb = (k + kTileK - 1) / kTileK;
+  const size_t chunks = bl_tiled_weight_bytes(n, k) / 16;
+  size_t blocks = (chunks + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  k_tile_weight<<<unsigned(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(src), static_cast<uint4*>(dst), n, k, ld, tkb, chunks);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_err(err, errlen, "barlink: tile_weight launch failed: %s", cudaGetErrorString(e));
     return -1;
   }
   return 0;

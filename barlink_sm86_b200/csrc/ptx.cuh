@@ -199,6 +199,16 @@ __device__ __forceinline__ void tma_load_2d_hint_s(uint32_t smem_dst, const void
       "l"(tmap), "r"(bar), "r"(x), "r"(y), "l"(hint)
       : "memory");
 }
+// untiled bulk copy global -> this CTA's shared memory (16-byte aligned both
+// sides, size a multiple of 16); completes on the mbarrier like a tensor copy
+__device__ __forceinline__ void bulk_load_s(uint32_t smem_dst, const void* gsrc, uint32_t bytes,
+                                            uint32_t bar, uint64_t hint) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1], %2, [%3], %4;" ::"r"(smem_dst),
+      "l"(gsrc), "r"(bytes), "r"(bar), "l"(hint)
+      : "memory");
+}
 // createpolicy-equivalent constants (the encodings CUTLASS ships as
 // TMA::CacheHintSm90): stream weights through L2, keep activations.
 constexpr uint64_t kHintEvictFirst = 0x12F0000000000000ull;

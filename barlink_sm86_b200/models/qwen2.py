@@ -67,8 +67,13 @@ class Qwen2Weights:
     """Per-rank shards of a seeded random-init model."""
 
     def __init__(self, cfg: Qwen2Config, tp: int, rank: int, device, dtype, seed: int = 0,
-                 layers: Optional[int] = None):
+                 layers: Optional[int] = None, tiled: Optional[bool] = None):
         self.cfg, self.tp, self.rank = cfg, tp, rank
+        if tiled is None:
+            import os
+            tiled = (torch.device(device).type == "cuda" and dtype == torch.bfloat16
+                     and os.environ.get("BL_TILED_WEIGHTS", "0") == "1")
+        self.tiled = tiled
         H, hd = cfg.hidden, cfg.head_dim
         self.plan = head_plan(cfg.n_heads, cfg.n_kv_heads, tp, rank)
         n_layers = cfg.layers if layers is None else layers
@@ -109,6 +114,8 @@ class Qwen2Weights:
                                                     device=device)], 1)
             wdown = shard_cols(down, tp, rank)
             del down
+            if tiled:
+                wqkv, wo, wgu, wdown = (ops.tile_weight(t) for t in (wqkv, wo, wgu, wdown))
             self.layers.append(dict(
                 wqkv=wqkv, bqkv=bqkv, wo=wo, wgu=wgu, wdown=wdown,
                 ln1=torch.ones(H, dtype=dtype, device=device),
@@ -121,6 +128,8 @@ class Qwen2Weights:
         self.vocab_local = vocab_pad // tp
         self.lm_head = shard_rows(head, tp, rank)
         del head
+        if tiled:
+            self.lm_head = ops.tile_weight(self.lm_head)
         self.ln_f = torch.ones(H, dtype=dtype, device=device)
 
     def nbytes(self):
@@ -303,12 +312,12 @@ class Qwen2Model:
             a = ops.paged_attn_decode(qkv, cache.k[li], cache.v[li], cache.block_tables, ctx_lens,
                                       nq, nkv, hd, self.scale, splits)
             ops._count(2)
-            units, S = C.tp_gemm_rs(a, L["wo"], inbox)
+            units, S = C.tp_gemm_rs(a, *ops._w(L["wo"])[:1], inbox, *ops._w(L["wo"])[1:])
             C.tp_rs_finish(inbox, gather, res, L["ln2"], cfg.eps, T, S, units)
             act = ops.linear(gather, L["wgu"], silu_mul=True, gate_tokens=T)
             nxt = w.layers[li + 1]["ln1"] if li + 1 < len(w.layers) else w.ln_f
             ops._count(2)
-            units, S = C.tp_gemm_rs(act, L["wdown"], inbox)
+            units, S = C.tp_gemm_rs(act, *ops._w(L["wdown"])[:1], inbox, *ops._w(L["wdown"])[1:])
             C.tp_rs_finish(inbox, gather, res, nxt, cfg.eps, T, S, units)
             x, gate = gather, T
             c.ar_calls += 2

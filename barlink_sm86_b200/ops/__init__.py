@@ -26,13 +26,50 @@ def _count(n=1):
     launch_count += n
 
 
+class TiledWeight:
+    """A linear layer's weight [n, k] stored as 16 KiB tiles in the layout the
+    tensor core reads from shared memory, so that the GEMM fetches a tile with
+    one bulk copy.  Built once at load with `tile_weight`."""
+
+    __slots__ = ("data", "n", "k")
+
+    def __init__(self, data, n, k):
+        self.data, self.n, self.k = data, n, k
+
+    @property
+    def shape(self):
+        return (self.n, self.k)
+
+    def numel(self):
+        return self.data.numel()
+
+    def element_size(self):
+        return self.data.element_size()
+
+
+def tile_weight(weight):
+    """[n, k] bf16 CUDA tensor -> TiledWeight (other tensors are returned as is)."""
+    if isinstance(weight, TiledWeight) or not weight.is_cuda or weight.dtype != torch.bfloat16:
+        return weight
+    n, k = weight.shape
+    return TiledWeight(_C().tile_weight(weight.contiguous()), n, k)
+
+
+def _w(weight):
+    if isinstance(weight, TiledWeight):
+        return weight.data, weight.n, weight.k
+    return weight, 0, 0
+
+
 def linear(x, weight, bias=None, residual=None, silu_mul=False, out=None, gate_tokens=0):
     """gate_tokens > 0: x is the all-gather buffer of the fused tensor-parallel
     path; the kernel waits for the peers' rows before it reads x."""
     if x.is_cuda:
         _count()
         x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
-        y = _C().linear(x2, weight, bias, residual, silu_mul, out, gate_tokens=gate_tokens)
+        w, tn, tk = _w(weight)
+        y = _C().linear(x2, w, bias, residual, silu_mul, out, gate_tokens=gate_tokens, tiled_n=tn,
+                        tiled_k=tk)
         return y if x.dim() == 2 else y.view(*x.shape[:-1], y.shape[-1])
     return ref.linear(x, weight, bias, residual, silu_mul)
 
@@ -47,7 +84,8 @@ def linear_split(x, weight, gate_tokens=0):
         splits = C.gemm_splits(weight.shape[0], weight.shape[1], x.shape[0])
         if splits > 1:
             _count()
-            return C.linear_partial(x, weight, splits, None, gate_tokens)
+            w, tn, tk = _w(weight)
+            return C.linear_partial(x, w, splits, None, gate_tokens, tn, tk)
     return linear(x, weight, gate_tokens=gate_tokens)
 
 
@@ -127,6 +165,6 @@ def w8a16_linear(x, wq, scale, bias=None, silu_mul=False):
 
 
 __all__ = [
-    "linear", "rmsnorm", "rope_kv_write", "rope", "silu_mul", "embedding", "argmax",
+    "linear", "linear_split", "TiledWeight", "tile_weight", "rmsnorm", "rope_kv_write", "rope", "silu_mul", "embedding", "argmax",
     "paged_attn_decode", "attention", "w8a16_linear", "ref",
 ]

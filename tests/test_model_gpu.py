@@ -26,9 +26,9 @@ def test_prefill_logits_match_fp32_cpu_model(ext):
     for Lc, Lg in zip(cpu.w.layers, gpu.w.layers):
         for k in Lc:
             if Lc[k] is not None:
-                Lc[k].copy_(Lg[k].float().cpu())
+                Lc[k].copy_(gpu.w.dense(Lg[k]).float().cpu())
     cpu.w.embed.copy_(gpu.w.embed.float().cpu())
-    cpu.w.lm_head.copy_(gpu.w.lm_head.float().cpu())
+    cpu.w.lm_head.copy_(gpu.w.dense(gpu.w.lm_head).float().cpu())
     lg = gpu.logits(gpu.prefill(ids.cuda())).float().cpu()
     lc = cpu.logits(cpu.prefill(ids))
     assert rel_l2(lg, lc) < 3e-2
