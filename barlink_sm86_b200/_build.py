@@ -22,6 +22,7 @@ SOURCES = [
     "gemm_kernels.cu",
     "ops_kernels.cu",
     "attn_kernels.cu",
+    "attn_tc_kernels.cu",
     "w8a16_kernels.cu",
     "backend.cc",
     "binding.cc",

@@ -451,7 +451,7 @@ at::Tensor linear(const at::Tensor& x, const at::Tensor& w, const c10::optional<
                   const c10::optional<at::Tensor>& residual, bool silu_mul,
                   c10::optional<at::Tensor> out_opt, int force_swap, int bn, int splits,
                   bool dynamic_weights, c10::optional<at::Tensor> trace, int gate_tokens, int tiled_n,
-                  int tiled_k) {
+                  int tiled_k, bool gelu) {
   check_bf16(w, "weight");
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
               "barlink: x must be a 2-D bfloat16 CUDA tensor with unit inner stride");
@@ -498,6 +498,7 @@ at::Tensor linear(const at::Tensor& x, const at::Tensor& w, const c10::optional<
     a.residual = residual->data_ptr();
   }
   a.silu_mul = silu_mul ? 1 : 0;
+  a.gelu = gelu ? 1 : 0;
   a.bn = bn;
   a.splits = splits;
   a.ws = s.ws.data_ptr();
@@ -923,7 +924,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("residual") = py::none(), py::arg("silu_mul") = false, py::arg("out") = py::none(),
         py::arg("force_swap") = -1, py::arg("bn") = 0, py::arg("splits") = 0,
         py::arg("dynamic_weights") = false, py::arg("trace") = py::none(), py::arg("gate_tokens") = 0,
-        py::arg("tiled_n") = 0, py::arg("tiled_k") = 0);
+        py::arg("tiled_n") = 0, py::arg("tiled_k") = 0, py::arg("gelu") = false);
   m.def("gemm_error_flag", &gemm_error_flag, py::arg("device") = 0);
   m.def("rmsnorm", &rmsnorm, py::arg("x"), py::arg("gamma"), py::arg("eps"),
         py::arg("residual") = py::none(), py::arg("out") = py::none());

@@ -105,9 +105,18 @@ void sp_sendrecv(int src, int dst, const at::Tensor& in, const at::Tensor& out) 
 }
 
 // q [T, nq, hd], k / v [Tk, nkv, hd] (token stride free, heads and dims dense)
+at::Tensor& attn_err(int dev) {
+  static std::map<int, at::Tensor> m;
+  auto it = m.find(dev);
+  if (it != m.end()) return it->second;
+  return m.emplace(dev, at::zeros({4}, at::TensorOptions().device(at::kCUDA, dev).dtype(at::kInt))).first->second;
+}
+int attn_error_flag(int dev) { return attn_err(dev).cpu()[0].item<int>(); }
+
+// max_k > 0 (longest key sequence) selects the tcgen05 kernel; BL_ATTN_TC=0 keeps the mma.sync kernel
 at::Tensor attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                     const at::Tensor& cu_q, const at::Tensor& cu_k, int max_q, double scale,
-                    bool causal) {
+                    bool causal, int max_k) {
   auto chk = [](const at::Tensor& t, const char* name) {
     TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 3 && t.stride(2) == 1 &&
                     t.stride(1) == t.size(2),
@@ -124,6 +133,19 @@ at::Tensor attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& 
   at::Tensor out = at::empty({q.size(0), nq, hd}, q.options());
   c10::cuda::CUDAGuard guard(q.device());
   void* st = at::cuda::getCurrentCUDAStream(q.device().index()).stream();
+  static const bool tc_on = [] {
+    const char* e = getenv("BL_ATTN_TC");
+    return !(e && e[0] == '0');
+  }();
+  if (q.size(0) > 0 && tc_on && max_k > 0 && hd == 128) {
+    at::Tensor vt = at::empty({int64_t(bl_attn_tc_scratch_bytes(batch, max_k, nkv) / 2)}, q.options());
+    BL_CHECK(bl_attn_fwd_tc(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), cu_q.data_ptr<int>(),
+                            cu_k.data_ptr<int>(), batch, max_q, max_k, int(q.size(0)), int(k.size(0)), nq, nkv,
+                            hd, int(q.stride(0)), int(k.stride(0)), int(v.stride(0)), nq * hd, float(scale),
+                            causal ? 1 : 0, vt.data_ptr(), attn_err(q.device().index()).data_ptr(), st, err,
+                            errlen));
+    return out;
+  }
   if (q.size(0) > 0)
     BL_CHECK(bl_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
                          cu_q.data_ptr<int>(), cu_k.data_ptr<int>(), batch, max_q, nq, nkv, hd,
@@ -250,9 +272,67 @@ at::Tensor w8a16_gemm(const at::Tensor& xq, const at::Tensor& xs, const at::Tens
   return out;
 }
 
+void qknorm_rope(const at::Tensor& qkv, const c10::optional<at::Tensor>& gq,
+                 const c10::optional<at::Tensor>& gk, const at::Tensor& positions, int heads, double eps,
+                 double theta, int axes) {
+  TORCH_CHECK(qkv.is_cuda() && qkv.scalar_type() == at::kBFloat16 && qkv.dim() == 2 && qkv.stride(1) == 1 &&
+                  qkv.size(1) >= int64_t(2 * heads) * 128,
+              "barlink: qknorm_rope needs a 2-D bfloat16 CUDA tensor whose rows start with the q and k heads");
+  TORCH_CHECK(positions.is_cuda() && positions.scalar_type() == at::kInt && positions.is_contiguous() &&
+                  positions.numel() == qkv.size(0) * axes,
+              "barlink: positions must be int32 [rows, axes]");
+  if (gq) check_bf16x(*gq, "gq");
+  if (gk) check_bf16x(*gk, "gk");
+  c10::cuda::CUDAGuard guard(qkv.device());
+  void* st = at::cuda::getCurrentCUDAStream(qkv.device().index()).stream();
+  if (qkv.size(0) > 0)
+    BL_CHECK(bl_qknorm_rope(qkv.data_ptr(), gq ? gq->data_ptr() : nullptr, gk ? gk->data_ptr() : nullptr,
+                            positions.data_ptr<int>(), int(qkv.size(0)), heads, 128, int(qkv.stride(0)),
+                            float(eps), float(theta), axes, st, err, errlen));
+}
+
+at::Tensor layernorm_modulate(const at::Tensor& x, const at::Tensor& shift, const at::Tensor& scale,
+                              int rows_per_batch, double eps) {
+  check_bf16x(x, "x");
+  TORCH_CHECK(shift.is_cuda() && scale.is_cuda() && shift.scalar_type() == at::kBFloat16 &&
+                  scale.scalar_type() == at::kBFloat16 && shift.dim() == 2 && scale.dim() == 2 &&
+                  shift.stride(1) == 1 && scale.stride(1) == 1 && shift.stride(0) == scale.stride(0),
+              "barlink: shift/scale must be bfloat16 [batch, hidden] views with the same pitch");
+  const int hidden = int(x.size(-1));
+  const int rows = int(x.numel() / hidden);
+  at::Tensor out = at::empty_like(x);
+  c10::cuda::CUDAGuard guard(x.device());
+  void* st = at::cuda::getCurrentCUDAStream(x.device().index()).stream();
+  if (rows > 0)
+    BL_CHECK(bl_layernorm_modulate(x.data_ptr(), shift.data_ptr(), scale.data_ptr(), out.data_ptr(), rows,
+                                   hidden, rows_per_batch, int(shift.stride(0)), float(eps), st, err, errlen));
+  return out;
+}
+
+void gate_residual(const at::Tensor& x, const at::Tensor& y, const at::Tensor& gate, int rows_per_batch) {
+  check_bf16x(x, "x");
+  check_bf16x(y, "y");
+  TORCH_CHECK(gate.is_cuda() && gate.scalar_type() == at::kBFloat16 && gate.dim() == 2 && gate.stride(1) == 1 &&
+                  x.sizes() == y.sizes(),
+              "barlink: gate must be a bfloat16 [batch, hidden] view and y must match x");
+  const int hidden = int(x.size(-1));
+  const int rows = int(x.numel() / hidden);
+  c10::cuda::CUDAGuard guard(x.device());
+  void* st = at::cuda::getCurrentCUDAStream(x.device().index()).stream();
+  if (rows > 0)
+    BL_CHECK(bl_gate_residual(x.data_ptr(), y.data_ptr(), gate.data_ptr(), rows, hidden, rows_per_batch,
+                              int(gate.stride(0)), st, err, errlen));
+}
+
 }  // namespace
 
 void bind_extra(py::module_& m) {
+  m.def("qknorm_rope", &qknorm_rope, py::arg("qkv"), py::arg("gq"), py::arg("gk"), py::arg("positions"),
+        py::arg("heads"), py::arg("eps") = 1e-6, py::arg("theta") = 1e4, py::arg("axes") = 2);
+  m.def("layernorm_modulate", &layernorm_modulate, py::arg("x"), py::arg("shift"), py::arg("scale"),
+        py::arg("rows_per_batch"), py::arg("eps") = 1e-6);
+  m.def("gate_residual", &gate_residual, py::arg("x"), py::arg("y"), py::arg("gate"),
+        py::arg("rows_per_batch"));
   m.def("w8a16_linear", &w8a16_linear, py::arg("x"), py::arg("wq"), py::arg("scale"),
         py::arg("bias") = py::none(), py::arg("silu_mul") = false, py::arg("splits") = 0);
   m.def("w8_error_flag", &w8_error_flag, py::arg("device") = 0);
@@ -260,7 +340,8 @@ void bind_extra(py::module_& m) {
   m.def("w8a16_gemm", &w8a16_gemm, py::arg("xq"), py::arg("xs"), py::arg("wq_t"), py::arg("sw_t"),
         py::arg("N"), py::arg("K"), py::arg("S"));
   m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("cu_q"),
-        py::arg("cu_k"), py::arg("max_q"), py::arg("scale"), py::arg("causal"));
+        py::arg("cu_k"), py::arg("max_q"), py::arg("scale"), py::arg("causal"), py::arg("max_k") = 0);
+  m.def("attn_error_flag", &attn_error_flag, py::arg("device") = 0);
   m.def("sp_collective", &sp_collective, py::arg("kind"), py::arg("ins") = std::vector<at::Tensor>{},
         py::arg("outs") = std::vector<at::Tensor>{}, py::arg("aux_in") = std::vector<at::Tensor>{},
         py::arg("aux_out") = std::vector<at::Tensor>{}, py::arg("gamma") = std::vector<at::Tensor>{},

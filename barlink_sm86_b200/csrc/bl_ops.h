@@ -50,6 +50,7 @@ typedef struct blGemmArgs {
   const void* bias;
   const void* residual;
   int silu_mul;
+  int gelu;            /* tanh-GELU on (acc + bias) */
   int bn;
   int splits;
   void* ws;
@@ -174,6 +175,14 @@ int bl_attn_fwd(const void* q, const void* k, const void* v, void* out, const in
                 const int* cu_k, int batch, int max_q, int nq, int nkv, int hd, int q_stride,
                 int k_stride, int v_stride, int o_stride, float scale, int causal, void* stream,
                 char* err, size_t errlen);
+/* same contract on the tcgen05 tensor cores (head_dim 128).  vt: scratch of
+ * bl_attn_tc_scratch_bytes(); total_q / total_k: rows of q and k; err_flag: a
+ * device word set to 1 if a bounded wait inside the kernel ran out */
+size_t bl_attn_tc_scratch_bytes(int batch, int max_k, int nkv);
+int bl_attn_fwd_tc(const void* q, const void* k, const void* v, void* out, const int* cu_q, const int* cu_k,
+                   int batch, int max_q, int max_k, int total_q, int total_k, int nq, int nkv, int hd,
+                   int q_stride, int k_stride, int v_stride, int o_stride, float scale, int causal, void* vt,
+                   void* err_flag, void* stream, char* err, size_t errlen);
 /* arg max over the last dim of [rows x n] bf16 logits -> idx (int32) and
  * value (fp32); `offset` is added to the index (vocab-parallel shards). */
 int bl_argmax(const void* logits, int rows, int n, int ld, int offset, int* idx, float* val,
@@ -186,6 +195,20 @@ int bl_argmax_merge(const void* pairs, int parts, int rows, int* idx, void* stre
 int bl_decode_advance(int* positions, int* ctx_lens, int* slots, const int* block_tables, int* ids,
                       const int* sampled, int batch, int max_blocks, int block_size, void* stream,
                       char* err, size_t errlen);
+
+/* ---- MMDiT (Flux-style) elementwise kernels --------------------------------- */
+/* per-head RMSNorm of the q and k heads of a fused qkv row (weights gq, gk of
+ * head_dim 128, null = no norm), then RoPE with 1 or 2 position axes */
+int bl_qknorm_rope(void* qkv, const void* gq, const void* gk, const int* positions, int rows, int heads,
+                   int hd, int row_stride, float eps, float theta, int axes, void* stream, char* err,
+                   size_t errlen);
+/* out = LayerNorm(x) * (1 + scale[b]) + shift[b], b = row / rows_per_batch */
+int bl_layernorm_modulate(const void* x, const void* shift, const void* scale, void* out, int rows,
+                          int hidden, int rows_per_batch, int mod_stride, float eps, void* stream,
+                          char* err, size_t errlen);
+/* x += gate[b] * y */
+int bl_gate_residual(void* x, const void* y, const void* gate, int rows, int hidden, int rows_per_batch,
+                     int mod_stride, void* stream, char* err, size_t errlen);
 
 /* ---- fused GEMM + collective (tensor-parallel linears) -------------------
  * Decode with T tokens on `world` ranks, T % world == 0: token m belongs to

@@ -89,6 +89,13 @@ struct LocalSink {
             x[0] += b0.x; x[1] += b0.y; x[2] += b1.x; x[3] += b1.y;
             x[4] += b2.x; x[5] += b2.y; x[6] += b3.x; x[7] += b3.y;
           }
+          if (epi & 8) {
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+              const float u = x[t];
+              x[t] = 0.5f * u * (1.f + tanhf(0.7978845608f * (u + 0.044715f * u * u * u)));
+            }
+          }
           if (epi & 2) {
             const uint4 b = *reinterpret_cast<const uint4*>(rrow + j0 + c);
             const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z),
@@ -107,6 +114,7 @@ struct LocalSink {
           if (c < ncols && n < rb) {
             float x = v[c];
             if (epi & 1) x += __bfloat162float(bias[n]);
+            if (epi & 8) x = 0.5f * x * (1.f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x)));
             if (epi & 2) x += __bfloat162float(rrow[n]);
             orow[n] = __float2bfloat16(x);
           }
@@ -136,6 +144,7 @@ struct LocalSink {
         const int m = j0 + c;
         if (c < ncols && m < rb) {
           float x = v[c] + bv;
+          if (epi & 8) x = 0.5f * x * (1.f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x)));
           if (epi & 2) x += __bfloat162float(residual[size_t(m) * ldo + n]);
           out[size_t(m) * ldo + n] = __float2bfloat16(x);
         }
@@ -506,7 +515,7 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
     sink.ra = a.ra;
     sink.rb = a.rb;
     sink.swap = a.swap;
-    sink.epi = (a.bias ? 1 : 0) | (a.residual ? 2 : 0) | (a.silu_mul ? 4 : 0);
+    sink.epi = (a.bias ? 1 : 0) | (a.residual ? 2 : 0) | (a.silu_mul ? 4 : 0) | (a.gelu ? 8 : 0);
     sink.scale = nullptr;
     static bool attr_set = false;
     if (!attr_set) {

@@ -804,6 +804,162 @@ extern "C" int bl_paged_attn_decode(const void* q, int q_stride, const void* k_c
 }
 
 // ---------------------------------------------------------------------------
+// MMDiT (Flux-style) elementwise kernels
+// ---------------------------------------------------------------------------
+// Per-head RMSNorm of q and k (weights gq, gk over head_dim = 128) followed by
+// RoPE with 1 or 2 position axes, on a fused qkv row [(3*heads) * 128].
+// One warp per (token, head); lane l owns dims l, l+32, l+64, l+96, which are
+// exactly the rotation partners for both axis layouts.
+__global__ void __launch_bounds__(256) k_qknorm_rope(__nv_bfloat16* __restrict__ qkv,
+                                                     const __nv_bfloat16* __restrict__ gq,
+                                                     const __nv_bfloat16* __restrict__ gk,
+                                                     const int* __restrict__ positions, int heads,
+                                                     int row_stride, float eps, float log2_theta,
+                                                     int axes) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x, lane = threadIdx.x & 31;
+  for (int h = (threadIdx.x >> 5) + blockIdx.y * 8; h < 2 * heads; h += 8 * gridDim.y) {
+    __nv_bfloat16* p = qkv + size_t(row) * row_stride + size_t(h) * 128;  // q heads then k heads
+    const __nv_bfloat16* gm = h < heads ? gq : gk;
+    float x[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) x[j] = __bfloat162float(p[lane + 32 * j]);
+    if (gm) {
+      float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+      ss = warp_sum(ss);
+      const float rstd = rsqrtf(ss / 128.f + eps);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        x[j] = __bfloat162float(__float2bfloat16(x[j] * rstd)) * __bfloat162float(gm[lane + 32 * j]);
+    }
+    if (axes == 2) {
+      // dims [0,64): axis 0, pairs (l, l+32); dims [64,128): axis 1, pairs (l+64, l+96)
+      const float inv = exp2f(-log2_theta * (2.f * float(lane) / 64.f));
+#pragma unroll
+      for (int ax = 0; ax < 2; ++ax) {
+        float sn, cs;
+        sincosf(float(positions[row * 2 + ax]) * inv, &sn, &cs);
+        const float a = x[2 * ax], b = x[2 * ax + 1];
+        x[2 * ax] = a * cs - b * sn;
+        x[2 * ax + 1] = b * cs + a * sn;
+      }
+    } else {
+      // pairs (l, l+64) and (l+32, l+96)
+      const float pos = float(positions[row]);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const float inv = exp2f(-log2_theta * (2.f * float(lane + 32 * j) / 128.f));
+        float sn, cs;
+        sincosf(pos * inv, &sn, &cs);
+        const float a = x[j], b = x[j + 2];
+        x[j] = a * cs - b * sn;
+        x[j + 2] = b * cs + a * sn;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) p[lane + 32 * j] = __float2bfloat16(x[j]);
+  }
+}
+
+// out = LayerNorm(x) * (1 + scale[b]) + shift[b]   (no affine weights; b = row / rows_per_batch)
+__global__ void __launch_bounds__(512) k_layernorm_modulate(const uint4* __restrict__ x,
+                                                            const __nv_bfloat16* __restrict__ shift,
+                                                            const __nv_bfloat16* __restrict__ scale,
+                                                            uint4* __restrict__ out, int vpr,
+                                                            int rows_per_batch, int mod_stride,
+                                                            float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float s_a[16], s_b[16];
+  __shared__ float s_mean, s_rstd;
+  const size_t row = blockIdx.x;
+  const int b = int(row / rows_per_batch);
+  float v[kNormMaxVpt][8];
+  float sum = 0.f, sq = 0.f;
+#pragma unroll
+  for (int k = 0; k < kNormMaxVpt; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < vpr) {
+      const uint4 a = x[row * vpr + i];
+      const float2 p0 = unpack_bf16x2(a.x), p1 = unpack_bf16x2(a.y), p2 = unpack_bf16x2(a.z),
+                   p3 = unpack_bf16x2(a.w);
+      const float f[8] = {p0.x, p0.y, p1.x, p1.y, p2.x, p2.y, p3.x, p3.y};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[k][j] = f[j];
+        sum += f[j];
+        sq += f[j] * f[j];
+      }
+    }
+  }
+  sum = warp_sum(sum);
+  sq = warp_sum(sq);
+  if ((threadIdx.x & 31) == 0) {
+    s_a[threadIdx.x >> 5] = sum;
+    s_b[threadIdx.x >> 5] = sq;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float a = threadIdx.x < (blockDim.x >> 5) ? s_a[threadIdx.x] : 0.f;
+    float c = threadIdx.x < (blockDim.x >> 5) ? s_b[threadIdx.x] : 0.f;
+    a = warp_sum(a);
+    c = warp_sum(c);
+    if (threadIdx.x == 0) {
+      const float n = float(vpr * 8);
+      const float mean = a / n;
+      s_mean = mean;
+      s_rstd = rsqrtf(fmaxf(c / n - mean * mean, 0.f) + eps);
+    }
+  }
+  __syncthreads();
+  const float mean = s_mean, rstd = s_rstd;
+#pragma unroll
+  for (int k = 0; k < kNormMaxVpt; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < vpr) {
+      const uint4 sh = *reinterpret_cast<const uint4*>(shift + size_t(b) * mod_stride + i * 8);
+      const uint4 sc = *reinterpret_cast<const uint4*>(scale + size_t(b) * mod_stride + i * 8);
+      const float2 h0 = unpack_bf16x2(sh.x), h1 = unpack_bf16x2(sh.y), h2 = unpack_bf16x2(sh.z),
+                   h3 = unpack_bf16x2(sh.w);
+      const float2 c0 = unpack_bf16x2(sc.x), c1 = unpack_bf16x2(sc.y), c2 = unpack_bf16x2(sc.z),
+                   c3 = unpack_bf16x2(sc.w);
+      const float hs[8] = {h0.x, h0.y, h1.x, h1.y, h2.x, h2.y, h3.x, h3.y};
+      const float cs[8] = {c0.x, c0.y, c1.x, c1.y, c2.x, c2.y, c3.x, c3.y};
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (v[k][j] - mean) * rstd * (1.f + cs[j]) + hs[j];
+      out[row * vpr + i] = make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]),
+                                      pack_bf16x2(o[4], o[5]), pack_bf16x2(o[6], o[7]));
+    }
+  }
+}
+
+// x += gate[b] * y
+__global__ void k_gate_residual(uint4* __restrict__ x, const uint4* __restrict__ y,
+                                const __nv_bfloat16* __restrict__ gate, int vpr, int rows_per_batch,
+                                int mod_stride, size_t total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x; t < total;
+       t += size_t(gridDim.x) * blockDim.x) {
+    const size_t row = t / vpr;
+    const int i = int(t % vpr);
+    const int b = int(row / rows_per_batch);
+    const uint4 a = x[t], c = y[t];
+    const uint4 g = *reinterpret_cast<const uint4*>(gate + size_t(b) * mod_stride + i * 8);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, cw[4] = {c.x, c.y, c.z, c.w}, gw[4] = {g.x, g.y, g.z, g.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 fa = unpack_bf16x2(aw[j]), fc = unpack_bf16x2(cw[j]), fg = unpack_bf16x2(gw[j]);
+      o[j] = pack_bf16x2(fa.x + fg.x * fc.x, fa.y + fg.y * fc.y);
+    }
+    x[t] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // arg max for callers that may not allocate (see bl_noalloc.h)
 // ---------------------------------------------------------------------------
 #include "bl_noalloc.h"
@@ -862,5 +1018,56 @@ extern "C" int bl_argmax_noalloc(const void* logits, int rows, int n, int ld, in
   OPS_LAUNCH_CHECK("argmax_noalloc");
   k_argmax_merge<<<(rows + 127) / 128, 128, 0, st>>>(scratch, kArgmaxChunks, rows, idx, val);
   OPS_LAUNCH_CHECK("argmax_noalloc merge");
+  return 0;
+}
+
+extern "C" int bl_qknorm_rope(void* qkv, const void* gq, const void* gk, const int* positions, int rows,
+                              int heads, int hd, int row_stride, float eps, float theta, int axes,
+                              void* stream, char* err, size_t errlen) {
+  if (hd != 128 || axes < 1 || axes > 2 || rows < 1) {
+    set_err(err, errlen, "barlink: qknorm_rope is built for head_dim 128 and 1 or 2 position axes");
+    return -1;
+  }
+  const int gy = (2 * heads + 7) / 8 < 8 ? (2 * heads + 7) / 8 : 8;
+  launch_k(k_qknorm_rope, dim3(rows, gy), dim3(256), 0, static_cast<cudaStream_t>(stream),
+           static_cast<__nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(gq),
+           static_cast<const __nv_bfloat16*>(gk), positions, heads, row_stride, eps, log2f(theta), axes);
+  OPS_LAUNCH_CHECK("qknorm_rope");
+  return 0;
+}
+
+extern "C" int bl_layernorm_modulate(const void* x, const void* shift, const void* scale, void* out,
+                                     int rows, int hidden, int rows_per_batch, int mod_stride, float eps,
+                                     void* stream, char* err, size_t errlen) {
+  if (rows < 1 || (hidden & 7) || hidden / 8 > 512 * kNormMaxVpt || rows_per_batch < 1 || (mod_stride & 7)) {
+    set_err(err, errlen, "barlink: layernorm_modulate needs hidden %% 8 == 0 (<= %d) and a modulation pitch %% 8 == 0",
+            512 * kNormMaxVpt * 8);
+    return -1;
+  }
+  const int vpr = hidden / 8;
+  int threads = (vpr + 31) / 32 * 32;
+  if (threads > 512) threads = 512;
+  launch_k(k_layernorm_modulate, dim3(rows), dim3(threads), 0, static_cast<cudaStream_t>(stream),
+           static_cast<const uint4*>(x), static_cast<const __nv_bfloat16*>(shift),
+           static_cast<const __nv_bfloat16*>(scale), static_cast<uint4*>(out), vpr, rows_per_batch,
+           mod_stride, eps);
+  OPS_LAUNCH_CHECK("layernorm_modulate");
+  return 0;
+}
+
+extern "C" int bl_gate_residual(void* x, const void* y, const void* gate, int rows, int hidden,
+                                int rows_per_batch, int mod_stride, void* stream, char* err,
+                                size_t errlen) {
+  if (rows < 1 || (hidden & 7) || (mod_stride & 7) || rows_per_batch < 1) {
+    set_err(err, errlen, "barlink: gate_residual needs hidden %% 8 == 0 and a gate pitch %% 8 == 0");
+    return -1;
+  }
+  const size_t total = size_t(rows) * (hidden / 8);
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  launch_k(k_gate_residual, dim3(unsigned(blocks)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+           static_cast<uint4*>(x), static_cast<const uint4*>(y), static_cast<const __nv_bfloat16*>(gate),
+           hidden / 8, rows_per_batch, mod_stride, total);
+  OPS_LAUNCH_CHECK("gate_residual");
   return 0;
 }

@@ -132,6 +132,11 @@ class Qwen2Weights:
             self.lm_head = ops.tile_weight(self.lm_head)
         self.ln_f = torch.ones(H, dtype=dtype, device=device)
 
+    @staticmethod
+    def dense(w):
+        """The plain [n, k] tensor of a weight, whichever way it is stored."""
+        return ops.untile_weight(w)
+
     def nbytes(self):
         n = self.embed.numel() + self.lm_head.numel() + self.ln_f.numel()
         for L in self.layers:
@@ -230,7 +235,7 @@ class Qwen2Model:
                 T = qkv.shape[0]
                 v3 = qkv.view(T, nq + 2 * nkv, hd)
                 o = ops.attention(v3[:, :nq], v3[:, nq:nq + nkv], v3[:, nq + nkv:], cu, cu, seq,
-                                  self.scale, True)
+                                  self.scale, True, max_k=seq)
                 return o.reshape(T, nq * hd)
             return attn
 

@@ -55,23 +55,41 @@ def tile_weight(weight):
     return TiledWeight(_C().tile_weight(weight.contiguous()), n, k)
 
 
+def untile_weight(weight):
+    """TiledWeight -> the plain [n, k] tensor (other tensors are returned as is)."""
+    if not isinstance(weight, TiledWeight):
+        return weight
+    n, k = weight.n, weight.k
+    rt, kb = -(-n // 128), -(-k // 64)
+    t = weight.data[: rt * kb * 8192].view(rt, kb, 128, 8, 8)
+    r = torch.arange(128, device=t.device)[:, None]
+    c = torch.arange(8, device=t.device)[None, :]
+    phys = (c ^ (r & 7))[None, None, :, :, None].expand(rt, kb, 128, 8, 8)  # 16-byte chunk c of row r sits at c ^ (r & 7)
+    return torch.gather(t, 3, phys).permute(0, 2, 1, 3, 4).reshape(rt * 128, kb * 64)[:n, :k].contiguous()
+
+
 def _w(weight):
     if isinstance(weight, TiledWeight):
         return weight.data, weight.n, weight.k
     return weight, 0, 0
 
 
-def linear(x, weight, bias=None, residual=None, silu_mul=False, out=None, gate_tokens=0):
-    """gate_tokens > 0: x is the all-gather buffer of the fused tensor-parallel
+def linear(x, weight, bias=None, residual=None, silu_mul=False, out=None, gate_tokens=0, gelu=False):
+    """y = x @ weight.T (+ bias) (tanh-GELU if `gelu`) (+ residual).
+    gate_tokens > 0: x is the all-gather buffer of the fused tensor-parallel
     path; the kernel waits for the peers' rows before it reads x."""
     if x.is_cuda:
         _count()
         x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
         w, tn, tk = _w(weight)
         y = _C().linear(x2, w, bias, residual, silu_mul, out, gate_tokens=gate_tokens, tiled_n=tn,
-                        tiled_k=tk)
+                        tiled_k=tk, gelu=gelu)
         return y if x.dim() == 2 else y.view(*x.shape[:-1], y.shape[-1])
-    return ref.linear(x, weight, bias, residual, silu_mul)
+    y = ref.linear(x, weight, bias, residual, silu_mul, gelu)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
 
 
 def linear_split(x, weight, gate_tokens=0):
@@ -119,6 +137,35 @@ def rope(x, positions, theta, axes=1):
     return ref.rope(x, positions, theta, axes)
 
 
+def qknorm_rope(qkv, gq, gk, positions, heads, eps=1e-6, theta=1e4, axes=2):
+    """In place on the first 2*heads*128 columns of qkv [rows, width]: per-head
+    RMSNorm of the q and k heads (weights gq, gk; None = no norm), then RoPE
+    with `axes` position coordinates per row (positions int32 [rows, axes])."""
+    if qkv.is_cuda:
+        _count()
+        _C().qknorm_rope(qkv, gq, gk, positions, heads, eps, theta, axes)
+        return qkv
+    return ref.qknorm_rope(qkv, gq, gk, positions, heads, eps, theta, axes)
+
+
+def layernorm_modulate(x, shift, scale, rows_per_batch, eps=1e-6):
+    """LayerNorm(x) * (1 + scale[b]) + shift[b] with b = row // rows_per_batch
+    (adaLN modulation; shift/scale are [batch, hidden] views of one row pitch)."""
+    if x.is_cuda:
+        _count()
+        return _C().layernorm_modulate(x, shift, scale, rows_per_batch, eps)
+    return ref.layernorm_modulate(x, shift, scale, rows_per_batch, eps)
+
+
+def gate_residual(x, y, gate, rows_per_batch):
+    """x += gate[b] * y in place; returns x."""
+    if x.is_cuda:
+        _count()
+        _C().gate_residual(x, y, gate, rows_per_batch)
+        return x
+    return ref.gate_residual(x, y, gate, rows_per_batch)
+
+
 def silu_mul(gate_up, interleaved=False):
     if gate_up.is_cuda:
         _count()
@@ -149,11 +196,13 @@ def paged_attn_decode(qkv, k_cache, v_cache, block_tables, ctx_lens, nq, nkv, hd
     return ref.paged_attn_decode(qkv, k_cache, v_cache, block_tables, ctx_lens, nq, nkv, hd, scale)
 
 
-def attention(q, k, v, cu_q, cu_k, max_q, scale, causal):
-    """Dense attention over packed sequences (prefill, joint attention)."""
+def attention(q, k, v, cu_q, cu_k, max_q, scale, causal, max_k=0):
+    """Dense attention over packed sequences (prefill, joint attention).
+    With max_k (length of the longest key sequence) the tcgen05 kernel runs
+    (V transpose + attention: two launches); without it the mma.sync kernel."""
     if q.is_cuda:
-        _count()
-        return _C().attn_fwd(q, k, v, cu_q, cu_k, max_q, scale, causal)
+        _count(2 if max_k > 0 else 1)
+        return _C().attn_fwd(q, k, v, cu_q, cu_k, max_q, scale, causal, max_k)
     return ref.attention(q, k, v, cu_q, cu_k, scale, causal)
 
 
@@ -165,6 +214,6 @@ def w8a16_linear(x, wq, scale, bias=None, silu_mul=False):
 
 
 __all__ = [
-    "linear", "linear_split", "TiledWeight", "tile_weight", "rmsnorm", "rope_kv_write", "rope", "silu_mul", "embedding", "argmax",
-    "paged_attn_decode", "attention", "w8a16_linear", "ref",
+    "linear", "linear_split", "TiledWeight", "tile_weight", "untile_weight", "rmsnorm", "rope_kv_write", "rope", "silu_mul", "embedding", "argmax",
+    "paged_attn_decode", "attention", "w8a16_linear", "qknorm_rope", "layernorm_modulate", "gate_residual", "ref",
 ]

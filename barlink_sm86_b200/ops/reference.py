@@ -11,12 +11,14 @@ import math
 import torch
 
 
-def linear(x, weight, bias=None, residual=None, silu_mul=False):
-    """y = x @ weight.T (+ bias) (+ residual); silu_mul: rows of `weight` are
+def linear(x, weight, bias=None, residual=None, silu_mul=False, gelu=False):
+    """y = x @ weight.T (+ bias) (tanh-GELU) (+ residual); silu_mul: rows of `weight` are
     interleaved (gate, up) pairs and y = silu(gate) * up has half the columns."""
     y = x.float() @ weight.float().t()
     if bias is not None:
         y = y + bias.float()
+    if gelu:
+        y = torch.nn.functional.gelu(y, approximate="tanh")
     if silu_mul:
         g, u = y[..., 0::2], y[..., 1::2]
         y = torch.nn.functional.silu(g) * u
@@ -59,6 +61,38 @@ def rope(x, positions, theta, axes=1):
         c, s = cos[:, None, :], sin[:, None, :]
         out[..., a * sub:(a + 1) * sub] = torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], -1)
     return out.to(x.dtype)
+
+
+def qknorm_rope(qkv, gq, gk, positions, heads, eps=1e-6, theta=1e4, axes=2):
+    """In place: per-head RMSNorm of the q and k heads at the start of each row
+    of qkv [rows, width] (head_dim 128), then RoPE with `axes` coordinates."""
+    rows = qkv.shape[0]
+    qk = qkv[:, : 2 * heads * 128].reshape(rows, 2 * heads, 128).float()
+    for lo, g in ((0, gq), (heads, gk)):
+        if g is None:
+            continue
+        seg = qk[:, lo:lo + heads]
+        n = (seg * torch.rsqrt(seg.pow(2).mean(-1, keepdim=True) + eps)).to(qkv.dtype).float()
+        qk[:, lo:lo + heads] = n * g.float()
+    rot = rope(qk.to(qkv.dtype), positions, theta, axes)
+    qkv[:, : 2 * heads * 128] = rot.reshape(rows, 2 * heads * 128)
+    return qkv
+
+
+def layernorm_modulate(x, shift, scale, rows_per_batch, eps=1e-6):
+    rows = x.numel() // x.shape[-1]
+    f = x.reshape(rows, -1).float()
+    n = torch.nn.functional.layer_norm(f, (f.shape[-1],), eps=eps)
+    b = torch.arange(rows, device=x.device) // rows_per_batch
+    out = n * (1.0 + scale.float()[b]) + shift.float()[b]
+    return out.to(x.dtype).view_as(x)
+
+
+def gate_residual(x, y, gate, rows_per_batch):
+    rows = x.numel() // x.shape[-1]
+    b = torch.arange(rows, device=x.device) // rows_per_batch
+    x.copy_((x.reshape(rows, -1).float() + gate.float()[b] * y.reshape(rows, -1).float()).to(x.dtype).view_as(x))
+    return x
 
 
 def rope_kv_write(qkv, positions, slots, k_cache, v_cache, nq, nkv, hd, block_size, theta):

@@ -71,6 +71,21 @@ elif mode == "tiny":
     assert err < 1e-4, err
     nt, n1 = tp.next_tokens(tp.prefill(ids)), one.next_tokens(one.prefill(ids))
     assert torch.equal(nt, n1)
+elif mode == "mmdit":
+    from barlink_sm86_b200.models import MMDiTConfig, MMDiTModel, MMDiTWeights, grid_positions
+    from barlink_sm86_b200.parallel import TPComm
+    cfg = MMDiTConfig.tiny()
+    g = torch.Generator().manual_seed(5)
+    img = torch.randn(2, 16, cfg.in_channels, generator=g)
+    txt = torch.randn(2, 8, cfg.txt_dim, generator=g)
+    t = torch.tensor([0.9, 0.3])
+    pos = grid_positions(4, 4, "cpu")
+    tp = MMDiTModel(cfg, MMDiTWeights(cfg, "cpu", torch.float32, 0, world, rank), TPComm(dist.group.WORLD))
+    one = MMDiTModel(cfg, MMDiTWeights(cfg, "cpu", torch.float32, 0), TPComm.single())
+    yt, y1 = tp.forward(img, txt, t, pos), one.forward(img, txt, t, pos)
+    err = ((yt - y1).norm() / y1.norm()).item()
+    print("tiny MMDiT TP=%d rel-L2 vs one rank %.2e" % (world, err))
+    assert err < 1e-4, err
 elif mode == "raise":
     # a rank that raises between steps: the others learn of it on the host
     store = dist.distributed_c10d._get_default_store()

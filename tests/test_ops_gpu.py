@@ -234,6 +234,41 @@ def test_dense_attention_on_fused_qkv_views(ext):
     assert rel_l2(got, want) < 1e-2
 
 
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("nq,nkv", [(4, 1), (6, 2), (3, 3)])
+def test_dense_attention_tensor_core(ext, causal, nq, nkv):
+    """The tcgen05 kernel (selected by max_k) against the fp32 statement:
+    ragged packed sequences, tiles with one or both 128-row halves in use, key
+    counts off the 64-key step, scores large enough to force a rescale."""
+    from barlink_sm86_b200.ops import reference as ref
+    hd = 128
+    lens_q = [70, 1, 129, 64, 300, 513]
+    lens_k = lens_q if causal else [70, 33, 200, 64, 1000, 257]
+    cu_q = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32, device="cuda")
+    cu_k = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32, device="cuda")
+    q = _bf(sum(lens_q), nq, hd, seed=1) * 3
+    k = _bf(sum(lens_k), nkv, hd, seed=2) * 3
+    v = _bf(sum(lens_k), nkv, hd, seed=3)
+    scale = 1.0 / math.sqrt(hd)
+    got = ext.attn_fwd(q, k, v, cu_q, cu_k, max(lens_q), scale, causal, max(lens_k))
+    want = ref.attention(q, k, v, cu_q.cpu(), cu_k.cpu(), scale, causal)
+    assert ext.attn_error_flag(0) == 0
+    assert rel_l2(got, want) < 1e-2
+
+
+def test_dense_attention_tensor_core_on_fused_qkv_views(ext):
+    from barlink_sm86_b200.ops import reference as ref
+    T, nq, nkv, hd = 1200, 4, 4, 128
+    qkv = _bf(T, (nq + 2 * nkv) * hd + 256, seed=4)
+    v3 = qkv[:, : (nq + 2 * nkv) * hd].unflatten(1, (nq + 2 * nkv, hd))
+    cu = torch.tensor([0, 600, 1200], dtype=torch.int32, device="cuda")
+    scale = 1.0 / math.sqrt(hd)
+    got = ext.attn_fwd(v3[:, :nq], v3[:, nq:nq + nkv], v3[:, nq + nkv:], cu, cu, 600, scale, False, 600)
+    want = ref.attention(v3[:, :nq], v3[:, nq:nq + nkv], v3[:, nq + nkv:], cu.cpu(), cu.cpu(), scale, False)
+    assert ext.attn_error_flag(0) == 0
+    assert rel_l2(got, want) < 1e-2
+
+
 @pytest.mark.parametrize("tokens,n,k", [(64, 4608, 3584), (7, 1000, 448), (300, 640, 320), (1024, 1024, 512),
                                         (16, 256, 18944), (200, 300, 200)])
 def test_linear_with_pretiled_weights(ext, tokens, n, k):
@@ -244,6 +279,7 @@ def test_linear_with_pretiled_weights(ext, tokens, n, k):
     x, w = _bf(tokens, k, seed=31), _bf(n, k, seed=32, std=0.05)
     tw = ops.tile_weight(w)
     assert isinstance(tw, ops.TiledWeight) and tw.shape == (n, k)
+    assert torch.equal(ops.untile_weight(tw), w)
     got = ops.linear(x, tw)
     torch.cuda.synchronize()
     assert ext.gemm_error_flag(0) == 0

@@ -53,6 +53,12 @@ def test_tiny_qwen2_tp2_matches_single_rank():
     assert "max abs logit error" in res[0][1]
 
 
+def test_tiny_mmdit_tp2_matches_single_rank():
+    res = _run("mmdit", 2)
+    assert all(rc == 0 for rc, _ in res), "\n".join(o for _, o in res)
+    assert "rel-L2 vs one rank" in res[0][1]
+
+
 def test_rank_that_never_joins_gives_a_timeout_not_a_hang():
     res = _run("late", 2, timeout=120)
     assert res[1][0] == 0          # the absent rank
