@@ -4,7 +4,8 @@
 target of `ncu` captures (see profiles/).  Weights are larger than L2 or
 rotate, launches are few, memory stays within a few GB.
 
-    python bench/gemm/one_kernel.py gate_up|down_slabs|qkv_slabs|lm_head|w8a16|attn_decode|rmsnorm|attn_prefill [reps]
+    python bench/gemm/one_kernel.py gate_up|down_slabs|qkv_slabs|lm_head|w8a16|attn_decode|rmsnorm|attn_prefill|
+                                    attn_joint|attn_joint_small|linear_big [reps]
 """
 import math
 import sys
@@ -67,6 +68,17 @@ elif which == "attn_prefill":
     v3 = qkv.view(nb * S, nq + 2 * nkv, hd)
     cu = torch.arange(0, (nb + 1) * S, S, device=dev, dtype=torch.int32)
     fn = lambda i: C.attn_fwd(v3[:, :nq], v3[:, nq:nq + nkv], v3[:, nq + nkv:], cu, cu, S, 1 / math.sqrt(hd), True)  # noqa: E731
+elif which in ("attn_joint", "attn_joint_small"):
+    # MMDiT joint attention: 24 heads over 4608 tokens (small: 8 heads over 2304)
+    nh, hd, L = (24, 128, 4608) if which == "attn_joint" else (8, 128, 2304)
+    qkv = bf(L, 3 * nh * hd)
+    v3 = qkv.view(L, 3 * nh, hd)
+    cu = torch.tensor([0, L], device=dev, dtype=torch.int32)
+    fn = lambda i: C.attn_fwd(v3[:, :nh], v3[:, nh:2 * nh], v3[:, 2 * nh:], cu, cu, L, 1 / math.sqrt(hd), False, L)  # noqa: E731
+elif which == "linear_big":
+    # MMDiT MLP-in at 4608 tokens: [4608, 3072] x [12288, 3072]^T with bias + GELU
+    x, w, b = bf(4608, 3072), bf(12288, 3072, std=0.02), bf(12288)
+    fn = lambda i: C.linear(x, w, b, None, False, None, gelu=True)  # noqa: E731
 else:
     raise SystemExit("unknown kernel " + which)
 
