@@ -24,6 +24,7 @@ SOURCES = [
     "attn_kernels.cu",
     "attn_tc_kernels.cu",
     "w8a16_kernels.cu",
+    "w4a16_kernels.cu",
     "backend.cc",
     "binding.cc",
     "binding_extra.cc",

@@ -272,6 +272,52 @@ at::Tensor w8a16_gemm(const at::Tensor& xq, const at::Tensor& xs, const at::Tens
   return out;
 }
 
+// GPTQ-v1 int4 linear: 1..16 rows use the GEMV; more rows widen the weight and use the bf16 GEMM
+at::Tensor w4a16_linear(const at::Tensor& x, const at::Tensor& qweight, const at::Tensor& scales,
+                        const at::Tensor& qzeros, int group, int splits) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.is_contiguous(),
+              "barlink: x must be a contiguous 2-D bfloat16 CUDA tensor");
+  TORCH_CHECK(qweight.is_cuda() && qweight.is_contiguous() && qweight.scalar_type() == at::kInt &&
+                  qweight.dim() == 2 && qweight.size(0) * 8 == x.size(1),
+              "barlink: qweight must be a contiguous int32 [K/8, N] CUDA tensor with K = x.shape[1]");
+  const int m = int(x.size(0)), k = int(x.size(1)), n = int(qweight.size(1));
+  TORCH_CHECK(group > 0 && k % group == 0, "barlink: K must be a multiple of the group size");
+  TORCH_CHECK(scales.is_cuda() && scales.is_contiguous() && scales.scalar_type() == at::kHalf &&
+                  scales.dim() == 2 && scales.size(0) == k / group && scales.size(1) == n,
+              "barlink: scales must be a contiguous float16 [K/group, N] CUDA tensor");
+  TORCH_CHECK(qzeros.is_cuda() && qzeros.is_contiguous() && qzeros.scalar_type() == at::kInt &&
+                  qzeros.dim() == 2 && qzeros.size(0) == k / group && qzeros.size(1) * 8 == n,
+              "barlink: qzeros must be a contiguous int32 [K/group, N/8] CUDA tensor");
+  const int dev = x.device().index();
+  c10::cuda::CUDAGuard guard(x.device());
+  void* st = at::cuda::getCurrentCUDAStream(dev).stream();
+  if (m == 0) return at::empty({0, n}, x.options());
+  if (m > 16) {
+    at::Tensor w = at::empty({n, k}, x.options());
+    BL_CHECK(bl_w4_dequant(qweight.data_ptr(), scales.data_ptr(), qzeros.data_ptr(), w.data_ptr(), n, k, group,
+                           st, err, errlen));
+    return at::matmul(x, w.t());  // prefill path, not the decode hot path
+  }
+  W8Scratch& s = w8_scratch(dev);
+  at::Tensor out = at::empty({m, n}, x.options());
+  BL_CHECK(bl_w4a16_gemv(x.data_ptr(), qweight.data_ptr(), scales.data_ptr(), qzeros.data_ptr(), out.data_ptr(),
+                         m, n, k, group, splits, s.ws.data_ptr(), size_t(s.ws.nbytes()), st, err, errlen));
+  return out;
+}
+
+at::Tensor w4_dequant(const at::Tensor& qweight, const at::Tensor& scales, const at::Tensor& qzeros, int group) {
+  TORCH_CHECK(qweight.is_cuda() && qweight.is_contiguous() && qweight.scalar_type() == at::kInt &&
+                  scales.is_cuda() && scales.is_contiguous() && scales.scalar_type() == at::kHalf &&
+                  qzeros.is_cuda() && qzeros.is_contiguous() && qzeros.scalar_type() == at::kInt,
+              "barlink: w4_dequant needs contiguous CUDA qweight (int32), scales (float16), qzeros (int32)");
+  const int k = int(qweight.size(0)) * 8, n = int(qweight.size(1));
+  c10::cuda::CUDAGuard guard(qweight.device());
+  at::Tensor w = at::empty({n, k}, scales.options().dtype(at::kBFloat16));
+  BL_CHECK(bl_w4_dequant(qweight.data_ptr(), scales.data_ptr(), qzeros.data_ptr(), w.data_ptr(), n, k, group,
+                         at::cuda::getCurrentCUDAStream(qweight.device().index()).stream(), err, errlen));
+  return w;
+}
+
 void qknorm_rope(const at::Tensor& qkv, const c10::optional<at::Tensor>& gq,
                  const c10::optional<at::Tensor>& gk, const at::Tensor& positions, int heads, double eps,
                  double theta, int axes) {
@@ -327,6 +373,9 @@ void gate_residual(const at::Tensor& x, const at::Tensor& y, const at::Tensor& g
 }  // namespace
 
 void bind_extra(py::module_& m) {
+  m.def("w4a16_linear", &w4a16_linear, py::arg("x"), py::arg("qweight"), py::arg("scales"), py::arg("qzeros"),
+        py::arg("group") = 128, py::arg("splits") = 0);
+  m.def("w4_dequant", &w4_dequant, py::arg("qweight"), py::arg("scales"), py::arg("qzeros"), py::arg("group") = 128);
   m.def("qknorm_rope", &qknorm_rope, py::arg("qkv"), py::arg("gq"), py::arg("gk"), py::arg("positions"),
         py::arg("heads"), py::arg("eps") = 1e-6, py::arg("theta") = 1e4, py::arg("axes") = 2);
   m.def("layernorm_modulate", &layernorm_modulate, py::arg("x"), py::arg("shift"), py::arg("scale"),

@@ -196,6 +196,16 @@ int bl_decode_advance(int* positions, int* ctx_lens, int* slots, const int* bloc
                       const int* sampled, int batch, int max_blocks, int block_size, void* stream,
                       char* err, size_t errlen);
 
+/* ---- W4A16: GPTQ-v1 int4 weights, bf16 activations -------------------------- */
+/* y[m, n] = sum_k x[m, k] * (nibble(n, k) - zero(g, n)) * scale(g, n); 1..16 rows;
+ * splits <= 0: chosen here; a k-split needs ws of splits*m*n floats.  -2: too many rows */
+int bl_w4a16_gemv(const void* x, const void* qweight, const void* scales, const void* qzeros, void* out,
+                  int m, int n, int k, int group, int splits, void* ws, size_t ws_bytes, void* stream,
+                  char* err, size_t errlen);
+/* packed tensors -> bf16 [n, k] */
+int bl_w4_dequant(const void* qweight, const void* scales, const void* qzeros, void* w, int n, int k,
+                  int group, void* stream, char* err, size_t errlen);
+
 /* ---- MMDiT (Flux-style) elementwise kernels --------------------------------- */
 /* per-head RMSNorm of the q and k heads of a fused qkv row (weights gq, gk of
  * head_dim 128, null = no norm), then RoPE with 1 or 2 position axes */

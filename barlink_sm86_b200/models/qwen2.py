@@ -57,6 +57,59 @@ class Qwen2Config:
                            intermediate=1376, vocab=32000, name="tiny-qwen2")
 
 
+class W8Weight:
+    """int8 weight [n, k] with one bf16 scale per output channel (W8A16)."""
+    __slots__ = ("wq", "scale", "shape")
+
+    def __init__(self, w, scale=None):
+        """scale: per-row scales to use (a row-parallel shard passes the scales
+        of the unsharded rows, so that every shard quantises to the same values
+        as the whole weight); None = from the rows of w."""
+        if scale is None:
+            self.wq, self.scale = ops.ref.quantize_w8(w)
+        else:
+            self.scale = scale
+            self.wq = torch.round(w.float() / scale.float()[:, None]).clamp(-127, 127).to(torch.int8)
+        self.shape = tuple(w.shape)
+
+    def numel(self):
+        return self.wq.numel() // 2 + self.scale.numel()  # in bf16-element units of memory
+
+    def dense(self):
+        return (self.wq.float() * self.scale.float()[:, None]).to(self.scale.dtype)
+
+
+class W4Weight:
+    """GPTQ-v1 int4 weight (group 128): the reference's Int4Linear format
+    (demos/qwen_tp/int4linear.py:5-12)."""
+    __slots__ = ("qw", "sc", "qz", "group", "shape")
+
+    def __init__(self, w, group=128):
+        self.qw, self.sc, self.qz = ops.ref.pack_int4(w, group)
+        self.group, self.shape = group, tuple(w.shape)
+
+    def numel(self):
+        return self.qw.numel() * 2 + self.sc.numel() + self.qz.numel() * 2
+
+    def dense(self):
+        return ops.ref.w4_dequant(self.qw, self.sc, self.qz, self.group).to(torch.bfloat16)
+
+
+def qlinear(x, w, bias=None, silu_mul=False, split=False):
+    """x @ w.T for any stored form of w (plain / tiled bf16, W8Weight, W4Weight).
+    split=True allows the k-split slab output of the bf16 decode GEMM."""
+    if isinstance(w, W8Weight):
+        return ops.w8a16_linear(x, w.wq, w.scale, bias, silu_mul)
+    if isinstance(w, W4Weight):
+        y = ops.w4a16_linear(x, w.qw, w.sc, w.qz, w.group)
+        if bias is not None:
+            y = y + bias
+        return ops.silu_mul(y, interleaved=True) if silu_mul else y
+    if split and bias is None and not silu_mul:
+        return ops.linear_split(x, w)
+    return ops.linear(x, w, bias, silu_mul=silu_mul)
+
+
 def _randn(shape, seed, device, dtype, std=0.02):
     g = torch.Generator(device=device)
     g.manual_seed(seed)
@@ -67,8 +120,16 @@ class Qwen2Weights:
     """Per-rank shards of a seeded random-init model."""
 
     def __init__(self, cfg: Qwen2Config, tp: int, rank: int, device, dtype, seed: int = 0,
-                 layers: Optional[int] = None, tiled: Optional[bool] = None):
+                 layers: Optional[int] = None, tiled: Optional[bool] = None, quant: str = "none"):
+        """quant: "none" (bf16), "w8a16" (every linear int8 per-channel, the
+        reference's INT8 demo, demos/qwen_tp/qwen38_int8/worker.py:97-150) or
+        "w4a16" (MLP int4 group-128, the rest int8: demos/qwen_tp/worker.py:1-25).
+        Quantisation is per output row / per (row, group), so a shard quantises
+        to the same values as the matching rows of the unsharded weight."""
         self.cfg, self.tp, self.rank = cfg, tp, rank
+        if quant not in ("none", "w8a16", "w4a16"):
+            raise ValueError("quant must be none, w8a16 or w4a16")
+        self.quant = quant
         if tiled is None:
             import os
             tiled = (torch.device(device).type == "cuda" and dtype == torch.bfloat16
@@ -79,7 +140,8 @@ class Qwen2Weights:
         n_layers = cfg.layers if layers is None else layers
         self.layers = []
         base = seed * 1000003
-        inter_pad = -(-cfg.intermediate // (tp * 8)) * (tp * 8)  # shards stay 16-byte multiples
+        unit = tp * (128 if quant == "w4a16" else 8)  # shards stay 16-byte multiples (int4: whole groups)
+        inter_pad = -(-cfg.intermediate // unit) * unit
         self.inter_local = inter_pad // tp
         for l in range(n_layers):
             s = base + l * 64
@@ -100,6 +162,7 @@ class Qwen2Weights:
                                   gather_heads(bv[:, None], self.plan.kv_heads, hd)[:, 0]]).contiguous()
             wo_full = _randn((H, cfg.n_heads * hd), s + 7, device, dtype)
             wo = gather_head_cols(wo_full, self.plan.q_heads, hd).contiguous()
+            wo_scale = ops.ref.quantize_w8(wo_full)[1] if quant != "none" else None
             del wo_full
             gate = _randn((cfg.intermediate, H), s + 8, device, dtype)
             up = _randn((cfg.intermediate, H), s + 9, device, dtype)
@@ -113,8 +176,15 @@ class Qwen2Weights:
                 down = torch.cat([down, torch.zeros(H, inter_pad - cfg.intermediate, dtype=dtype,
                                                     device=device)], 1)
             wdown = shard_cols(down, tp, rank)
+            down_scale = ops.ref.quantize_w8(down)[1] if quant == "w8a16" else None
             del down
-            if tiled:
+            if quant != "none":
+                wqkv, wo = W8Weight(wqkv), W8Weight(wo, wo_scale)
+                if quant == "w4a16":
+                    wgu, wdown = W4Weight(wgu), W4Weight(wdown)
+                else:
+                    wgu, wdown = W8Weight(wgu), W8Weight(wdown, down_scale)
+            elif tiled:
                 wqkv, wo, wgu, wdown = (ops.tile_weight(t) for t in (wqkv, wo, wgu, wdown))
             self.layers.append(dict(
                 wqkv=wqkv, bqkv=bqkv, wo=wo, wgu=wgu, wdown=wdown,
@@ -128,13 +198,17 @@ class Qwen2Weights:
         self.vocab_local = vocab_pad // tp
         self.lm_head = shard_rows(head, tp, rank)
         del head
-        if tiled:
+        if quant != "none":
+            self.lm_head = W8Weight(self.lm_head)
+        elif tiled:
             self.lm_head = ops.tile_weight(self.lm_head)
         self.ln_f = torch.ones(H, dtype=dtype, device=device)
 
     @staticmethod
     def dense(w):
         """The plain [n, k] tensor of a weight, whichever way it is stored."""
+        if isinstance(w, (W8Weight, W4Weight)):
+            return w.dense()
         return ops.untile_weight(w)
 
     def nbytes(self):
@@ -169,11 +243,12 @@ class PagedKV:
 
 class Qwen2Model:
     def __init__(self, cfg: Qwen2Config, comm: Optional[TPComm] = None, device="cpu",
-                 dtype=torch.float32, seed=0, layers=None):
+                 dtype=torch.float32, seed=0, layers=None, quant="none"):
         self.cfg = cfg
         self.comm = comm or TPComm(None)
         self.device, self.dtype = torch.device(device), dtype
-        self.w = Qwen2Weights(cfg, self.comm.world, self.comm.rank, self.device, dtype, seed, layers)
+        self.w = Qwen2Weights(cfg, self.comm.world, self.comm.rank, self.device, dtype, seed, layers,
+                              quant=quant)
         self.nq, self.nkv, self.hd = self.w.plan.nq, self.w.plan.nkv, cfg.head_dim
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
 
@@ -189,7 +264,11 @@ class Qwen2Model:
                 normed, res = c.allreduce_rmsnorm(h, res, L["ln1"], cfg.eps)
             else:
                 normed, res = ops.rmsnorm(h, L["ln1"], cfg.eps, res)
-            if split_k:
+            if w.quant != "none":
+                qkv = qlinear(normed, L["wqkv"], L["bqkv"])
+                a = attn_factory(li)(qkv, None)
+                h = qlinear(a, L["wo"])
+            elif split_k:
                 # decode: k-split linears leave fp32 slabs that the next kernel sums
                 qkv = ops.linear_split(normed, L["wqkv"])
                 if qkv.dtype == torch.float32:
@@ -204,8 +283,8 @@ class Qwen2Model:
                 a = attn_factory(li)(qkv, None)
                 h = ops.linear(a, L["wo"])
             normed, res = c.allreduce_rmsnorm(h, res, L["ln2"], cfg.eps)
-            act = ops.linear(normed, L["wgu"], silu_mul=True)
-            h = ops.linear_split(act, L["wdown"]) if split_k else ops.linear(act, L["wdown"])
+            act = qlinear(normed, L["wgu"], silu_mul=True)
+            h = qlinear(act, L["wdown"], split=split_k)
             pending = True
         if pending:
             normed, res = c.allreduce_rmsnorm(h, res, w.ln_f, cfg.eps)
@@ -266,7 +345,8 @@ class Qwen2Model:
         import os
         c = self.comm
         return (c.world > 1 and c.use_link and tokens % c.world == 0 and tokens <= 256
-                and self.device.type == "cuda" and os.environ.get("BL_FUSED_LINEAR", "0") == "1")
+                and self.device.type == "cuda" and self.w.quant == "none"
+                and os.environ.get("BL_FUSED_LINEAR", "0") == "1")
 
     def _fused_buffers(self, tokens):
         key = ("fused", tokens)
@@ -329,7 +409,7 @@ class Qwen2Model:
         return gather, T
 
     def logits_local(self, hidden):
-        return ops.linear(hidden, self.w.lm_head)
+        return qlinear(hidden, self.w.lm_head)
 
     def logits(self, hidden):
         """Full-vocabulary logits (vocab-parallel head + gather)."""

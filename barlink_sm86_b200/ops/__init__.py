@@ -137,6 +137,17 @@ def rope(x, positions, theta, axes=1):
     return ref.rope(x, positions, theta, axes)
 
 
+def w4a16_linear(x, qweight, scales, qzeros, group_size=128):
+    """Weight-only int4 linear on GPTQ-v1 tensors (see `ref.pack_int4`): a
+    hand-written GEMV for 1..16 rows, widen + GEMM above that."""
+    if x.is_cuda:
+        _count(2)
+        x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
+        y = _C().w4a16_linear(x2.contiguous(), qweight, scales, qzeros, group_size)
+        return y if x.dim() == 2 else y.view(*x.shape[:-1], y.shape[-1])
+    return ref.w4a16_linear(x, qweight, scales, qzeros, group_size)
+
+
 def qknorm_rope(qkv, gq, gk, positions, heads, eps=1e-6, theta=1e4, axes=2):
     """In place on the first 2*heads*128 columns of qkv [rows, width]: per-head
     RMSNorm of the q and k heads (weights gq, gk; None = no norm), then RoPE
@@ -215,5 +226,5 @@ def w8a16_linear(x, wq, scale, bias=None, silu_mul=False):
 
 __all__ = [
     "linear", "linear_split", "TiledWeight", "tile_weight", "untile_weight", "rmsnorm", "rope_kv_write", "rope", "silu_mul", "embedding", "argmax",
-    "paged_attn_decode", "attention", "w8a16_linear", "qknorm_rope", "layernorm_modulate", "gate_residual", "ref",
+    "paged_attn_decode", "attention", "w8a16_linear", "w4a16_linear", "qknorm_rope", "layernorm_modulate", "gate_residual", "ref",
 ]

@@ -216,3 +216,39 @@ def allreduce_rmsnorm(parts, residual, gamma, eps):
 
 def default_scale(hd):
     return 1.0 / math.sqrt(hd)
+
+
+def pack_int4(weight, group_size=128):
+    """[n, k] weight -> GPTQ-v1 tensors (qweight int32 [k/8, n], scales fp16
+    [k/group, n], qzeros int32 [k/group, n/8]), symmetric with zero point 8:
+    the format of the reference's Int4Linear (demos/qwen_tp/int4linear.py:47-69)."""
+    w = weight.float()
+    n, k = w.shape
+    assert k % group_size == 0 and n % 8 == 0 and k % 8 == 0
+    groups = k // group_size
+    wg = w.reshape(n, groups, group_size)
+    scale = (wg.abs().amax(2) / 7.0).clamp(min=1e-8).half()            # [n, groups], as stored
+    q = torch.round(wg / scale.float()[..., None] + 8.0).clamp(0, 15).to(torch.int64).reshape(n, k)
+    qk = q.reshape(n, k // 8, 8)
+    qw = sum(qk[..., j] << (4 * j) for j in range(8))
+    qw = ((qw + 2 ** 31) % 2 ** 32 - 2 ** 31).to(torch.int32).t().contiguous()
+    z = torch.full((groups, n // 8, 8), 8, dtype=torch.int64, device=w.device)
+    qz = sum(z[..., j] << (4 * j) for j in range(8))
+    qz = ((qz + 2 ** 31) % 2 ** 32 - 2 ** 31).to(torch.int32).contiguous()
+    return qw, scale.t().contiguous(), qz
+
+
+def w4_dequant(qweight, scales, qzeros, group_size=128):
+    """GPTQ-v1 tensors -> fp32 [n, k]."""
+    k, n = qweight.shape[0] * 8, qweight.shape[1]
+    w = qweight.t().long() & 0xFFFFFFFF
+    nib = torch.stack([(w >> (4 * j)) & 0xF for j in range(8)], 2).reshape(n, k)
+    zz = qzeros.long() & 0xFFFFFFFF
+    z = torch.stack([(zz >> (4 * j)) & 0xF for j in range(8)], 2).reshape(-1, n)     # [groups, n]
+    z = z.repeat_interleave(group_size, 0)[:k].t()
+    sc = scales.float().repeat_interleave(group_size, 0)[:k].t()
+    return (nib - z).float() * sc
+
+
+def w4a16_linear(x, qweight, scales, qzeros, group_size=128):
+    return (x.float() @ w4_dequant(qweight, scales, qzeros, group_size).t()).to(x.dtype)

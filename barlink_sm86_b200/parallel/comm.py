@@ -38,6 +38,10 @@ class TPComm:
         self.max_chunk = load_extension().info()["max_chunk"] if use_link else 0
         self.ar_calls = 0
         self.ar_bytes = 0
+        # timing control of the reference's demos (`--no-comm`,
+        # demos/qwen_tp/qwen38_int8/worker.py:157-183): every collective is
+        # skipped, results are wrong, the step time is compute only
+        self.no_comm = False
 
     @classmethod
     def single(cls):
@@ -45,12 +49,13 @@ class TPComm:
         c = cls.__new__(cls)
         c.group, c.world, c.rank = None, 1, 0
         c.use_link, c.oneshot_max, c.ar_calls, c.ar_bytes, c.max_chunk = False, 0, 0, 0, 0
+        c.no_comm = False
         return c
 
     # ---- collectives -----------------------------------------------------
     def all_reduce(self, x):
         """In-place sum over the group; returns x."""
-        if self.world == 1:
+        if self.world == 1 or self.no_comm:
             return x
         self.ar_calls += 1
         self.ar_bytes += x.numel() * x.element_size()
@@ -103,7 +108,9 @@ class TPComm:
 
         One kernel on the link when the message fits the one-shot inbox;
         otherwise all-reduce followed by the add+norm kernel."""
-        if self.world == 1:
+        if self.world == 1 or self.no_comm:
+            if x.dtype == torch.float32 and x.dim() == 3 and gamma.dtype != torch.float32 and not x.is_cuda:
+                x = x.sum(0).to(gamma.dtype)
             return _ops.rmsnorm(x, gamma, eps, residual)
         slabs = x.dtype == torch.float32 and x.dim() == 3 and gamma.dtype != torch.float32
         nbytes = (x[0].numel() * gamma.element_size()) if slabs else x.numel() * x.element_size()
@@ -125,7 +132,7 @@ class TPComm:
     def argmax_vocab_parallel(self, logits_local, vocab_per_rank):
         """Global arg max over vocab-parallel logits [rows, vocab_per_rank]."""
         idx, val = _ops.argmax(logits_local, self.rank * vocab_per_rank)
-        if self.world == 1:
+        if self.world == 1 or self.no_comm:
             return idx
         pairs = torch.stack([val, idx.view(torch.float32) if idx.dtype == torch.int32 else idx.float()], -1)
         if logits_local.is_cuda and self.use_link:

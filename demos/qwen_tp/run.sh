@@ -1,0 +1,27 @@
+#!/usr/bin/env bash
+# SPDX-License-Identifier: MIT
+# Tensor-parallel decode demo: TP=1, TP=N over the link, TP=N over NCCL (same kernels),
+# the no-communication control, then the comparisons.
+# Usage: run.sh [N] [out-dir] [extra worker flags, e.g. --quant w8a16 --batch 8]
+set -euo pipefail
+HERE="$(cd "$(dirname "$0")" && pwd)"
+N="${1:-2}"
+OUT="${2:-$HERE/results}"
+shift $(( $# > 2 ? 2 : $# ))
+PORT="${PORT:-29551}"
+LIMIT="${LIMIT:-600}"   # seconds per run; a stuck run ends instead of holding the GPUs
+
+run_tp() {  # backend tag [flags]
+  timeout "$LIMIT" python -m torch.distributed.run --nnodes=1 --nproc-per-node "$N" \
+    --master-addr 127.0.0.1 --master-port "$PORT" "$HERE/worker.py" \
+    --backend "$1" --tag "$2" --out "$OUT" "${@:3}"
+}
+
+timeout "$LIMIT" python "$HERE/worker.py" --out "$OUT" --tag tp1 "$@"
+if [ "$N" -gt 1 ]; then
+  run_tp barlink "tp${N}" "$@"
+  run_tp barlink "tp${N}nocomm" --no-comm "$@"
+  NCCL_NVLS_ENABLE="${NCCL_NVLS_ENABLE:-0}" run_tp nccl "tp${N}nccl" "$@"
+  python "$HERE/compare.py" --dir "$OUT" --left-tag tp1 --right-tag "tp${N}" --nocomm-tag "tp${N}nocomm"
+  python "$HERE/compare.py" --dir "$OUT" --left-tag "tp${N}nccl" --right-tag "tp${N}"
+fi

@@ -71,6 +71,17 @@ elif mode == "tiny":
     assert err < 1e-4, err
     nt, n1 = tp.next_tokens(tp.prefill(ids)), one.next_tokens(one.prefill(ids))
     assert torch.equal(nt, n1)
+    # quantised weights: a shard quantises to the same values as the unsharded rows, so TP stays exact;
+    # against the unquantised model the logits only have to stay close
+    for quant in ("w8a16", "w4a16"):
+        qt = Qwen2Model(cfg, TPComm(dist.group.WORLD), "cpu", torch.float32, seed=0, quant=quant)
+        q1 = Qwen2Model(cfg, TPComm.single(), "cpu", torch.float32, seed=0, quant=quant)
+        a, b = qt.logits(qt.prefill(ids[:1, :32])), q1.logits(q1.prefill(ids[:1, :32]))
+        ref_l = one.logits(one.prefill(ids[:1, :32]))
+        err = (a - b).abs().max().item()
+        cos = torch.cosine_similarity(b.flatten(), ref_l.flatten(), dim=0).item()
+        print("tiny %s TP=%d max abs logit error %.2e, cosine vs unquantised %.4f" % (quant, world, err, cos))
+        assert err < 1e-3 and cos > (0.99 if quant == "w8a16" else 0.9), (quant, err, cos)
 elif mode == "mmdit":
     from barlink_sm86_b200.models import MMDiTConfig, MMDiTModel, MMDiTWeights, grid_positions
     from barlink_sm86_b200.parallel import TPComm

@@ -86,6 +86,17 @@ def test_w8_quantisation_round_trip():
     assert (back - w).abs().max() <= s.float().max() * 0.51 + 1e-3
 
 
+def test_int4_pack_round_trip():
+    w = torch.randn(64, 512) * 0.02
+    qw, sc, qz = ref.pack_int4(w, 128)
+    assert qw.shape == (64, 64) and qw.dtype == torch.int32 and sc.shape == (4, 64) and qz.shape == (4, 8)
+    d = ref.w4_dequant(qw, sc, qz, 128)
+    step = sc.float().t().repeat_interleave(128, 1)
+    assert torch.all((d - w).abs() <= 0.5 * step + 1e-6)
+    x = torch.randn(3, 512)
+    assert torch.allclose(ref.w4a16_linear(x, qw, sc, qz), x @ d.t(), atol=1e-5)
+
+
 def test_package_imports_without_a_gpu():
     import barlink_sm86_b200 as bl
     assert callable(bl.init) and callable(bl.allreduce_into) and callable(bl.copy_large)
