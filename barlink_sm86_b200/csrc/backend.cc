@@ -273,6 +273,34 @@ void BarlinkBackend::recv_cuda(at::Tensor& t, int src) {
   if (!direct) t.copy_(dst.narrow(0, 0, t.numel()).view(t.sizes()));
 }
 
+// MAX / MIN / PRODUCT / AVG: the reduce kernels of the link only add, so these
+// (control-plane sized in practice: loss scales, timings, flags) gather every
+// rank's tensor over the link and reduce locally.
+void BarlinkBackend::allreduce_other_cuda(at::Tensor& t, const c10d::ReduceOp& op) {
+  // argument errors surface before any rank has put traffic on the link
+  TORCH_CHECK(op == c10d::ReduceOp::MAX || op == c10d::ReduceOp::MIN || op == c10d::ReduceOp::PRODUCT ||
+                  op == c10d::ReduceOp::AVG,
+              "barlink: all_reduce on CUDA tensors supports SUM, AVG, MAX, MIN and PRODUCT");
+  TORCH_CHECK(t.is_contiguous(), "barlink: all_reduce needs a contiguous tensor");
+  c10::cuda::CUDAGuard guard(t.device());
+  const int64_t n = t.numel();
+  if (n == 0) return;
+  // pad to a 16-byte multiple so that the gather runs zero-copy sized chunks
+  const int64_t esz = int64_t(t.element_size());
+  const int64_t padded = (n * esz + 15) / 16 * 16 / esz;
+  at::Tensor in = at::zeros({padded}, t.options());
+  in.narrow(0, 0, n).copy_(t.view({-1}));
+  at::Tensor all = at::empty({int64_t(getSize()) * padded}, t.options());
+  allgather_cuda(all, in);
+  at::Tensor rows = all.view({int64_t(getSize()), padded}).narrow(1, 0, n);
+  at::Tensor r;
+  if (op == c10d::ReduceOp::MAX) r = rows.amax(0);
+  else if (op == c10d::ReduceOp::MIN) r = rows.amin(0);
+  else if (op == c10d::ReduceOp::PRODUCT) r = rows.prod(0);
+  else r = at::isFloatingType(t.scalar_type()) ? rows.mean(0) : rows.sum(0).floor_divide(int64_t(getSize()));
+  t.view({-1}).copy_(r);
+}
+
 // ---------------------------------------------------------------------------
 
 static void check_sum(const c10d::ReduceOp& op, const char* what) {
@@ -289,9 +317,11 @@ c10::intrusive_ptr<c10d::Work> BarlinkBackend::allreduce(std::vector<at::Tensor>
     return done(c10d::OpType::ALLREDUCE, tensors);
   }
   if (t.is_cuda()) {
-    // argument errors surface before any rank has put traffic on the link
-    check_sum(opts.reduceOp, "all_reduce");
-    allreduce_cuda(t);
+    if (opts.reduceOp == c10d::ReduceOp::SUM) {
+      allreduce_cuda(t);
+    } else {
+      allreduce_other_cuda(t, opts.reduceOp);
+    }
     return done(c10d::OpType::ALLREDUCE, tensors);
   }
   return cpu("all_reduce").allreduce(tensors, opts);

@@ -104,6 +104,7 @@ class BarlinkBackend : public c10d::Backend {
  private:
   c10::intrusive_ptr<c10d::Work> done(c10d::OpType op, std::vector<at::Tensor> outs);
   void allreduce_cuda(at::Tensor& t);
+  void allreduce_other_cuda(at::Tensor& t, const c10d::ReduceOp& op);
   void allgather_cuda(at::Tensor& out, const at::Tensor& in);
   void reduce_scatter_cuda(at::Tensor& out, const at::Tensor& in);
   void broadcast_cuda(at::Tensor& t, int root);

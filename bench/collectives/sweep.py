@@ -5,8 +5,8 @@ reduce-scatter from 4 KiB to 1 GiB in bf16 and fp32, plus the fused
 all-reduce + residual + RMSNorm at hidden 3584 for 1..256 tokens, on the
 barlink link or on NCCL (the reference's A/B arm: bench/latency/nccl_lat.py,
 pg_lat.py, pg_bw.py there).  Every number is timed on the device with CUDA
-events inside a captured graph of `--iters` calls and reported as the maximum
-over ranks; bus bandwidth uses the usual 2(N-1)/N factor for all-reduce and
+events around `--iters` calls (one captured graph on the link; an eager loop
+on NCCL unless --nccl-graph) and reported as the maximum over ranks; bus bandwidth uses the usual 2(N-1)/N factor for all-reduce and
 (N-1)/N for the other two.
 
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
@@ -28,11 +28,13 @@ sys.path.insert(0, ROOT)
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--backend", default="barlink", choices=["barlink", "nccl"])
-    ap.add_argument("--min", type=int, default=4096)
-    ap.add_argument("--max", type=int, default=1 << 30)
+    ap.add_argument("--min-bytes", type=int, default=4096)
+    ap.add_argument("--max-bytes", type=int, default=1 << 30)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--out", default="")
     ap.add_argument("--dtypes", default="bf16,fp32")
+    ap.add_argument("--nccl-graph", action="store_true",
+                    help="time NCCL inside a captured graph too (default: eager loop of --iters calls)")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     lr = int(os.environ.get("LOCAL_RANK", "0"))
@@ -58,6 +60,8 @@ def main():
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         try:
+            if args.backend == "nccl" and not args.nccl_graph:
+                raise RuntimeError("eager")
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 for _ in range(iters):
@@ -87,8 +91,8 @@ def main():
     dts = {"bf16": torch.bfloat16, "fp32": torch.float32}
     for dname in args.dtypes.split(","):
         dt = dts[dname]
-        size = args.min
-        while size <= args.max:
+        size = args.min_bytes
+        while size <= args.max_bytes:
             n = size // (2 if dt == torch.bfloat16 else 4)
             x = torch.randn(n, device=dev).to(dt)
             iters = args.iters if size <= (64 << 20) else max(2, args.iters // 5)

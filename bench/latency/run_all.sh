@@ -5,7 +5,8 @@
 set -u
 N="${1:-2}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
-RUN="python -m torch.distributed.run --nnodes=1 --nproc-per-node $N --master-addr 127.0.0.1"
+LIMIT="${LIMIT:-180}"   # seconds per program: a stuck run ends instead of holding the GPUs
+RUN="timeout $LIMIT python -m torch.distributed.run --nnodes=1 --nproc-per-node $N --master-addr 127.0.0.1"
 $RUN --master-port 29601 "$HERE/link_lat.py"
 for B in barlink nccl; do
   $RUN --master-port 29602 "$HERE/pg_lat.py" --backend $B

@@ -21,7 +21,12 @@ timeout "$LIMIT" python "$HERE/worker.py" --out "$OUT" --tag tp1 "$@"
 if [ "$N" -gt 1 ]; then
   run_tp barlink "tp${N}" "$@"
   run_tp barlink "tp${N}nocomm" --no-comm "$@"
-  NCCL_NVLS_ENABLE="${NCCL_NVLS_ENABLE:-0}" run_tp nccl "tp${N}nccl" "$@"
+  # the NCCL arm is a baseline: its failure must not hide the link's results
+  NCCL_NVLS_ENABLE="${NCCL_NVLS_ENABLE:-0}" run_tp nccl "tp${N}nccl" "$@" > "$OUT/tp${N}nccl.log" 2>&1 \
+    || echo "NCCL arm exited non-zero (see $OUT/tp${N}nccl.log)"
+  grep -E "^\[tp" "$OUT/tp${N}nccl.log" || true
   python "$HERE/compare.py" --dir "$OUT" --left-tag tp1 --right-tag "tp${N}" --nocomm-tag "tp${N}nocomm"
-  python "$HERE/compare.py" --dir "$OUT" --left-tag "tp${N}nccl" --right-tag "tp${N}"
+  if [ -f "$OUT/stats_tp${N}nccl.json" ]; then
+    python "$HERE/compare.py" --dir "$OUT" --left-tag "tp${N}nccl" --right-tag "tp${N}"
+  fi
 fi

@@ -145,6 +145,9 @@ def main():
                        "allreduce_calls_timed": comm.ar_calls - ar0, "peak_mem_gib": mem,
                        "weight_gib": model.w.nbytes() / (1 << 30), "link": link_stats()}, f, indent=2)
     if world > 1:
+        # captured graphs hold references to the communicator's kernels: drop them first
+        del eng
+        sync()
         dist.barrier()
         dist.destroy_process_group()
 

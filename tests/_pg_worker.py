@@ -224,7 +224,15 @@ for it in range(10):
 log("graph replay ok")
 
 # ---- argument errors come before any traffic ------------------------------------------------
-for bad in (lambda: dist.all_reduce(torch.ones(4, device=dev), op=dist.ReduceOp.MIN),
+for op, want_fn in ((dist.ReduceOp.MAX, lambda v: max(v)), (dist.ReduceOp.MIN, lambda v: min(v)),
+                    (dist.ReduceOp.AVG, lambda v: sum(v) / len(v)), (dist.ReduceOp.PRODUCT, None)):
+    # non-SUM ops: gathered over the link and reduced locally (odd length: exercises the padding)
+    t = torch.full((5,), float(rank + 2), device=dev)
+    dist.all_reduce(t, op=op)
+    vals = [float(r + 2) for r in range(world)]
+    want = want_fn(vals) if want_fn else float(torch.tensor(vals).prod())
+    assert torch.allclose(t, torch.full_like(t, want)), (op, t, want)
+for bad in (lambda: dist.all_reduce(torch.ones(4, dtype=torch.int32, device=dev), op=dist.ReduceOp.BAND),
             lambda: dist.all_reduce(torch.ones(4, dtype=torch.int64, device=dev)),
             lambda: dist.send(torch.ones(4, device=dev), rank)):
     try:
