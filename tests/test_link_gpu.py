@@ -1,7 +1,10 @@
 # SPDX-License-Identifier: MIT
-"""The N-rank collective protocols on ONE GPU: four ranks share device 0 and
-every collective runs as one cooperative kernel over all ranks' data, which
-is how protocols that wait on peers may be exercised without several GPUs."""
+"""The N-rank collective protocols on ONE GPU: four ranks (BL_TEST_WORLD, up
+to 8) share device 0 and every collective runs as one cooperative kernel over
+all ranks' data, which is how protocols that wait on peers may be exercised
+without several GPUs."""
+import os
+
 import pytest
 import torch
 
@@ -9,7 +12,7 @@ from conftest import rel_l2
 
 pytestmark = pytest.mark.gpu
 
-WORLD = 4
+WORLD = int(os.environ.get("BL_TEST_WORLD", "4"))
 
 
 @pytest.fixture(scope="module")
