@@ -767,6 +767,18 @@ void rope(const at::Tensor& x, const at::Tensor& positions, int heads, int hd, d
 }
 
 at::Tensor silu_mul(const at::Tensor& gate_up, bool interleaved) {
+  if (gate_up.scalar_type() == at::kFloat && gate_up.dim() == 3) {
+    // k-split slabs [split][rows][2*inter] of the gate/up linear (interleaved columns)
+    TORCH_CHECK(gate_up.is_cuda() && gate_up.is_contiguous() && interleaved && gate_up.size(2) % 8 == 0,
+                "barlink: silu_mul over slabs needs contiguous float32 CUDA slabs with interleaved gate/up columns");
+    const int rows = int(gate_up.size(1)), inter = int(gate_up.size(2) / 2);
+    at::Tensor out = at::empty({rows, inter}, gate_up.options().dtype(at::kBFloat16));
+    c10::cuda::CUDAGuard guard(gate_up.device());
+    if (rows > 0)
+      BL_CHECK(bl_silu_mul_slabs(gate_up.data_ptr(), int(gate_up.size(0)), out.data_ptr(), rows, inter,
+                                 stream_of(gate_up), err, errlen));
+    return out;
+  }
   check_bf16(gate_up, "gate_up");
   const int two = int(gate_up.size(-1));
   TORCH_CHECK(two % 2 == 0, "barlink: silu_mul needs an even last dim");

@@ -156,6 +156,9 @@ int bl_rope(void* x, const int* positions, int rows, int heads, int hd, int row_
             int axes, void* stream, char* err, size_t errlen);
 int bl_silu_mul(const void* gate_up, void* out, int rows, int inter, int interleaved, void* stream,
                 char* err, size_t errlen);
+/* slabs: fp32 [nsplit][rows][2*inter], interleaved (gate, up) columns; out bf16 [rows][inter] */
+int bl_silu_mul_slabs(const void* slabs, int nsplit, void* out, int rows, int inter, void* stream, char* err,
+                      size_t errlen);
 int bl_embedding(const int* ids, const void* table, void* out, int rows, int hidden, int vocab_lo,
                  int vocab_hi, void* stream, char* err, size_t errlen);
 /* Decode attention over a paged KV cache.  q rows live in qkv (pitch

@@ -322,6 +322,12 @@ __global__ void k_barrier(CollArgs a) {
 template <int DT, bool kNorm>
 __global__ void __launch_bounds__(kThreads) k_lamport(CollArgs a) {
   using E = Elem<DT>;
+  // Launched as a programmatic dependent in peer mode: the kernel after this
+  // one (a GEMM) may become resident now and stream its first weight tiles
+  // while this kernel waits for the peers; this kernel itself reads nothing
+  // before its predecessors have completed.
+  pdl_launch_dependents();
+  pdl_wait();
   const Comm& c = comm_of(a.pack);
   const int y = a.pack.emu ? blockIdx.y : 0;
   const int rank = c.rank, world = c.world;
@@ -1075,7 +1081,7 @@ static int check_health(blCtx* ctx, char* err, size_t errlen) {
 
 template <typename K>
 static int launch_local(blCtx* ctx, K kernel, CollArgs base, const PerRank* pr, int grid_x,
-                        int threads, char* err, size_t errlen, bool join_sends = true) {
+                        int threads, char* err, size_t errlen, bool join_sends = true, bool pdl = false) {
   if (ctx->peer_mode) {
     // collectives are ordered after every send issued so far
     if (join_sends && ctx->send_pending) {
@@ -1095,7 +1101,14 @@ static int launch_local(blCtx* ctx, K kernel, CollArgs base, const PerRank* pr, 
     a.aux_in[0] = pr[0].aux_in;
     a.aux_out[0] = pr[0].aux_out;
     a.gamma[0] = pr[0].gamma;
-    kernel<<<dim3(grid_x, 1, 1), threads, 0, static_cast<cudaStream_t>(pr[0].stream)>>>(a);
+    if (pdl) {
+      // only for kernels that execute griddepcontrol.wait before their first read
+      RT_TRY(launch_k(kernel, dim3(grid_x, 1, 1), dim3(threads, 1, 1), 0,
+                      static_cast<cudaStream_t>(pr[0].stream), a),
+             "collective launch");
+    } else {
+      kernel<<<dim3(grid_x, 1, 1), threads, 0, static_cast<cudaStream_t>(pr[0].stream)>>>(a);
+    }
     RT_TRY(cudaGetLastError(), "collective launch");
     return 0;
   }
@@ -1237,7 +1250,7 @@ static int allreduce_local(blCtx* ctx, const PerRank* pr, size_t bytes, int dtyp
       if constexpr (DT == BL_DTYPE_U8 || DT == BL_DTYPE_FP64) {
         return -1;
       } else {
-        return launch_local(ctx, k_lamport<DT, false>, a, pr, grid, kThreads, err, errlen);
+        return launch_local(ctx, k_lamport<DT, false>, a, pr, grid, kThreads, err, errlen, true, true);
       }
     });
     ctx->stats[BL_STAT_ONESHOT]++;
@@ -1494,13 +1507,13 @@ static int norm_local(blCtx* ctx, const PerRank* pr, int rows, int hidden, float
   if (threads < 64) threads = 64;
   switch (dtype) {
     case BL_DTYPE_BF16:
-      rc = launch_local(ctx, k_lamport<BL_DTYPE_BF16, true>, a, pr, grid, threads, err, errlen);
+      rc = launch_local(ctx, k_lamport<BL_DTYPE_BF16, true>, a, pr, grid, threads, err, errlen, true, true);
       break;
     case BL_DTYPE_FP16:
-      rc = launch_local(ctx, k_lamport<BL_DTYPE_FP16, true>, a, pr, grid, threads, err, errlen);
+      rc = launch_local(ctx, k_lamport<BL_DTYPE_FP16, true>, a, pr, grid, threads, err, errlen, true, true);
       break;
     default:
-      rc = launch_local(ctx, k_lamport<BL_DTYPE_FP32, true>, a, pr, grid, threads, err, errlen);
+      rc = launch_local(ctx, k_lamport<BL_DTYPE_FP32, true>, a, pr, grid, threads, err, errlen, true, true);
   }
   ctx->stats[BL_STAT_OPS]++;
   ctx->stats[BL_STAT_FUSED_NORM]++;

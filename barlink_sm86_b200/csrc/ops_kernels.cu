@@ -239,6 +239,26 @@ __global__ void k_silu_mul(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* 
   }
 }
 
+// Same on the fp32 k-split slabs [split][row][2*inter] of the gate/up linear
+// (interleaved gate/up columns): sums the slabs while reading, 4 outputs per thread.
+__global__ void k_silu_mul_slabs(const float* __restrict__ slabs, size_t slab_stride, int nsplit,
+                                 __nv_bfloat16* __restrict__ out, size_t total4) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t t = size_t(blockIdx.x) * blockDim.x + threadIdx.x; t < total4;
+       t += size_t(gridDim.x) * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    sum_slabs8(slabs + t * 8, slab_stride, nsplit, acc);
+    float o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float g = acc[2 * j], u = acc[2 * j + 1];
+      o[j] = g / (1.f + __expf(-g)) * u;
+    }
+    *reinterpret_cast<uint2*>(out + t * 4) = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
+  }
+}
+
 __global__ void k_embedding(const int* __restrict__ ids, const uint4* __restrict__ table,
                             uint4* __restrict__ out, int vpr, int lo, int hi) {
   pdl_launch_dependents();
@@ -697,6 +717,22 @@ extern "C" int bl_silu_mul(const void* gate_up, void* out, int rows, int inter, 
       static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), rows, inter,
       interleaved);
   OPS_LAUNCH_CHECK("silu_mul");
+  return 0;
+}
+
+extern "C" int bl_silu_mul_slabs(const void* slabs, int nsplit, void* out, int rows, int inter, void* stream,
+                                 char* err, size_t errlen) {
+  if (nsplit < 1 || rows < 1 || (inter & 3)) {
+    set_err(err, errlen, "barlink: silu_mul over slabs needs inter %% 4 == 0");
+    return -1;
+  }
+  const size_t total4 = size_t(rows) * inter / 4;
+  size_t grid = (total4 + 255) / 256;
+  if (grid > 148 * 8) grid = 148 * 8;
+  launch_k(k_silu_mul_slabs, dim3(unsigned(grid)), dim3(256), 0, static_cast<cudaStream_t>(stream),
+           static_cast<const float*>(slabs), size_t(rows) * 2 * inter, nsplit,
+           static_cast<__nv_bfloat16*>(out), total4);
+  OPS_LAUNCH_CHECK("silu_mul_slabs");
   return 0;
 }
 

@@ -243,12 +243,15 @@ class PagedKV:
 
 class Qwen2Model:
     def __init__(self, cfg: Qwen2Config, comm: Optional[TPComm] = None, device="cpu",
-                 dtype=torch.float32, seed=0, layers=None, quant="none"):
+                 dtype=torch.float32, seed=0, layers=None, quant="none", shard_of=None):
+        """shard_of=(tp, rank): hold that rank's shard of a tp-way split while
+        running alone (collectives are no-ops, results are partial sums): the
+        per-rank compute of a larger tensor-parallel job, for tuning on one GPU."""
         self.cfg = cfg
         self.comm = comm or TPComm(None)
         self.device, self.dtype = torch.device(device), dtype
-        self.w = Qwen2Weights(cfg, self.comm.world, self.comm.rank, self.device, dtype, seed, layers,
-                              quant=quant)
+        tp, rank = shard_of if shard_of is not None else (self.comm.world, self.comm.rank)
+        self.w = Qwen2Weights(cfg, tp, rank, self.device, dtype, seed, layers, quant=quant)
         self.nq, self.nkv, self.hd = self.w.plan.nq, self.w.plan.nkv, cfg.head_dim
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
 
@@ -283,7 +286,12 @@ class Qwen2Model:
                 a = attn_factory(li)(qkv, None)
                 h = ops.linear(a, L["wo"])
             normed, res = c.allreduce_rmsnorm(h, res, L["ln2"], cfg.eps)
-            act = qlinear(normed, L["wgu"], silu_mul=True)
+            if split_k and w.quant == "none" and ops.k_splits(normed, L["wgu"]) > 1:
+                # a gate/up shard with few row tiles fills the SMs only with a k-split;
+                # SiLU*mul then runs over the slabs (one small kernel) instead of in the epilogue
+                act = ops.silu_mul(ops.linear_split(normed, L["wgu"]), interleaved=True)
+            else:
+                act = qlinear(normed, L["wgu"], silu_mul=True)
             h = qlinear(act, L["wdown"], split=split_k)
             pending = True
         if pending:

@@ -92,6 +92,13 @@ def linear(x, weight, bias=None, residual=None, silu_mul=False, out=None, gate_t
     return y
 
 
+def k_splits(x, weight):
+    """Number of k-splits `linear_split` would use for this call (1: none)."""
+    if x.is_cuda and x.dim() == 2 and x.shape[0] <= 128:
+        return _C().gemm_splits(weight.shape[0], weight.shape[1], x.shape[0])
+    return 1
+
+
 def linear_split(x, weight, gate_tokens=0):
     """Decode-path linear: when the shape wants a k-split, returns fp32 slabs
     [splits, tokens, n] whose sum is x @ weight.T (the consumer -- `rmsnorm`,
@@ -225,6 +232,6 @@ def w8a16_linear(x, wq, scale, bias=None, silu_mul=False):
 
 
 __all__ = [
-    "linear", "linear_split", "TiledWeight", "tile_weight", "untile_weight", "rmsnorm", "rope_kv_write", "rope", "silu_mul", "embedding", "argmax",
+    "linear", "linear_split", "k_splits", "TiledWeight", "tile_weight", "untile_weight", "rmsnorm", "rope_kv_write", "rope", "silu_mul", "embedding", "argmax",
     "paged_attn_decode", "attention", "w8a16_linear", "w4a16_linear", "qknorm_rope", "layernorm_modulate", "gate_residual", "ref",
 ]

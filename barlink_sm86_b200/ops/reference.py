@@ -113,6 +113,9 @@ def rope_kv_write(qkv, positions, slots, k_cache, v_cache, nq, nkv, hd, block_si
 
 
 def silu_mul(gate_up, interleaved=False):
+    if gate_up.dtype == torch.float32 and gate_up.dim() == 3:  # k-split slabs: summed first
+        g, u = gate_up.sum(0)[..., 0::2], gate_up.sum(0)[..., 1::2]
+        return (torch.nn.functional.silu(g) * u).to(torch.bfloat16)
     f = gate_up.float()
     if interleaved:
         g, u = f[..., 0::2], f[..., 1::2]

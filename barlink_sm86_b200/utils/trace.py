@@ -78,7 +78,7 @@ class OpTrace:
         from ..parallel import comm as comm_mod
         for name in ops.__all__:
             fn = getattr(ops, name, None)
-            if callable(fn) and not isinstance(fn, type) and name not in ("tile_weight", "untile_weight"):
+            if callable(fn) and not isinstance(fn, type) and name not in ("tile_weight", "untile_weight", "k_splits"):
                 self._saved.append((ops, name, fn))
                 setattr(ops, name, self._wrap(name, fn))
         for name in _COMM_METHODS:

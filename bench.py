@@ -42,6 +42,8 @@ def parse():
     p.add_argument("--batch", type=int, default=64)
     p.add_argument("--prompt", type=int, default=1024)
     p.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the result invalid)")
+    p.add_argument("--shard-of", type=int, default=0,
+                   help="debug only: one GPU holds rank 0's shard of this TP degree, no communication (invalid result)")
     p.add_argument("--prefill", default="real", choices=["real", "synthetic"],
                    help="real: run the 1024-token prompts through the model; synthetic: random KV")
     p.add_argument("--no-graph", action="store_true")
@@ -92,7 +94,8 @@ def main():
     cfg = Qwen2Config.qwen25_7b()
     n_layers = args.layers if args.layers > 0 else None
     t0 = time.time()
-    model = Qwen2Model(cfg, comm, dev, torch.bfloat16, seed=0, layers=n_layers)
+    model = Qwen2Model(cfg, comm, dev, torch.bfloat16, seed=0, layers=n_layers,
+                       shard_of=(args.shard_of, 0) if args.shard_of > 1 and world == 1 else None)
     torch.cuda.synchronize()
     load_s = time.time() - t0
 
@@ -177,7 +180,9 @@ def main():
             "impl": "barlink",
             "config": {
                 "model": cfg.name + (" TRUNCATED to %d layers (invalid for comparison)" % args.layers
-                                     if args.layers else ""),
+                                     if args.layers else "")
+                + (" ONE SHARD of tp%d without communication (invalid for comparison)" % args.shard_of
+                   if args.shard_of > 1 else ""),
                 "hidden": cfg.hidden, "layers": len(model.w.layers), "heads": cfg.n_heads,
                 "kv_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim,
                 "intermediate": cfg.intermediate, "vocab": cfg.vocab,

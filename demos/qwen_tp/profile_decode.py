@@ -23,11 +23,13 @@ ap.add_argument("--quant", default="none", choices=["none", "w8a16", "w4a16"])
 ap.add_argument("--batch", type=int, default=64)
 ap.add_argument("--ctx", type=int, default=1024)
 ap.add_argument("--steps", type=int, default=3)
+ap.add_argument("--shard-of", type=int, default=0, help="profile rank 0's shard of this TP degree (no communication)")
 a = ap.parse_args()
 cuda = torch.cuda.is_available()
 dev, dt = ("cuda:0", torch.bfloat16) if cuda else ("cpu", torch.float32)
 cfg = Qwen2Config.qwen25_7b() if a.model == "qwen25_7b" else Qwen2Config.tiny()
-m = Qwen2Model(cfg, TPComm.single(), dev, dt, seed=0, quant=a.quant)
+m = Qwen2Model(cfg, TPComm.single(), dev, dt, seed=0, quant=a.quant,
+               shard_of=(a.shard_of, 0) if a.shard_of > 1 else None)
 e = DecodeEngine(m, a.batch, a.ctx + a.steps + 8, use_graph=False)
 e.set_context(a.ctx)  # the cache content does not matter for timing
 for _ in range(2):

@@ -234,6 +234,16 @@ def test_dense_attention_on_fused_qkv_views(ext):
     assert rel_l2(got, want) < 1e-2
 
 
+@pytest.mark.parametrize("splits,rows,inter", [(4, 64, 2368), (2, 7, 4736), (1, 128, 64)])
+def test_silu_mul_over_k_split_slabs(ext, splits, rows, inter):
+    from barlink_sm86_b200.ops import reference as ref
+    g = torch.Generator(device="cuda").manual_seed(inter)
+    slabs = torch.randn(splits, rows, 2 * inter, device="cuda", generator=g)
+    got = ext.silu_mul(slabs, True)
+    want = ref.silu_mul(slabs, True)
+    assert got.dtype == torch.bfloat16 and rel_l2(got, want) < 5e-3
+
+
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("nq,nkv", [(4, 1), (6, 2), (3, 3)])
 def test_dense_attention_tensor_core(ext, causal, nq, nkv):
