@@ -361,9 +361,15 @@ constexpr int kPageTokens = 16;
 constexpr int kHd = 128;
 constexpr int kRowPitch = kHd * 2 + 16;               // bytes, padded against bank conflicts
 constexpr int kPageBytes = kPageTokens * kRowPitch;   // one K or V page in shared memory
-constexpr int kWarpSmem = 4 * kPageBytes;             // K,V x 2 buffers
+constexpr int kAttnStages = 3;                        // pages in flight per warp: kAttnStages - 1
+constexpr int kWarpSmem = kAttnStages * 2 * kPageBytes;  // (K, V) x stages
 constexpr int kAttnWarps = 4;
 
+__device__ __forceinline__ float fast_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
@@ -394,8 +400,11 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 }
 
 // grid (nkv, batch, splits), 128 threads.  Each warp walks its own pages with
-// a private double buffer (cp.async), the four warps are merged through
-// shared memory, splits through `scratch` and k_attn_merge.
+// a private ring of kAttnStages page buffers (cp.async, two pages in flight
+// while one is consumed); the warp's block-table entries are fetched 32 at a
+// time into registers so that no page address waits on a dependent load.  The
+// four warps are merged through shared memory, splits through `scratch` and
+// k_attn_merge.
 __global__ void __launch_bounds__(kAttnWarps * 32)
     k_paged_attn_decode(const __nv_bfloat16* __restrict__ q, int q_stride,
                         const __nv_bfloat16* __restrict__ k_cache,
@@ -436,48 +445,71 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
   const uint32_t wbase = smem_u32(smem) + warp * kWarpSmem;
-  auto issue = [&](int page, int buf) {
-    const int blk = table[page];
+  // pages of this warp: p0 + warp + i * kAttnWarps, i in [0, count)
+  const int count = p1 > p0 + warp ? (p1 - p0 - warp + kAttnWarps - 1) / kAttnWarps : 0;
+  int tbl = 0;        // lane l holds the table entry of page index (chunk * 32 + l)
+  int tbl_chunk = -1;
+  auto issue = [&](int i, int buf) {
+    if ((i >> 5) != tbl_chunk) {
+      tbl_chunk = i >> 5;
+      const int mine = tbl_chunk * 32 + lane;
+      tbl = mine < count ? table[p0 + warp + mine * kAttnWarps] : 0;
+    }
+    const int blk = __shfl_sync(0xffffffffu, tbl, i & 31);
     const uint8_t* ks = reinterpret_cast<const uint8_t*>(k_cache) +
                         (size_t(blk) * nkv + h) * (kPageTokens * kHd * 2);
     const uint8_t* vs = reinterpret_cast<const uint8_t*>(v_cache) +
                         (size_t(blk) * nkv + h) * (kPageTokens * kHd * 2);
     const uint32_t kd = wbase + buf * 2 * kPageBytes, vd = kd + kPageBytes;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int c = lane + i * 32;  // 256 chunks of 16 B per page
+    for (int j = 0; j < 8; ++j) {
+      const int c = lane + j * 32;  // 256 chunks of 16 B per page
       const int r = c >> 4, cc = c & 15;
       cp_async16(kd + r * kRowPitch + cc * 16, ks + c * 16);
       cp_async16(vd + r * kRowPitch + cc * 16, vs + c * 16);
     }
-    cp_async_commit();
   };
 
-  int page = p0 + warp;
+  // prologue: kAttnStages - 1 pages in flight (one commit group per slot, empty when past the end)
+#pragma unroll
+  for (int i = 0; i < kAttnStages - 1; ++i) {
+    if (i < count) issue(i, i);
+    cp_async_commit();
+  }
   int buf = 0;
-  if (page < p1) issue(page, 0);
-  for (; page < p1; page += kAttnWarps, buf ^= 1) {
-    const int nxt = page + kAttnWarps;
-    if (nxt < p1) {
-      issue(nxt, buf ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+  for (int i = 0; i < count; ++i) {
+    const int page = p0 + warp + i * kAttnWarps;
+    {
+      const int nxt = i + kAttnStages - 1;
+      int nbuf = buf + kAttnStages - 1;
+      if (nbuf >= kAttnStages) nbuf -= kAttnStages;
+      if (nxt < count) issue(nxt, nbuf);
+      cp_async_commit();
+      cp_async_wait<kAttnStages - 1>();
     }
     __syncwarp();
     const uint32_t kd = wbase + buf * 2 * kPageBytes, vd = kd + kPageBytes;
     // S = Q K^T for 16 tokens (two n8 tiles)
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     {
+      // two accumulator sets (even / odd k-steps) halve the dependent MMA chain
+      float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       const int mi = lane >> 3, r = lane & 7;
       const uint32_t a0 = kd + ((mi >> 1) * 8 + r) * kRowPitch + (mi & 1) * 16;
 #pragma unroll
-      for (int ks = 0; ks < kHd / 16; ++ks) {
-        uint32_t b0, b1, b2, b3;
+      for (int ks = 0; ks < kHd / 16; ks += 2) {
+        uint32_t b0, b1, b2, b3, c0, c1, c2, c3;
         ldsm_x4(a0 + ks * 32, b0, b1, b2, b3);
+        ldsm_x4(a0 + ks * 32 + 32, c0, c1, c2, c3);
         mma_bf16_16816(s[0], qa[ks], b0, b1);
         mma_bf16_16816(s[1], qa[ks], b2, b3);
+        mma_bf16_16816(s2[0], qa[ks + 1], c0, c1);
+        mma_bf16_16816(s2[1], qa[ks + 1], c2, c3);
       }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nt][e] += s2[nt][e];
     }
     // mask, online softmax
     const int tok0 = page * kPageTokens;
@@ -498,7 +530,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
     const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-    const float al0 = exp2f(m0 - n0), al1 = exp2f(m1 - n1);  // m = -inf -> 0
+    const float al0 = fast_ex2(m0 - n0), al1 = fast_ex2(m1 - n1);  // m = -inf -> 0
     m0 = n0;
     m1 = n1;
     float ps0 = 0.f, ps1 = 0.f;
@@ -507,10 +539,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
       float pv[2][4];
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
-        pv[nt][0] = exp2f(s[nt][0] - n0);
-        pv[nt][1] = exp2f(s[nt][1] - n0);
-        pv[nt][2] = exp2f(s[nt][2] - n1);
-        pv[nt][3] = exp2f(s[nt][3] - n1);
+        pv[nt][0] = fast_ex2(s[nt][0] - n0);
+        pv[nt][1] = fast_ex2(s[nt][1] - n0);
+        pv[nt][2] = fast_ex2(s[nt][2] - n1);
+        pv[nt][3] = fast_ex2(s[nt][3] - n1);
         ps0 += pv[nt][0] + pv[nt][1];
         ps1 += pv[nt][2] + pv[nt][3];
       }
@@ -541,7 +573,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
       }
     }
     __syncwarp();
+    if (++buf == kAttnStages) buf = 0;
   }
+  cp_async_wait<0>();
   // row sums live spread over the quad
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
