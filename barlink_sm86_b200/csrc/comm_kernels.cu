@@ -1101,7 +1101,11 @@ static int launch_local(blCtx* ctx, K kernel, CollArgs base, const PerRank* pr, 
     a.aux_in[0] = pr[0].aux_in;
     a.aux_out[0] = pr[0].aux_out;
     a.gamma[0] = pr[0].gamma;
-    if (pdl) {
+    static const bool ar_pdl = [] {
+      const char* e = getenv("BL_AR_PDL");  // 0: plain stream order for the collective kernels
+      return !(e && e[0] == '0');
+    }();
+    if (pdl && ar_pdl) {
       // only for kernels that execute griddepcontrol.wait before their first read
       RT_TRY(launch_k(kernel, dim3(grid_x, 1, 1), dim3(threads, 1, 1), 0,
                       static_cast<cudaStream_t>(pr[0].stream), a),

@@ -836,8 +836,10 @@ extern "C" int bl_paged_attn_decode(const void* q, int q_stride, const void* k_c
     return -1;
   }
   if (splits <= 0) {
-    // enough CTAs to fill the GPU once; more splits only add merge traffic
-    const int want = (sm_count() + batch * nkv - 1) / (batch * nkv);
+    // enough CTAs to fill the GPU once; more splits only add merge traffic.  From 64 CTAs
+    // on, splitting measured no faster than one CTA per (sequence, KV head) and costs the
+    // merge kernel, so it is not done.
+    const int want = batch * nkv >= 64 ? 1 : (sm_count() + batch * nkv - 1) / (batch * nkv);
     const int by_len = max_blocks / (2 * kAttnWarps) > 0 ? max_blocks / (2 * kAttnWarps) : 1;
     splits = want < by_len ? want : by_len;
     if (splits > 32) splits = 32;
