@@ -53,6 +53,12 @@ def test_tiny_qwen2_tp2_matches_single_rank():
     assert "max abs logit error" in res[0][1]
 
 
+def test_tiny_qwen2_tp8_replicated_kv_heads():
+    """8 ranks, 2 KV heads: every KV head lives on 4 ranks and its query heads are dealt out."""
+    res = _run("tiny", 8, timeout=600)
+    assert all(rc == 0 for rc, _ in res), "\n".join(o for _, o in res)
+
+
 def test_tiny_mmdit_tp2_matches_single_rank():
     res = _run("mmdit", 2)
     assert all(rc == 0 for rc, _ in res), "\n".join(o for _, o in res)
