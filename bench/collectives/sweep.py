@@ -10,7 +10,7 @@ on NCCL unless --nccl-graph) and reported as the maximum over ranks; bus bandwid
 (N-1)/N for the other two.
 
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
-        bench/collectives/sweep.py --backend barlink --out gpurun_out/sweep_barlink.json
+        bench/collectives/sweep.py --backend barlink --out sweep_barlink.json
     ... --backend nccl
 """
 import argparse

@@ -69,8 +69,7 @@ def main():
             rows.append(row)
             print(row, flush=True)
             del w, q
-    out = os.path.join(ROOT, "gpurun_out", "w8a16_bench.json")
-    os.makedirs(os.path.dirname(out), exist_ok=True)
+    out = os.environ.get("BL_BENCH_OUT", "w8a16_bench.json")
     json.dump(rows, open(out, "w"))
 
 
