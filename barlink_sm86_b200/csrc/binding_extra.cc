@@ -11,6 +11,7 @@
 #include "backend.h"
 #include "bl_core.h"
 #include "bl_ops.h"
+#include "heap.h"
 
 namespace py = pybind11;
 
@@ -370,9 +371,51 @@ void gate_residual(const at::Tensor& x, const at::Tensor& y, const at::Tensor& g
                               int(gate.stride(0)), st, err, errlen));
 }
 
+// ---- host-only internals, exposed so that they can be unit-tested without a GPU ----
+py::dict layout_of(size_t pool_bytes, int world) {
+  const bl::Layout L = bl::compute_layout(pool_bytes, world);
+  py::dict d;
+  d["pool_bytes"] = L.pool_bytes;
+  d["user_bytes"] = L.user_bytes;
+  d["stage_off"] = L.stage_off;
+  d["stage_slice"] = L.stage_slice;
+  d["lamport_off"] = L.lamport_off;
+  d["lamport_slice"] = L.lamport_slice;
+  d["p2p_off"] = L.p2p_off;
+  d["p2p_slice"] = L.p2p_slice;
+  d["sig_off"] = L.sig_off;
+  return d;
+}
+
+// ops: ("alloc", bytes) -> offset or -1; ("free", offset, bytes) -> 1 / 0
+std::vector<int64_t> arena_replay(size_t user_bytes, const std::vector<py::tuple>& ops) {
+  bl::Arena a;
+  std::vector<int64_t> out;
+  for (const auto& op : ops) {
+    const std::string kind = op[0].cast<std::string>();
+    if (kind == "alloc") out.push_back(bl::arena_alloc(a, user_bytes, op[1].cast<size_t>()));
+    else out.push_back(bl::arena_free(a, op[1].cast<size_t>(), op[2].cast<size_t>()) ? 1 : 0);
+  }
+  return out;
+}
+
 }  // namespace
 
 void bind_extra(py::module_& m) {
+  m.def("layout_of", &layout_of, py::arg("pool_bytes"), py::arg("world"));
+  m.def("arena_replay", &arena_replay, py::arg("user_bytes"), py::arg("ops"));
+  m.def("algo_for", [](size_t bytes, int world, const std::string& dtype, bool multicast, size_t pool_bytes,
+                       const std::string& algo) {
+    const int dt = dtype == "bf16" ? BL_DTYPE_BF16 : dtype == "fp16" ? BL_DTYPE_FP16 : dtype == "fp32" ? BL_DTYPE_FP32
+                 : dtype == "fp64" ? BL_DTYPE_FP64 : BL_DTYPE_U8;
+    const int al = algo == "oneshot" ? BL_ALGO_ONESHOT : algo == "twoshot" ? BL_ALGO_TWOSHOT
+                 : algo == "nvls" ? BL_ALGO_NVLS : BL_ALGO_AUTO;
+    static const char* names[] = {"auto", "oneshot", "twoshot", "nvls"};
+    return std::string(names[bl_algo_for(bytes, world, dt, multicast ? 1 : 0, pool_bytes, al)]);
+  }, py::arg("bytes"), py::arg("world"), py::arg("dtype") = "bf16", py::arg("multicast") = false,
+        py::arg("pool_bytes") = size_t(1) << 30, py::arg("algo") = "auto");
+  m.def("pick_splits", [](int tiles, int kblocks, int sms, int want) { return bl::pick_splits(tiles, kblocks, sms, want); },
+        py::arg("tiles"), py::arg("kblocks"), py::arg("sms") = 148, py::arg("want") = 0);
   m.def("w4a16_linear", &w4a16_linear, py::arg("x"), py::arg("qweight"), py::arg("scales"), py::arg("qzeros"),
         py::arg("group") = 128, py::arg("splits") = 0);
   m.def("w4_dequant", &w4_dequant, py::arg("qweight"), py::arg("scales"), py::arg("qzeros"), py::arg("group") = 128);

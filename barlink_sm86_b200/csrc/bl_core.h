@@ -69,6 +69,8 @@ size_t bl_max_chunk(const blCtx* ctx);
 /* largest p2p message per call, largest one-shot all-reduce message */
 size_t bl_p2p_chunk(const blCtx* ctx);
 size_t bl_oneshot_max(const blCtx* ctx);
+/* the algorithm the dispatcher takes for an all-reduce of `bytes` (host arithmetic only) */
+int bl_algo_for(size_t bytes, int world, int dtype, int has_multicast, size_t pool_bytes, int algo);
 size_t bl_pool_bytes(const blCtx* ctx);
 
 /* Symmetric allocator over the user zone of arena devIdx (peer mode: devIdx

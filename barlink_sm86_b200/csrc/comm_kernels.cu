@@ -1210,8 +1210,7 @@ static int resolve_algo(const blCtx* ctx, int algo, size_t bytes, int dtype) {
       // one hop of (world-1) x bytes beats two hops of 2 x bytes/world until
       // the link time outgrows the extra flag round trip
       size_t lim = oneshot_max > 0 ? size_t(oneshot_max)
-                                   : (ctx->world <= 2 ? (1u << 20) : ctx->world <= 4 ? (512u << 10)
-                                                                                     : (256u << 10));
+                                   : (ctx->world <= 2 ? (1u << 20) : (512u << 10));  // measured crossovers
       if (lamport_ok && bytes <= lim) algo = BL_ALGO_ONESHOT;
       else if (nvls_ok && bytes >= (512u << 10)) algo = BL_ALGO_NVLS;
       else algo = BL_ALGO_TWOSHOT;
@@ -1221,6 +1220,22 @@ static int resolve_algo(const blCtx* ctx, int algo, size_t bytes, int dtype) {
   if (algo == BL_ALGO_NVLS && !nvls_ok) algo = BL_ALGO_TWOSHOT;
   return algo;
 }
+
+}  // namespace bl
+// Algorithm the dispatcher would take for an all-reduce of `bytes` (host-only, no GPU needed):
+// 0 auto, 1 one-shot, 2 two-shot, 3 NVLS as in bl_core.h.
+extern "C" int bl_algo_for(size_t bytes, int world, int dtype, int has_multicast, size_t pool_bytes, int algo) {
+  blCtx* c = new blCtx();
+  c->world = world;
+  c->peer_mode = true;
+  c->has_mc = has_multicast != 0;
+  const bl::Layout L = bl::compute_layout(pool_bytes, world);
+  c->layout.lamport_slice = L.lamport_slice;
+  const int r = bl::resolve_algo(c, algo, bytes, dtype);
+  delete c;
+  return r;
+}
+namespace bl {
 
 // all-reduce on every local rank (peer mode: one)
 static int allreduce_local(blCtx* ctx, const PerRank* pr, size_t bytes, int dtype, int algo,
