@@ -16,6 +16,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)
 SHAPES = {
     "qwen2-1.5b": dict(hidden_size=1536, intermediate_size=8960, num_hidden_layers=28, num_attention_heads=12,
                        num_key_value_heads=2, vocab_size=151936),
+    "qwen2.5-32b": dict(hidden_size=5120, intermediate_size=27648, num_hidden_layers=64, num_attention_heads=40,
+                        num_key_value_heads=8, vocab_size=152064),
     "qwen2.5-7b": dict(hidden_size=3584, intermediate_size=18944, num_hidden_layers=28, num_attention_heads=28,
                        num_key_value_heads=4, vocab_size=152064),
 }
