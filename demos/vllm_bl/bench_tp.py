@@ -34,9 +34,13 @@ def main():
     ap.add_argument("--kv-dtype", default=None, help="e.g. fp8_e4m3")
     ap.add_argument("--chunked-prefill", action="store_true")
     ap.add_argument("--warm-repeat", type=int, default=1)
+    ap.add_argument("--quantization", default=None,
+                    help="a vLLM quantization method; barlink_w8a16 = this library's W8A16 linears")
     ap.add_argument("--out-json", default=None)
     a = ap.parse_args()
 
+    if a.quantization == "barlink_w8a16":
+        common.enable_w8a16()
     backend = common.load_hook()
     from vllm import LLM, SamplingParams
 
@@ -49,6 +53,8 @@ def main():
         kw["kv_cache_dtype"] = a.kv_dtype
     if a.chunked_prefill:
         kw["enable_chunked_prefill"] = True
+    if a.quantization:
+        kw["quantization"] = a.quantization
     llm = LLM(**kw)
 
     import random
@@ -71,7 +77,7 @@ def main():
     res = {"backend": backend, "tp": a.tp, "model": os.environ.get("BENCH_MODEL") or (a.shape + " (dummy weights)"),
            "prompt_tokens": a.prompt_tokens, "prompts": a.num_prompts, "gen_tokens": gen, "wall_s": wall,
            "tps": gen / wall, "warm_wall_s": warm, "decode_tps": (gen / warm) if warm else None,
-           "prefill_s": (wall - warm) if warm else None, "mtp": a.mtp, "kv_dtype": a.kv_dtype,
+           "prefill_s": (wall - warm) if warm else None, "mtp": a.mtp, "kv_dtype": a.kv_dtype, "quantization": a.quantization,
            "enforce_eager": os.environ.get("ENFORCE_EAGER") == "1",
            "first_tokens": list(outs[0].outputs[0].token_ids[:8])}
     print("BENCH RESULT " + json.dumps(res), flush=True)

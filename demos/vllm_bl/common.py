@@ -23,6 +23,15 @@ SHAPES = {
 }
 
 
+def enable_w8a16():
+    """Turn on the hook's quantization step (vLLM quantization="barlink_w8a16": linear layers
+    run this library's W8A16 kernel) for this process and the workers it spawns.  Call before load_hook()."""
+    steps = os.environ.get("BL_SHIM_STEPS", "1,2,3,4").split(",")
+    if "6" not in steps:
+        steps.append("6")
+    os.environ["BL_SHIM_STEPS"] = ",".join(steps)
+
+
 def load_hook():
     """Install the barlink hook unless BL_SHIM_OFF=1 (then vLLM keeps NCCL: the A/B baseline)."""
     if ROOT not in sys.path:

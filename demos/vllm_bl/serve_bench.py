@@ -105,10 +105,12 @@ def main():
     ap.add_argument("--max-num-seqs", type=int, default=256)
     ap.add_argument("--gpu-mem", type=float, default=0.85)
     ap.add_argument("--kv-dtype", default=None)
-    ap.add_argument("--quantization", default=None, help="a vLLM quantization method name, passed through")
+    ap.add_argument("--quantization", default=None, help="a vLLM quantization method; barlink_w8a16 = this library's W8A16 linears")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--out-json", default=None)
     a = ap.parse_args()
+    if a.quantization == "barlink_w8a16":
+        common.enable_w8a16()
     backend = common.load_hook()
     asyncio.run(run(a, backend))
 

@@ -21,7 +21,9 @@ switches as the reference's shim (vllm_barlink/__init__.py:34-142 there):
   5. (opt-in) add `vllm::all_reduce` to the compilation splitting ops so that
      it runs between captured graph pieces.  barlink's collectives are safe to
      capture (their expectations are device counters), so this is only an
-     escape hatch.
+     escape hatch;
+  6. (opt-in) register the quantization method "barlink_w8a16"
+     (`vllm_barlink/quant.py`): linear layers run this library's W8A16 kernel.
 
 `BL_SHIM_STEPS` (default "1,2,3,4") selects steps, `BL_SHIM_OFF=1` disables
 the hook, `BL_SHIM_DEBUG=1` logs what it does.
@@ -163,6 +165,14 @@ def install():
             CompilationConfig.set_splitting_ops_for_v1 = set_splitting_ops_for_v1
         except Exception as e:
             _debug("splitting-ops patch skipped: %s" % e)
+
+    if _step(6):
+        try:
+            from . import quant
+
+            _debug("registered quantization method %r" % quant.register())
+        except Exception as e:
+            _debug("quantization method not registered: %s" % e)
 
 
 install()
