@@ -535,7 +535,23 @@ c10::intrusive_ptr<c10d::Work> BarlinkBackend::alltoall_base(at::Tensor& output,
     return done(c10d::OpType::ALLTOALL_BASE, {output});
   }
   if (!input.is_cuda()) return cpu("all_to_all").alltoall_base(output, input, outSplit, inSplit, opts);
-  TORCH_CHECK(false, "barlink: all_to_all on CUDA tensors is not implemented (no model of this library uses it)");
+  // Equal splits only: every rank gathers every input over the link and keeps the
+  // slices addressed to it (world x the minimal traffic; the models of this library
+  // have no all-to-all on their hot path, so this is a convenience, not a tuned kernel).
+  TORCH_CHECK(outSplit.empty() && inSplit.empty(),
+              "barlink: all_to_all on CUDA tensors supports equal splits only");
+  const int64_t w = getSize();
+  TORCH_CHECK(input.numel() == output.numel() && input.numel() % w == 0 && input.is_contiguous() &&
+                  output.is_contiguous() && input.scalar_type() == output.scalar_type(),
+              "barlink: all_to_all needs contiguous tensors of equal size, divisible by the world size");
+  const int64_t per = input.numel() / w;
+  at::Tensor all = at::empty({w, w, per}, input.options());
+  at::Tensor in = input.view({-1});
+  at::Tensor flat = all.view({-1});
+  allgather_cuda(flat, in);
+  // all[r][me] is what rank r addressed to this rank
+  output.view({w, per}).copy_(all.select(1, getRank()));
+  return done(c10d::OpType::ALLTOALL_BASE, {output});
 }
 
 c10::intrusive_ptr<c10d::Work> BarlinkBackend::send(std::vector<at::Tensor>& tensors, int dstRank,

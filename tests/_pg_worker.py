@@ -232,6 +232,11 @@ for op, want_fn in ((dist.ReduceOp.MAX, lambda v: max(v)), (dist.ReduceOp.MIN, l
     vals = [float(r + 2) for r in range(world)]
     want = want_fn(vals) if want_fn else float(torch.tensor(vals).prod())
     assert torch.allclose(t, torch.full_like(t, want)), (op, t, want)
+# all_to_all with equal splits: rank r sends value 100*r + d to rank d
+src = torch.stack([torch.full((3,), float(100 * rank + d), device=dev) for d in range(world)]).view(-1)
+dst = torch.empty_like(src)
+dist.all_to_all_single(dst, src)
+assert torch.equal(dst.view(world, 3)[:, 0].cpu(), torch.tensor([float(100 * r + rank) for r in range(world)]))
 for bad in (lambda: dist.all_reduce(torch.ones(4, dtype=torch.int32, device=dev), op=dist.ReduceOp.BAND),
             lambda: dist.all_reduce(torch.ones(4, dtype=torch.int64, device=dev)),
             lambda: dist.send(torch.ones(4, device=dev), rank)):
