@@ -896,6 +896,46 @@ at::Tensor paged_attn_decode(const at::Tensor& qkv, const at::Tensor& k_cache,
   return out;
 }
 
+// qkv: bf16 [batch, width] or fp32 k-split slabs [splits, batch, width] of the QKV linear
+at::Tensor rope_attn_decode(const at::Tensor& qkv, const c10::optional<at::Tensor>& bias,
+                            const at::Tensor& positions, const at::Tensor& slots, at::Tensor& k_cache,
+                            at::Tensor& v_cache, const at::Tensor& block_tables, const at::Tensor& ctx_lens,
+                            int nq, int nkv, int hd, double theta, double scale, int splits) {
+  const bool slabs = qkv.scalar_type() == at::kFloat && qkv.dim() == 3;
+  TORCH_CHECK(qkv.is_cuda() && qkv.is_contiguous() &&
+                  (slabs || (qkv.scalar_type() == at::kBFloat16 && qkv.dim() == 2)),
+              "barlink: qkv must be contiguous bfloat16 [batch, width] or float32 slabs [splits, batch, width]");
+  const int batch = int(qkv.size(slabs ? 1 : 0)), width = int(qkv.size(slabs ? 2 : 1));
+  TORCH_CHECK(width == (nq + 2 * nkv) * hd, "barlink: qkv rows must hold nq + 2 nkv heads");
+  check_bf16(k_cache, "k_cache");
+  check_bf16(v_cache, "v_cache");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.size(1) == nkv && k_cache.size(3) == hd,
+              "barlink: cache layout is [blocks, nkv, block_size, head_dim]");
+  TORCH_CHECK(block_tables.is_cuda() && block_tables.scalar_type() == at::kInt && block_tables.dim() == 2 &&
+                  block_tables.is_contiguous() && block_tables.size(0) == batch,
+              "barlink: block_tables must be contiguous int32 [batch, max_blocks]");
+  for (const at::Tensor* t : {&positions, &slots, &ctx_lens})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->is_contiguous() && t->numel() == batch,
+                "barlink: positions / slots / ctx_lens must be contiguous int32 [batch]");
+  if (bias) {
+    check_bf16(*bias, "bias");
+    TORCH_CHECK(bias->numel() == width, "barlink: bias must have one entry per qkv column");
+  }
+  at::Tensor out = at::empty({batch, int64_t(nq) * hd}, k_cache.options());
+  const int dev = qkv.device().index();
+  c10::cuda::CUDAGuard guard(qkv.device());
+  Scratch& s = scratch_for(dev);
+  if (batch > 0)
+    BL_CHECK(bl_rope_attn_decode(slabs ? nullptr : qkv.data_ptr(), width, slabs ? qkv.data_ptr() : nullptr,
+                                 slabs ? int(qkv.size(0)) : 0, size_t(batch) * width,
+                                 bias ? bias->data_ptr() : nullptr, positions.data_ptr<int>(),
+                                 slots.data_ptr<int>(), float(theta), k_cache.data_ptr(), v_cache.data_ptr(),
+                                 block_tables.data_ptr<int>(), ctx_lens.data_ptr<int>(), out.data_ptr(), batch,
+                                 nq, nkv, hd, int(k_cache.size(2)), int(block_tables.size(1)), float(scale),
+                                 splits, s.attn.data_ptr(), size_t(s.attn.nbytes()), stream_of(qkv), err, errlen));
+  return out;
+}
+
 }  // namespace
 
 void bind_extra(py::module_& m);  // binding_extra.cc: attention prefill, W8A16, fused TP linears
@@ -965,6 +1005,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("decode_advance", &decode_advance, py::arg("positions"), py::arg("ctx_lens"), py::arg("slots"),
         py::arg("block_tables"), py::arg("ids"), py::arg("sampled") = py::none(),
         py::arg("block_size") = 16);
+  m.def("rope_attn_decode", &rope_attn_decode, py::arg("qkv"), py::arg("bias"), py::arg("positions"),
+        py::arg("slots"), py::arg("k_cache"), py::arg("v_cache"), py::arg("block_tables"), py::arg("ctx_lens"),
+        py::arg("nq"), py::arg("nkv"), py::arg("hd"), py::arg("theta"), py::arg("scale"), py::arg("splits") = 0);
   m.def("paged_attn_decode", &paged_attn_decode, py::arg("qkv"), py::arg("k_cache"),
         py::arg("v_cache"), py::arg("block_tables"), py::arg("ctx_lens"), py::arg("nq"),
         py::arg("nkv"), py::arg("hd"), py::arg("scale"), py::arg("splits") = 0,

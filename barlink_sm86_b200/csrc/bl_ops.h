@@ -171,6 +171,13 @@ int bl_paged_attn_decode(const void* q, int q_stride, const void* k_cache, const
                          int nkv, int hd, int block_size, int max_blocks, float scale, int splits,
                          void* scratch, size_t scratch_bytes, void* stream, char* err,
                          size_t errlen);
+/* RoPE + KV write + paged attention in one launch (decode).  qkv: bf16 rows, or null with
+ * slabs = nsplit_in fp32 slabs of the QKV linear `slab` floats apart (+ bias). */
+int bl_rope_attn_decode(const void* qkv, int q_stride, const void* slabs, int nsplit_in, size_t slab,
+                        const void* bias, const int* positions, const int* slots, float theta, void* k_cache,
+                        void* v_cache, const int* block_tables, const int* ctx_lens, void* out, int batch, int nq,
+                        int nkv, int hd, int block_size, int max_blocks, float scale, int splits, void* scratch,
+                        size_t scratch_bytes, void* stream, char* err, size_t errlen);
 /* Dense attention (prefill / joint attention): q [tq x nq x hd], k, v
  * [tk x nkv x hd] per sequence, sequences given by cu_seqlens (batch+1);
  * causal aligns the last query with the last key. */

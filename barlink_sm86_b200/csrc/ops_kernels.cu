@@ -628,6 +628,332 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   }
 }
 
+// Source of the raw (pre-RoPE) QKV projection of the decode step: the bf16
+// buffer, or the fp32 k-split slabs of the QKV linear (+ bias), summed and
+// rounded to bf16 exactly as k_rope_kv_write does.
+struct QkvSrc {
+  const __nv_bfloat16* qkv;
+  int q_stride;
+  const float* slabs;
+  int nsplit;
+  size_t slab;
+  const __nv_bfloat16* bias;
+  int width;
+};
+// elements (col, col + 1) of row `row`; col even
+__device__ __forceinline__ float2 qkv_pair(const QkvSrc& s, int row, int col) {
+  if (s.slabs) {
+    const size_t e = size_t(row) * s.width + col;
+    float a = 0.f, c = 0.f;
+    for (int sp = 0; sp < s.nsplit; ++sp) {
+      const float2 v = __ldcg(reinterpret_cast<const float2*>(s.slabs + sp * s.slab + e));
+      a += v.x;
+      c += v.y;
+    }
+    if (s.bias) {
+      const float2 bb = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(s.bias + col));
+      a += bb.x;
+      c += bb.y;
+    }
+    return unpack_bf16x2(pack_bf16x2(a, c));
+  }
+  return unpack_bf16x2(*reinterpret_cast<const uint32_t*>(s.qkv + size_t(row) * s.q_stride + col));
+}
+
+// k_paged_attn_decode with the kernel before it folded in: the query heads and
+// the new token's key are taken raw from the QKV projection (the bf16 buffer,
+// or the k-split slabs of that linear plus bias), rotated here, the new key and
+// value are stored to the cache by the block that owns the last page, and that
+// block patches the row into its shared-memory copy of the page, so the cache
+// write never has to be visible to this kernel's own loads.  Selected with
+// BL_FUSE_ROPE_ATTN=1 (one launch less per layer).
+__global__ void __launch_bounds__(kAttnWarps * 32)
+    k_rope_attn_decode(QkvSrc src, const int* __restrict__ positions, const int* __restrict__ slots,
+                       float log2_theta, __nv_bfloat16* __restrict__ k_cache,
+                       __nv_bfloat16* __restrict__ v_cache,
+                        const int* __restrict__ block_tables, const int* __restrict__ ctx_lens,
+                        __nv_bfloat16* __restrict__ out, float* __restrict__ scratch, int nq,
+                        int nkv, int max_blocks, float scale_log2) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int h = blockIdx.x, b = blockIdx.y, sp = blockIdx.z, nsplit = gridDim.z;
+  const int G = nq / nkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int ctx = ctx_lens[b];
+  const int n_pages = (ctx + kPageTokens - 1) / kPageTokens;
+  const int per = (n_pages + nsplit - 1) / nsplit;
+  const int p0 = sp * per;
+  const int p1 = min(n_pages, p0 + per);
+  const int* table = block_tables + size_t(b) * max_blocks;
+
+  // cos / sin of this sequence's position for the 64 rotation pairs
+  __shared__ float2 s_cs[kHd / 2];
+  __shared__ __align__(16) __nv_bfloat16 s_new[2][kHd];  // rotated key, value of the new token
+  const float pos = float(positions[b]);
+  if (threadIdx.x < kHd / 2) {
+    const float inv = exp2f(-log2_theta * (2.f * float(threadIdx.x) / float(kHd)));
+    float sn, cs;
+    sincosf(pos * inv, &sn, &cs);
+    s_cs[threadIdx.x] = make_float2(cs, sn);
+  }
+  __syncthreads();
+  const int last_page = n_pages - 1;
+  const bool owns_last = last_page >= p0 && last_page < p1;
+  if (owns_last && warp == 0) {
+    // new key (rotated) and value of KV head h: lane l owns dims 2l, 2l+1 and 64+2l, 65+2l
+    const int kcol = (nq + h) * kHd, vcol = (nq + nkv + h) * kHd;
+    const float2 lo = qkv_pair(src, b, kcol + 2 * lane), hi = qkv_pair(src, b, kcol + 64 + 2 * lane);
+    const float2 c0 = s_cs[2 * lane], c1 = s_cs[2 * lane + 1];
+    const uint32_t klo = pack_bf16x2(lo.x * c0.x - hi.x * c0.y, lo.y * c1.x - hi.y * c1.y);
+    const uint32_t khi = pack_bf16x2(hi.x * c0.x + lo.x * c0.y, hi.y * c1.x + lo.y * c1.y);
+    const float2 v0 = qkv_pair(src, b, vcol + 2 * lane), v1 = qkv_pair(src, b, vcol + 64 + 2 * lane);
+    const uint32_t vlo = pack_bf16x2(v0.x, v0.y), vhi = pack_bf16x2(v1.x, v1.y);
+    reinterpret_cast<uint32_t*>(s_new[0])[lane] = klo;
+    reinterpret_cast<uint32_t*>(s_new[0])[32 + lane] = khi;
+    reinterpret_cast<uint32_t*>(s_new[1])[lane] = vlo;
+    reinterpret_cast<uint32_t*>(s_new[1])[32 + lane] = vhi;
+    const int slot = slots[b];
+    if (slot >= 0) {
+      const size_t row = (size_t(slot / kPageTokens) * nkv + h) * kPageTokens + slot % kPageTokens;
+      uint32_t* kc = reinterpret_cast<uint32_t*>(k_cache + row * kHd);
+      uint32_t* vc = reinterpret_cast<uint32_t*>(v_cache + row * kHd);
+      kc[lane] = klo;
+      kc[32 + lane] = khi;
+      vc[lane] = vlo;
+      vc[32 + lane] = vhi;
+    }
+  }
+  __syncthreads();
+
+  // Q fragments (rows = heads of this group, zero beyond G), rotated: the partner of
+  // dim d < 64 is d + 64, i.e. the same thread's fragment four k-steps further on
+  uint32_t qa[kHd / 16][4];
+  {
+    const int qcol = h * G * kHd;
+#pragma unroll
+    for (int ks = 0; ks < kHd / 32; ++ks) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {          // columns c and c + 8
+        const int c = ks * 16 + 2 * t + half * 8;      // < 64
+        const float2 c0 = s_cs[c], c1 = s_cs[c + 1];
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {               // rows g and g + 8
+          const int r = g + rr * 8;
+          uint32_t lo_o = 0u, hi_o = 0u;
+          if (r < G) {
+            const float2 lo = qkv_pair(src, b, qcol + r * kHd + c);
+            const float2 hi = qkv_pair(src, b, qcol + r * kHd + c + 64);
+            lo_o = pack_bf16x2(lo.x * c0.x - hi.x * c0.y, lo.y * c1.x - hi.y * c1.y);
+            hi_o = pack_bf16x2(hi.x * c0.x + lo.x * c0.y, hi.y * c1.x + lo.y * c1.y);
+          }
+          qa[ks][half * 2 + rr] = lo_o;
+          qa[ks + 4][half * 2 + rr] = hi_o;
+        }
+      }
+    }
+  }
+  float o[kHd / 8][4];
+#pragma unroll
+  for (int d = 0; d < kHd / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  const uint32_t wbase = smem_u32(smem) + warp * kWarpSmem;
+  // pages of this warp: p0 + warp + i * kAttnWarps, i in [0, count)
+  const int count = p1 > p0 + warp ? (p1 - p0 - warp + kAttnWarps - 1) / kAttnWarps : 0;
+  int tbl = 0;        // lane l holds the table entry of page index (chunk * 32 + l)
+  int tbl_chunk = -1;
+  auto issue = [&](int i, int buf) {
+    if ((i >> 5) != tbl_chunk) {
+      tbl_chunk = i >> 5;
+      const int mine = tbl_chunk * 32 + lane;
+      tbl = mine < count ? table[p0 + warp + mine * kAttnWarps] : 0;
+    }
+    const int blk = __shfl_sync(0xffffffffu, tbl, i & 31);
+    const uint8_t* ks = reinterpret_cast<const uint8_t*>(k_cache) +
+                        (size_t(blk) * nkv + h) * (kPageTokens * kHd * 2);
+    const uint8_t* vs = reinterpret_cast<const uint8_t*>(v_cache) +
+                        (size_t(blk) * nkv + h) * (kPageTokens * kHd * 2);
+    const uint32_t kd = wbase + buf * 2 * kPageBytes, vd = kd + kPageBytes;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = lane + j * 32;  // 256 chunks of 16 B per page
+      const int r = c >> 4, cc = c & 15;
+      cp_async16(kd + r * kRowPitch + cc * 16, ks + c * 16);
+      cp_async16(vd + r * kRowPitch + cc * 16, vs + c * 16);
+    }
+  };
+
+  // prologue: kAttnStages - 1 pages in flight (one commit group per slot, empty when past the end)
+#pragma unroll
+  for (int i = 0; i < kAttnStages - 1; ++i) {
+    if (i < count) issue(i, i);
+    cp_async_commit();
+  }
+  int buf = 0;
+  for (int i = 0; i < count; ++i) {
+    const int page = p0 + warp + i * kAttnWarps;
+    {
+      const int nxt = i + kAttnStages - 1;
+      int nbuf = buf + kAttnStages - 1;
+      if (nbuf >= kAttnStages) nbuf -= kAttnStages;
+      if (nxt < count) issue(nxt, nbuf);
+      cp_async_commit();
+      cp_async_wait<kAttnStages - 1>();
+    }
+    __syncwarp();
+    const uint32_t kd = wbase + buf * 2 * kPageBytes, vd = kd + kPageBytes;
+    if (page == last_page) {
+      // the new token's row comes from this block, not from the cache
+      const int r = (ctx - 1) % kPageTokens;
+      const uint2 kk = reinterpret_cast<const uint2*>(s_new[0])[lane];
+      const uint2 vv = reinterpret_cast<const uint2*>(s_new[1])[lane];
+      asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(kd + r * kRowPitch + lane * 8), "r"(kk.x), "r"(kk.y)
+                   : "memory");
+      asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(vd + r * kRowPitch + lane * 8), "r"(vv.x), "r"(vv.y)
+                   : "memory");
+      __syncwarp();
+    }
+    // S = Q K^T for 16 tokens (two n8 tiles)
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    {
+      // two accumulator sets (even / odd k-steps) halve the dependent MMA chain
+      float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      const int mi = lane >> 3, r = lane & 7;
+      const uint32_t a0 = kd + ((mi >> 1) * 8 + r) * kRowPitch + (mi & 1) * 16;
+#pragma unroll
+      for (int ks = 0; ks < kHd / 16; ks += 2) {
+        uint32_t b0, b1, b2, b3, c0, c1, c2, c3;
+        ldsm_x4(a0 + ks * 32, b0, b1, b2, b3);
+        ldsm_x4(a0 + ks * 32 + 32, c0, c1, c2, c3);
+        mma_bf16_16816(s[0], qa[ks], b0, b1);
+        mma_bf16_16816(s[1], qa[ks], b2, b3);
+        mma_bf16_16816(s2[0], qa[ks + 1], c0, c1);
+        mma_bf16_16816(s2[1], qa[ks + 1], c2, c3);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nt][e] += s2[nt][e];
+    }
+    // mask, online softmax
+    const int tok0 = page * kPageTokens;
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int tok = tok0 + nt * 8 + 2 * t + (e & 1);
+        float x = s[nt][e] * scale_log2;
+        if (tok >= ctx) x = -INFINITY;
+        s[nt][e] = x;
+        if (e < 2) mx0 = fmaxf(mx0, x);
+        else mx1 = fmaxf(mx1, x);
+      }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+    const float al0 = fast_ex2(m0 - n0), al1 = fast_ex2(m1 - n1);  // m = -inf -> 0
+    m0 = n0;
+    m1 = n1;
+    float ps0 = 0.f, ps1 = 0.f;
+    uint32_t pa[4];
+    {
+      float pv[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        pv[nt][0] = fast_ex2(s[nt][0] - n0);
+        pv[nt][1] = fast_ex2(s[nt][1] - n0);
+        pv[nt][2] = fast_ex2(s[nt][2] - n1);
+        pv[nt][3] = fast_ex2(s[nt][3] - n1);
+        ps0 += pv[nt][0] + pv[nt][1];
+        ps1 += pv[nt][2] + pv[nt][3];
+      }
+      pa[0] = pack_bf16x2(pv[0][0], pv[0][1]);
+      pa[1] = pack_bf16x2(pv[0][2], pv[0][3]);
+      pa[2] = pack_bf16x2(pv[1][0], pv[1][1]);
+      pa[3] = pack_bf16x2(pv[1][2], pv[1][3]);
+    }
+    l0 = l0 * al0 + ps0;
+    l1 = l1 * al1 + ps1;
+#pragma unroll
+    for (int d = 0; d < kHd / 8; ++d) {
+      o[d][0] *= al0;
+      o[d][1] *= al0;
+      o[d][2] *= al1;
+      o[d][3] *= al1;
+    }
+    // O += P V
+    {
+      const int mi = lane >> 3, r = lane & 7;
+      const uint32_t a0 = vd + ((mi & 1) * 8 + r) * kRowPitch + (mi >> 1) * 16;
+#pragma unroll
+      for (int d = 0; d < kHd / 8; d += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(a0 + d * 16, b0, b1, b2, b3);
+        mma_bf16_16816(o[d], pa, b0, b1);
+        mma_bf16_16816(o[d + 1], pa, b2, b3);
+      }
+    }
+    __syncwarp();
+    if (++buf == kAttnStages) buf = 0;
+  }
+  cp_async_wait<0>();
+  // row sums live spread over the quad
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+
+  // ---- merge the four warps ----------------------------------------------
+  float* wo = reinterpret_cast<float*>(smem + warp * kWarpSmem);  // [16][128] + m[16] + l[16]
+  float* wm = wo + 16 * kHd;
+  float* wl = wm + 16;
+#pragma unroll
+  for (int d = 0; d < kHd / 8; ++d) {
+    *reinterpret_cast<float2*>(wo + g * kHd + d * 8 + 2 * t) = make_float2(o[d][0], o[d][1]);
+    *reinterpret_cast<float2*>(wo + (g + 8) * kHd + d * 8 + 2 * t) = make_float2(o[d][2], o[d][3]);
+  }
+  if (t == 0) {
+    wm[g] = m0;
+    wm[g + 8] = m1;
+    wl[g] = l0;
+    wl[g + 8] = l1;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < G * kHd; e += blockDim.x) {
+    const int r = e / kHd, d = e % kHd;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w)
+      M = fmaxf(M, reinterpret_cast<const float*>(smem + w * kWarpSmem)[16 * kHd + r]);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float* base = reinterpret_cast<const float*>(smem + w * kWarpSmem);
+      const float mw = base[16 * kHd + r];
+      const float sc = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      L += base[16 * kHd + 16 + r] * sc;
+      acc += base[r * kHd + d] * sc;
+    }
+    const int head = h * G + r;
+    if (nsplit == 1) {
+      out[size_t(b) * nq * kHd + size_t(head) * kHd + d] =
+          __float2bfloat16(L > 0.f ? acc / L : 0.f);
+    } else {
+      float* sc = scratch + ((size_t(b) * nq + head) * nsplit + sp) * (kHd + 2);
+      sc[d] = acc;
+      if (d == 0) {
+        sc[kHd] = M;
+        sc[kHd + 1] = L;
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kHd) k_attn_merge(const float* __restrict__ scratch,
                                                     __nv_bfloat16* __restrict__ out, int nsplit) {
   pdl_launch_dependents();
@@ -867,6 +1193,77 @@ extern "C" int bl_paged_attn_decode(const void* q, int q_stride, const void* k_c
       static_cast<__nv_bfloat16*>(out), static_cast<float*>(scratch), nq, nkv, max_blocks,
       scale_log2);
   OPS_LAUNCH_CHECK("paged_attn_decode");
+  if (splits > 1) {
+    launch_k(k_attn_merge, dim3(batch * nq), dim3(kHd), 0, st, static_cast<const float*>(scratch),
+                                             static_cast<__nv_bfloat16*>(out), splits);
+    OPS_LAUNCH_CHECK("attn_merge");
+  }
+  return 0;
+}
+
+// RoPE + KV write + paged attention in one launch.  qkv: bf16 rows of width
+// (nq + 2 nkv) * hd with pitch q_stride, or null with `slabs` = nsplit_in fp32
+// slabs [rows][width] `slab` floats apart (+ optional bias of `width`).
+extern "C" int bl_rope_attn_decode(const void* qkv, int q_stride, const void* slabs, int nsplit_in,
+                                   size_t slab, const void* bias, const int* positions, const int* slots,
+                                   float theta, void* k_cache, void* v_cache, const int* block_tables,
+                                   const int* ctx_lens, void* out, int batch, int nq, int nkv,
+                                    int hd, int block_size, int max_blocks, float scale, int splits,
+                                    void* scratch, size_t scratch_bytes, void* stream, char* err,
+                                    size_t errlen) {
+  if (hd != kHd || block_size != kPageTokens) {
+    set_err(err, errlen, "barlink: paged attention is built for head_dim %d and block size %d", kHd,
+            kPageTokens);
+    return -1;
+  }
+  if (nkv < 1 || nq % nkv || nq / nkv > 16) {
+    set_err(err, errlen, "barlink: paged attention needs nq %% nkv == 0 and at most 16 query heads per KV head");
+    return -1;
+  }
+  if (splits <= 0) {
+    // enough CTAs to fill the GPU once; more splits only add merge traffic.  From 64 CTAs
+    // on, splitting measured no faster than one CTA per (sequence, KV head) and costs the
+    // merge kernel, so it is not done.
+    const int want = batch * nkv >= 64 ? 1 : (sm_count() + batch * nkv - 1) / (batch * nkv);
+    const int by_len = max_blocks / (2 * kAttnWarps) > 0 ? max_blocks / (2 * kAttnWarps) : 1;
+    splits = want < by_len ? want : by_len;
+    if (splits > 32) splits = 32;
+    if (splits < 1) splits = 1;
+  }
+  const size_t need = size_t(batch) * nq * splits * (kHd + 2) * sizeof(float);
+  if (splits > 1 && (!scratch || scratch_bytes < need)) splits = 1;
+  if ((!qkv && !slabs) || !positions || !slots || ((q_stride | (nq + 2 * nkv) * hd) & 1)) {
+    set_err(err, errlen, "barlink: fused RoPE + attention needs the QKV projection, positions and slots");
+    return -1;
+  }
+  QkvSrc src;
+  src.qkv = static_cast<const __nv_bfloat16*>(qkv);
+  src.q_stride = q_stride;
+  src.slabs = static_cast<const float*>(slabs);
+  src.nsplit = nsplit_in;
+  src.slab = slab;
+  src.bias = static_cast<const __nv_bfloat16*>(bias);
+  src.width = (nq + 2 * nkv) * hd;
+  static bool attr = false;
+  const int smem = kAttnWarps * kWarpSmem;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(k_rope_attn_decode,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+      set_err(err, errlen, "barlink: paged attention shared memory opt-in failed: %s",
+              cudaGetErrorString(e));
+      return -1;
+    }
+    attr = true;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  launch_k(k_rope_attn_decode, dim3(nkv, batch, splits), dim3(kAttnWarps * 32), smem, st, src, positions,
+      slots, log2f(theta), static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache),
+      block_tables, ctx_lens,
+      static_cast<__nv_bfloat16*>(out), static_cast<float*>(scratch), nq, nkv, max_blocks,
+      scale_log2);
+  OPS_LAUNCH_CHECK("rope_attn_decode");
   if (splits > 1) {
     launch_k(k_attn_merge, dim3(batch * nq), dim3(kHd), 0, st, static_cast<const float*>(scratch),
                                              static_cast<__nv_bfloat16*>(out), splits);

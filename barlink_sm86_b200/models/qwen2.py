@@ -332,8 +332,16 @@ class Qwen2Model:
     def decode_hidden(self, ids, positions, slots, ctx_lens, cache: PagedKV, splits=0):
         nq, nkv, hd = self.nq, self.nkv, self.hd
 
+        import os
+        fuse = os.environ.get("BL_FUSE_ROPE_ATTN", "0") == "1" and self.device.type == "cuda"
+
         def attn_factory(li):
             def attn(qkv, bias=None):
+                if fuse:
+                    # opt-in: RoPE, the KV write and the attention in one launch
+                    return ops.rope_attn_decode(qkv, bias, positions, slots, cache.k[li], cache.v[li],
+                                                cache.block_tables, ctx_lens, nq, nkv, hd, cache.block_size,
+                                                self.cfg.theta, self.scale, splits)
                 qkv = ops.rope_kv_write(qkv, positions, slots, cache.k[li], cache.v[li], nq, nkv, hd,
                                         cache.block_size, self.cfg.theta, bias)
                 return ops.paged_attn_decode(qkv, cache.k[li], cache.v[li], cache.block_tables,

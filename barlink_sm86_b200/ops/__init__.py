@@ -214,6 +214,20 @@ def paged_attn_decode(qkv, k_cache, v_cache, block_tables, ctx_lens, nq, nkv, hd
     return ref.paged_attn_decode(qkv, k_cache, v_cache, block_tables, ctx_lens, nq, nkv, hd, scale)
 
 
+def rope_attn_decode(qkv, bias, positions, slots, k_cache, v_cache, block_tables, ctx_lens, nq, nkv, hd,
+                     block_size, theta, scale, splits=0):
+    """Decode step of one layer's attention in one launch: RoPE on q and the
+    new k, the new k/v stored at `slots`, paged attention over the context.
+    qkv: bf16 [batch, width] or the fp32 k-split slabs of the QKV linear
+    (+ bias).  Same result as rope_kv_write followed by paged_attn_decode."""
+    if k_cache.is_cuda:
+        _count(2 if splits != 1 else 1)
+        return _C().rope_attn_decode(qkv, bias, positions, slots, k_cache, v_cache, block_tables, ctx_lens,
+                                     nq, nkv, hd, theta, scale, splits)
+    rot = rope_kv_write(qkv, positions, slots, k_cache, v_cache, nq, nkv, hd, block_size, theta, bias)
+    return ref.paged_attn_decode(rot, k_cache, v_cache, block_tables, ctx_lens, nq, nkv, hd, scale)
+
+
 def attention(q, k, v, cu_q, cu_k, max_q, scale, causal, max_k=0):
     """Dense attention over packed sequences (prefill, joint attention).
     With max_k (length of the longest key sequence) the tcgen05 kernel runs
@@ -233,5 +247,5 @@ def w8a16_linear(x, wq, scale, bias=None, silu_mul=False):
 
 __all__ = [
     "linear", "linear_split", "k_splits", "TiledWeight", "tile_weight", "untile_weight", "rmsnorm", "rope_kv_write", "rope", "silu_mul", "embedding", "argmax",
-    "paged_attn_decode", "attention", "w8a16_linear", "w4a16_linear", "qknorm_rope", "layernorm_modulate", "gate_residual", "ref",
+    "paged_attn_decode", "rope_attn_decode", "attention", "w8a16_linear", "w4a16_linear", "qknorm_rope", "layernorm_modulate", "gate_residual", "ref",
 ]

@@ -1,0 +1,48 @@
+# SPDX-License-Identifier: MIT
+"""Kernels that are built but not yet enabled by default.  They run only with
+BL_TEST_EXPERIMENTAL=1, against the default path they are meant to replace."""
+import math
+import os
+
+import pytest
+import torch
+
+from conftest import rel_l2
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(os.environ.get("BL_TEST_EXPERIMENTAL") != "1",
+                                 reason="set BL_TEST_EXPERIMENTAL=1 to run kernels that are not on by default")]
+
+
+@pytest.mark.parametrize("nq,nkv", [(28, 4), (4, 1), (7, 1), (14, 2)])
+@pytest.mark.parametrize("slabs", [0, 3])
+@pytest.mark.parametrize("splits", [0, 1, 3])
+def test_fused_rope_attention_matches_the_two_kernel_path(ext, nq, nkv, slabs, splits):
+    """RoPE + KV write + paged attention in one launch against rope_kv_write followed by
+    paged_attn_decode: same attention output, same cache contents."""
+    hd, bs = 128, 16
+    ctxs = [1, 16, 17, 300, 1024, 33, 640, 5]
+    batch, max_blocks = len(ctxs), 64
+    g = torch.Generator(device="cuda").manual_seed(nq * 10 + slabs)
+    width = (nq + 2 * nkv) * hd
+    nblk = batch * max_blocks
+    kc = (torch.randn(nblk, nkv, bs, hd, device="cuda", generator=g) * 0.5).bfloat16()
+    vc = (torch.randn(nblk, nkv, bs, hd, device="cuda", generator=g) * 0.5).bfloat16()
+    bt = torch.randperm(nblk, device="cuda", generator=g).to(torch.int32).view(batch, max_blocks).contiguous()
+    ctx = torch.tensor(ctxs, dtype=torch.int32, device="cuda")
+    pos = ctx - 1
+    slots = (bt[torch.arange(batch, device="cuda"), (pos // bs).long()] * bs + pos % bs).to(torch.int32)
+    bias = (torch.randn(width, device="cuda", generator=g) * 0.1).bfloat16()
+    if slabs:
+        qkv = torch.randn(slabs, batch, width, device="cuda", generator=g) * 0.3
+    else:
+        qkv = (torch.randn(batch, width, device="cuda", generator=g) * 0.5).bfloat16()
+    scale = 1.0 / math.sqrt(hd)
+    k1, v1, k2, v2 = kc.clone(), vc.clone(), kc.clone(), vc.clone()
+    rot = ext.rope_kv_write(qkv.clone(), pos, slots, k1, v1, nq, nkv, hd, bs, 1e6, bias if slabs else None)
+    want = ext.paged_attn_decode(rot, k1, v1, bt, ctx, nq, nkv, hd, scale, splits)
+    got = ext.rope_attn_decode(qkv, bias if slabs else None, pos, slots, k2, v2, bt, ctx, nq, nkv, hd, 1e6, scale,
+                               splits)
+    assert rel_l2(got, want) < 5e-3
+    assert torch.equal(v1, v2)
+    assert rel_l2(k2, k1) < 2e-3   # cos/sin come from a shared table here, from sincosf per element there
