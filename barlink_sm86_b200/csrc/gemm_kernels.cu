@@ -669,6 +669,282 @@ static int launch_w8(const blW8A16Args& a, cudaStream_t st, char* err, size_t er
   return 0;
 }
 
+// ---------------------------------------------------------------------------
+// Paired-CTA GEMM (opt-in, BL_GEMM_PAIR=1): two CTAs of a cluster work on one
+// 256 x 256 output tile.  Each CTA loads 128 rows of A and 128 rows of B per
+// k-block (32 KiB instead of the 48 KiB a lone CTA needs for 128 x 256), the
+// leader CTA issues tcgen05.mma.cta_group::2 (M = 256 over the pair, N = 256),
+// and each CTA's epilogue drains its own 128 accumulator rows.  The single-CTA
+// kernel at these sizes is bound by tile delivery from L2; the pair moves a
+// third less per SM.  Barrier protocol:
+//   full[s]   leader only: its producer arms it for both CTAs' bytes; both
+//             CTAs' TMA loads complete on the leader's barrier
+//   empty[s]  one per CTA: the leader's MMA thread commits to its own and to
+//             the peer's (two commits, the peer's through its cluster address)
+//   tfull[a]  one per CTA, committed the same way when a tile's MMAs are done
+//   tempty[a] leader only, 256 arrivals: every epilogue thread of both CTAs
+// Large, unsplit, token-major ("no swap") products only.
+// ---------------------------------------------------------------------------
+constexpr int kPairStages = 6;
+constexpr int kPairStageBytes = 2 * kTileA * kTileK * 2;  // A 16 KiB + B 16 KiB per CTA
+constexpr int kPairSmem = kPairStages * kPairStageBytes + 1024 + 1024;
+constexpr int kPairBN = 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const void* tmap, uint32_t leader_bar,
+                                                 int x, int y, uint64_t hint) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(smem_dst),
+      "l"(tmap), "r"(leader_bar), "r"(x), "r"(y), "l"(hint)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive (once every MMA issued so far is done) on a barrier given by its cluster address
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar_addr)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    k_gemm_pair(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                GemmShape g, LocalSink<kPairBN> sink, uint64_t hint_a, uint64_t hint_b) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (ring - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(gen + kPairStages * kPairStageBytes);
+  uint64_t* full_bar = bars;                       // kPairStages
+  uint64_t* empty_bar = bars + kPairStages;        // kPairStages
+  uint64_t* tfull_bar = bars + 2 * kPairStages;    // 2
+  uint64_t* tempty_bar = tfull_bar + 2;            // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile uint32_t* s_abort = reinterpret_cast<volatile uint32_t*>(tempty_bar + 3);
+
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cr = cluster_ctarank();           // 0 = leader
+  const uint32_t peer = cr ^ 1u;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int tiles_m = (g.ra + 255) / 256, tiles_n = (g.rb + 255) / 256;
+  const int units = tiles_m * tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 256);
+    }
+    *s_abort = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    // both CTAs of the pair allocate together (same warp index, same slot address)
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything arrives on them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+
+  if (warp == 0) {
+    // ------------------------------ producer (both CTAs) ------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      bool ok = true;
+      for (int u = pair; u < units && ok; u += n_pairs) {
+        const int tm = u / tiles_n, tn = u - tm * tiles_n;
+        for (int kb = 0; kb < g.kblocks; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, s_abort)) {
+            ok = false;
+            break;
+          }
+          const uint32_t leader_full = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (cr == 0) mbar_expect_tx(&full_bar[stage], 2 * kPairStageBytes);
+          const uint32_t dst = ring + stage * kPairStageBytes;
+          tma_load_2d_pair(dst, &tmap_a, leader_full, kb * kTileK, tm * 256 + int(cr) * 128, hint_a);
+          tma_load_2d_pair(dst + kTileA * kTileK * 2, &tmap_b, leader_full, kb * kTileK, tn * 256 + int(cr) * 128,
+                           hint_b);
+          ++issued;
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      (void)issued;
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader only) --------------
+    if (lane == 0 && cr == 0) {
+      const uint32_t idesc = umma_idesc_f16(256, kPairBN, g.ab_fmt);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t tphase[2] = {0, 0};
+      int it = 0;
+      bool ok = true;
+      for (int u = pair; u < units && ok; u += n_pairs, ++it) {
+        const int acc = it & 1;
+        if (!mbar_wait_bounded(&tempty_bar[acc], tphase[acc] ^ 1u, s_abort)) break;
+        tphase[acc] ^= 1u;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + uint32_t(acc * kPairBN);
+        for (int kb = 0; kb < g.kblocks; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, s_abort)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = ring + stage * kPairStageBytes;
+          const uint64_t da = umma_desc_k_sw128(sa);
+          const uint64_t db = umma_desc_k_sw128(sa + kTileA * kTileK * 2);
+#pragma unroll
+          for (int k = 0; k < kTileK / 16; ++k)
+            umma_f16_ss_pair(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          // the stage is free in both CTAs once these MMAs have read it
+          umma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 0));
+          umma_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 1));
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) {
+          umma_commit_pair(map_to_cta(smem_u32(&tfull_bar[acc]), 0));
+          umma_commit_pair(map_to_cta(smem_u32(&tfull_bar[acc]), 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both CTAs) ------------------
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    uint32_t tphase[2] = {0, 0};
+    int it = 0;
+    for (int u = pair; u < units; u += n_pairs, ++it) {
+      const int tm = u / tiles_n, tn = u - tm * tiles_n;
+      const int acc = it & 1;
+      if (!mbar_wait_bounded(&tfull_bar[acc], tphase[acc], s_abort)) break;
+      tphase[acc] ^= 1u;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * kPairBN);
+#pragma unroll 1
+      for (int c0 = 0; c0 < kPairBN; c0 += 32) {
+        float v[32];
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        // this CTA holds rows [tm*256 + cr*128, +128): the Sink's tile index is in units of 128 rows
+        sink(tm * 2 + int(cr), tn, 0, row, c0, v, 32);
+      }
+      tc_fence_before_sync();
+      mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves (or frees TMEM) while the other may still signal it
+  if (warp == 1) {
+    tc_fence_after_sync();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+  if (threadIdx.x == 0 && *s_abort && g.err) *g.err = 1u;
+}
+
+static bool gemm_pair_enabled() {
+  static const int v = env_int_or("BL_GEMM_PAIR", 0);
+  return v == 1;
+}
+
+// token-major product with at least 512 tokens, no k-split, no fused collective
+static bool gemm_pair_ok(const blGemmArgs& a) {
+  return gemm_pair_enabled() && !a.swap && a.ra >= 512 && a.rb >= 256 && !a.partial_out && !a.peer &&
+         !a.gate_flags && !a.weight_tiled && !a.silu_mul && a.splits <= 1;
+}
+
+static int launch_gemm_pair(const blGemmArgs& a, cudaStream_t st, char* err, size_t errlen) {
+  CUtensorMap ta, tb;
+  if (make_tmap_kmajor(a.a, a.ra, a.k, a.lda, kTileA, 2, &ta, err, errlen) != 0) return -1;
+  if (make_tmap_kmajor(a.b, a.rb, a.k, a.ldb, kTileA, 2, &tb, err, errlen) != 0) return -1;
+  GemmShape g{};
+  g.ra = a.ra;
+  g.rb = a.rb;
+  g.k = a.k;
+  g.kblocks = (a.k + kTileK - 1) / kTileK;
+  g.splits = 1;
+  g.ab_fmt = 1;
+  g.err = static_cast<uint32_t*>(a.err_flag);
+  LocalSink<kPairBN> sink;
+  sink.out = static_cast<__nv_bfloat16*>(a.out);
+  sink.bias = static_cast<const __nv_bfloat16*>(a.bias);
+  sink.residual = static_cast<const __nv_bfloat16*>(a.residual);
+  sink.ldo = a.ldo;
+  sink.ra = a.ra;
+  sink.rb = a.rb;
+  sink.swap = 0;
+  sink.epi = (a.bias ? 1 : 0) | (a.residual ? 2 : 0) | (a.gelu ? 8 : 0);
+  sink.scale = nullptr;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(k_gemm_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem);
+    if (e != cudaSuccess) {
+      set_err(err, errlen, "barlink: cannot raise shared memory to %d B: %s", kPairSmem, cudaGetErrorString(e));
+      return -1;
+    }
+    attr = true;
+  }
+  const int units = ((a.ra + 255) / 256) * ((a.rb + 255) / 256);
+  int pairs = sm_count() / 2;
+  if (pairs > units) pairs = units;
+  if (pairs < 1) pairs = 1;
+  // the cluster shape is compiled into the kernel (__cluster_dims__); the grid is a whole number of pairs
+  cudaError_t e = launch_k(k_gemm_pair, dim3(2 * pairs), dim3(kGemmThreads), size_t(kPairSmem), st, ta, tb, g, sink,
+                           kHintEvictLast, kHintEvictFirst);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_err(err, errlen, "barlink: paired GEMM launch failed: %s", cudaGetErrorString(e));
+    return -1;
+  }
+  return 0;
+}
+
 }  // namespace bl
 
 using namespace bl;
@@ -751,6 +1027,7 @@ extern "C" int bl_gemm_bf16(const blGemmArgs* a, void* stream, char* err, size_t
     return -1;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->bn <= 0 && gemm_pair_ok(*a)) return launch_gemm_pair(*a, st, err, errlen);
   int bn = a->bn;
   if (bn <= 0) {
     if (a->swap) bn = a->rb <= 16 ? 16 : a->rb <= 32 ? 32 : a->rb <= 64 ? 64 : a->rb <= 128 ? 128 : 256;

@@ -46,3 +46,37 @@ def test_fused_rope_attention_matches_the_two_kernel_path(ext, nq, nkv, slabs, s
     assert rel_l2(got, want) < 5e-3
     assert torch.equal(v1, v2)
     assert rel_l2(k2, k1) < 2e-3   # cos/sin come from a shared table here, from sincosf per element there
+
+
+PAIR_SCRIPT = r"""
+import os, sys, torch
+sys.path.insert(0, %r)
+from barlink_sm86_b200 import ops, load_extension
+C = load_extension()
+g = torch.Generator(device="cuda").manual_seed(0)
+worst = 0.0
+for m, n, k, extra in [(4608, 3072, 3072, "bias"), (1000, 300, 512, "none"), (512, 256, 64, "gelu"),
+                       (2304, 9216, 3072, "gelu"), (777, 1024, 1536, "residual"), (4608, 3072, 12288, "bias")]:
+    x = (torch.randn(m, k, device="cuda", generator=g) * 0.5).bfloat16()
+    w = (torch.randn(n, k, device="cuda", generator=g) / k ** 0.5).bfloat16()
+    b = torch.randn(n, device="cuda", generator=g).bfloat16()
+    res = torch.randn(m, n, device="cuda", generator=g).bfloat16() if extra == "residual" else None
+    y = ops.linear(x, w, None if extra == "none" else b, residual=res, gelu=extra == "gelu")
+    want = ops.ref.linear(x, w, None if extra == "none" else b, residual=res, gelu=extra == "gelu").float()
+    err = ((y.float() - want).norm() / want.norm()).item()
+    worst = max(worst, err)
+    assert err < 1e-2, (m, n, k, extra, err)
+torch.cuda.synchronize()
+assert C.gemm_error_flag(0) == 0
+print("PAIR OK worst rel-L2 %%.4f" %% worst)
+"""
+
+
+def test_paired_cta_gemm_matches_fp32():
+    """The cta_group::2 GEMM (BL_GEMM_PAIR=1, read once per process, hence the child process)."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, BL_GEMM_PAIR="1")
+    p = subprocess.run([sys.executable, "-c", PAIR_SCRIPT % root], capture_output=True, text=True, timeout=120, env=env)
+    assert p.returncode == 0 and "PAIR OK" in p.stdout, p.stdout[-1500:] + p.stderr[-3000:]
