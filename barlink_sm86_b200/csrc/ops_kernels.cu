@@ -688,6 +688,40 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   const int p1 = min(n_pages, p0 + per);
   const int* table = block_tables + size_t(b) * max_blocks;
 
+  // the first pages are requested before anything else, so that the preparation of q and of the
+  // new key/value below overlaps their flight
+  const uint32_t wbase = smem_u32(smem) + warp * kWarpSmem;
+  // pages of this warp: p0 + warp + i * kAttnWarps, i in [0, count)
+  const int count = p1 > p0 + warp ? (p1 - p0 - warp + kAttnWarps - 1) / kAttnWarps : 0;
+  int tbl = 0;        // lane l holds the table entry of page index (chunk * 32 + l)
+  int tbl_chunk = -1;
+  auto issue = [&](int i, int buf) {
+    if ((i >> 5) != tbl_chunk) {
+      tbl_chunk = i >> 5;
+      const int mine = tbl_chunk * 32 + lane;
+      tbl = mine < count ? table[p0 + warp + mine * kAttnWarps] : 0;
+    }
+    const int blk = __shfl_sync(0xffffffffu, tbl, i & 31);
+    const uint8_t* ks = reinterpret_cast<const uint8_t*>(k_cache) +
+                        (size_t(blk) * nkv + h) * (kPageTokens * kHd * 2);
+    const uint8_t* vs = reinterpret_cast<const uint8_t*>(v_cache) +
+                        (size_t(blk) * nkv + h) * (kPageTokens * kHd * 2);
+    const uint32_t kd = wbase + buf * 2 * kPageBytes, vd = kd + kPageBytes;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = lane + j * 32;  // 256 chunks of 16 B per page
+      const int r = c >> 4, cc = c & 15;
+      cp_async16(kd + r * kRowPitch + cc * 16, ks + c * 16);
+      cp_async16(vd + r * kRowPitch + cc * 16, vs + c * 16);
+    }
+  };
+
+  // prologue: kAttnStages - 1 pages in flight (one commit group per slot, empty when past the end)
+#pragma unroll
+  for (int i = 0; i < kAttnStages - 1; ++i) {
+    if (i < count) issue(i, i);
+    cp_async_commit();
+  }
   // cos / sin of this sequence's position for the 64 rotation pairs
   __shared__ float2 s_cs[kHd / 2];
   __shared__ __align__(16) __nv_bfloat16 s_new[2][kHd];  // rotated key, value of the new token
@@ -759,38 +793,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   for (int d = 0; d < kHd / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-  const uint32_t wbase = smem_u32(smem) + warp * kWarpSmem;
-  // pages of this warp: p0 + warp + i * kAttnWarps, i in [0, count)
-  const int count = p1 > p0 + warp ? (p1 - p0 - warp + kAttnWarps - 1) / kAttnWarps : 0;
-  int tbl = 0;        // lane l holds the table entry of page index (chunk * 32 + l)
-  int tbl_chunk = -1;
-  auto issue = [&](int i, int buf) {
-    if ((i >> 5) != tbl_chunk) {
-      tbl_chunk = i >> 5;
-      const int mine = tbl_chunk * 32 + lane;
-      tbl = mine < count ? table[p0 + warp + mine * kAttnWarps] : 0;
-    }
-    const int blk = __shfl_sync(0xffffffffu, tbl, i & 31);
-    const uint8_t* ks = reinterpret_cast<const uint8_t*>(k_cache) +
-                        (size_t(blk) * nkv + h) * (kPageTokens * kHd * 2);
-    const uint8_t* vs = reinterpret_cast<const uint8_t*>(v_cache) +
-                        (size_t(blk) * nkv + h) * (kPageTokens * kHd * 2);
-    const uint32_t kd = wbase + buf * 2 * kPageBytes, vd = kd + kPageBytes;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int c = lane + j * 32;  // 256 chunks of 16 B per page
-      const int r = c >> 4, cc = c & 15;
-      cp_async16(kd + r * kRowPitch + cc * 16, ks + c * 16);
-      cp_async16(vd + r * kRowPitch + cc * 16, vs + c * 16);
-    }
-  };
-
-  // prologue: kAttnStages - 1 pages in flight (one commit group per slot, empty when past the end)
-#pragma unroll
-  for (int i = 0; i < kAttnStages - 1; ++i) {
-    if (i < count) issue(i, i);
-    cp_async_commit();
-  }
   int buf = 0;
   for (int i = 0; i < count; ++i) {
     const int page = p0 + warp + i * kAttnWarps;
