@@ -68,6 +68,15 @@ c10d::Backend& BarlinkBackend::cpu(const char* what) {
   return *cpu_;
 }
 
+// A CUDA tensor in a group that the link does not serve (a subgroup of 2..world-1 ranks, e.g. the
+// tensor-parallel group of a TP x PP job): staged through host memory and the gloo companion.
+// Slow, but the group works; the hot groups (the whole world) never take this path.
+bool BarlinkBackend::host_staged(const at::Tensor& t) {
+  if (!t.is_cuda() || use_link_ || !cpu_) return false;
+  ++n_host_staged;
+  return true;
+}
+
 static void* cur_stream(const at::Tensor& t) {
   return at::cuda::getCurrentCUDAStream(t.device().index()).stream();
 }
@@ -316,6 +325,12 @@ c10::intrusive_ptr<c10d::Work> BarlinkBackend::allreduce(std::vector<at::Tensor>
     ++n_local;
     return done(c10d::OpType::ALLREDUCE, tensors);
   }
+  if (host_staged(t)) {
+    std::vector<at::Tensor> h{t.cpu()};
+    cpu_->allreduce(h, opts)->wait();
+    t.copy_(h[0]);
+    return done(c10d::OpType::ALLREDUCE, tensors);
+  }
   if (t.is_cuda()) {
     if (opts.reduceOp == c10d::ReduceOp::SUM) {
       allreduce_cuda(t);
@@ -343,6 +358,12 @@ c10::intrusive_ptr<c10d::Work> BarlinkBackend::broadcast(std::vector<at::Tensor>
   TORCH_CHECK(tensors.size() == 1, "barlink: broadcast takes one tensor");
   if (getSize() == 1) {
     ++n_local;
+    return done(c10d::OpType::BROADCAST, tensors);
+  }
+  if (host_staged(tensors[0])) {
+    std::vector<at::Tensor> h{tensors[0].cpu()};
+    cpu_->broadcast(h, opts)->wait();
+    tensors[0].copy_(h[0]);
     return done(c10d::OpType::BROADCAST, tensors);
   }
   if (tensors[0].is_cuda()) {
@@ -376,6 +397,12 @@ c10::intrusive_ptr<c10d::Work> BarlinkBackend::_allgather_base(at::Tensor& outpu
     output.copy_(input.reshape(output.sizes()));
     return done(c10d::OpType::_ALLGATHER_BASE, {output});
   }
+  if (host_staged(input)) {
+    at::Tensor ho = at::empty(output.sizes(), output.options().device(at::kCPU)), hi = input.cpu();
+    cpu_->_allgather_base(ho, hi, opts)->wait();
+    output.copy_(ho);
+    return done(c10d::OpType::_ALLGATHER_BASE, {output});
+  }
   if (input.is_cuda()) {
     allgather_cuda(output, input);
     return done(c10d::OpType::_ALLGATHER_BASE, {output});
@@ -391,6 +418,14 @@ c10::intrusive_ptr<c10d::Work> BarlinkBackend::allgather(
   if (getSize() == 1) {
     ++n_local;
     outputs[0][0].copy_(inputs[0]);
+    return done(c10d::OpType::ALLGATHER, outputs[0]);
+  }
+  if (host_staged(inputs[0])) {
+    std::vector<std::vector<at::Tensor>> ho(1);
+    for (auto& o : outputs[0]) ho[0].push_back(at::empty(o.sizes(), o.options().device(at::kCPU)));
+    std::vector<at::Tensor> hi{inputs[0].cpu()};
+    cpu_->allgather(ho, hi, opts)->wait();
+    for (size_t r = 0; r < outputs[0].size(); ++r) outputs[0][r].copy_(ho[0][r]);
     return done(c10d::OpType::ALLGATHER, outputs[0]);
   }
   if (inputs[0].is_cuda()) {
@@ -421,6 +456,12 @@ c10::intrusive_ptr<c10d::Work> BarlinkBackend::_reduce_scatter_base(
   if (getSize() == 1) {
     ++n_local;
     output.copy_(input.reshape(output.sizes()));
+    return done(c10d::OpType::_REDUCE_SCATTER_BASE, {output});
+  }
+  if (host_staged(input)) {
+    at::Tensor ho = at::empty(output.sizes(), output.options().device(at::kCPU)), hi = input.cpu();
+    cpu_->_reduce_scatter_base(ho, hi, opts)->wait();
+    output.copy_(ho);
     return done(c10d::OpType::_REDUCE_SCATTER_BASE, {output});
   }
   if (input.is_cuda()) {
@@ -557,6 +598,11 @@ c10::intrusive_ptr<c10d::Work> BarlinkBackend::alltoall_base(at::Tensor& output,
 c10::intrusive_ptr<c10d::Work> BarlinkBackend::send(std::vector<at::Tensor>& tensors, int dstRank,
                                                     int tag) {
   TORCH_CHECK(tensors.size() == 1, "barlink: send takes one tensor");
+  if (host_staged(tensors[0])) {
+    std::vector<at::Tensor> h{tensors[0].cpu()};
+    cpu_->send(h, dstRank, tag)->wait();
+    return done(c10d::OpType::SEND, {});
+  }
   if (tensors[0].is_cuda()) {
     send_cuda(tensors[0], dstRank);
     return done(c10d::OpType::SEND, {});
@@ -567,6 +613,12 @@ c10::intrusive_ptr<c10d::Work> BarlinkBackend::send(std::vector<at::Tensor>& ten
 c10::intrusive_ptr<c10d::Work> BarlinkBackend::recv(std::vector<at::Tensor>& tensors, int srcRank,
                                                     int tag) {
   TORCH_CHECK(tensors.size() == 1, "barlink: recv takes one tensor");
+  if (host_staged(tensors[0])) {
+    std::vector<at::Tensor> h{at::empty(tensors[0].sizes(), tensors[0].options().device(at::kCPU))};
+    cpu_->recv(h, srcRank, tag)->wait();
+    tensors[0].copy_(h[0]);
+    return done(c10d::OpType::RECV, tensors);
+  }
   if (tensors[0].is_cuda()) {
     recv_cuda(tensors[0], srcRank);
     return done(c10d::OpType::RECV, tensors);

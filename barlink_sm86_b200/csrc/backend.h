@@ -99,10 +99,11 @@ class BarlinkBackend : public c10d::Backend {
   ~BarlinkBackend() override { drain_sends(); }
 
   // counters for tests: how many ops took which path
-  int64_t n_zero_copy = 0, n_staged = 0, n_cpu = 0, n_local = 0;
+  int64_t n_zero_copy = 0, n_staged = 0, n_cpu = 0, n_local = 0, n_host_staged = 0;
 
  private:
   c10::intrusive_ptr<c10d::Work> done(c10d::OpType op, std::vector<at::Tensor> outs);
+  bool host_staged(const at::Tensor& t);
   void allreduce_cuda(at::Tensor& t);
   void allreduce_other_cuda(at::Tensor& t, const c10d::ReduceOp& op);
   void allgather_cuda(at::Tensor& out, const at::Tensor& in);

@@ -1024,7 +1024,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_readonly("n_zero_copy", &blpg::BarlinkBackend::n_zero_copy)
       .def_readonly("n_staged", &blpg::BarlinkBackend::n_staged)
       .def_readonly("n_cpu", &blpg::BarlinkBackend::n_cpu)
-      .def_readonly("n_local", &blpg::BarlinkBackend::n_local);
+      .def_readonly("n_local", &blpg::BarlinkBackend::n_local)
+      .def_readonly("n_host_staged", &blpg::BarlinkBackend::n_host_staged);
 
   bind_extra(m);
 }

@@ -8,7 +8,8 @@ Capability parity with the reference's backend module
 * the Backend class itself is C++ (`_C.BarlinkBackend`); this module only
   resolves the device, brings the link up and hands both to the class;
 * 2..8 ranks instead of exactly 2; groups of one member are local no-ops;
-  groups of 2..world-1 members get CPU (gloo) service only;
+  groups of 2..world-1 members are served by the gloo companion (CUDA tensors
+  are staged through host memory: functional, not fast);
 * the rendezvous socket path is agreed through the c10d store instead of a
   fixed /tmp name, so two jobs on one host cannot collide
   (`BL_SOCK_PATH` still overrides it);

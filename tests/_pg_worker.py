@@ -232,6 +232,20 @@ for op, want_fn in ((dist.ReduceOp.MAX, lambda v: max(v)), (dist.ReduceOp.MIN, l
     vals = [float(r + 2) for r in range(world)]
     want = want_fn(vals) if want_fn else float(torch.tensor(vals).prod())
     assert torch.allclose(t, torch.full_like(t, want)), (op, t, want)
+# a subgroup of 2 ranks inside a larger world: served through host memory by the gloo companion
+if world >= 4:
+    pairs = [dist.new_group([2 * i, 2 * i + 1]) for i in range(world // 2)]
+    mine = pairs[rank // 2]
+    t = torch.full((1000,), float(rank + 1), device=dev)
+    dist.all_reduce(t, group=mine)
+    lo = 2 * (rank // 2)
+    assert torch.all(t == float(lo + 1 + lo + 2)), t[:4]
+    gathered = torch.empty(2 * 8, device=dev)
+    dist.all_gather_into_tensor(gathered, torch.full((8,), float(rank), device=dev), group=mine)
+    assert torch.equal(gathered.cpu(), torch.tensor([float(lo)] * 8 + [float(lo + 1)] * 8))
+    assert blpg.backend_of(mine).n_host_staged >= 2
+    log("subgroup service ok")
+
 # all_to_all with equal splits: rank r sends value 100*r + d to rank d
 src = torch.stack([torch.full((3,), float(100 * rank + d), device=dev) for d in range(world)]).view(-1)
 dst = torch.empty_like(src)
