@@ -39,6 +39,9 @@ def load_extension(required=True):
     global _C_MODULE, _C_ERROR
     if _C_MODULE is not None:
         return _C_MODULE
+    if "barlink_sm86_b200._C" in sys.modules:  # adopted from an in-process build
+        _C_MODULE = sys.modules["barlink_sm86_b200._C"]
+        return _C_MODULE
     try:
         import torch  # noqa: F401  (also makes libc10/libtorch resolvable for the .so)
     except ImportError as e:  # pragma: no cover

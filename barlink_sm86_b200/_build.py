@@ -47,6 +47,13 @@ def so_path():
 
 def build(verbose=False):
     """Compile (or incrementally rebuild) the extension; returns the module."""
+    if "barlink_sm86_b200._C" in sys.modules:
+        # already loaded in this process: rebuild in a child (importing the shared object a second
+        # time would register its classes twice); the running process keeps the module it has
+        import subprocess
+
+        subprocess.check_call([sys.executable, os.path.abspath(__file__)] + (["-v"] if verbose else []))
+        return sys.modules["barlink_sm86_b200._C"]
     from torch.utils import cpp_extension
 
     os.makedirs(BUILD_DIR, exist_ok=True)
@@ -64,6 +71,9 @@ def build(verbose=False):
         with_cuda=True,
         verbose=verbose,
     )
+    # the build imports the module; the package must use this instance (loading the
+    # same shared object a second time would register its classes twice)
+    sys.modules["barlink_sm86_b200._C"] = mod
     return mod
 
 
