@@ -102,3 +102,37 @@ def test_package_imports_without_a_gpu():
     assert callable(bl.init) and callable(bl.allreduce_into) and callable(bl.copy_large)
     import barlink_sm86 as old
     assert old.init is bl.init
+
+
+def test_mmdit_batches_are_independent_and_sampler_runs():
+    """Two samples in one batch give the same rows as each sample alone (joint attention
+    must not mix sequences), and the Euler sampler walks the requested number of steps."""
+    from barlink_sm86_b200.models import MMDiTConfig, MMDiTModel, MMDiTWeights, denoise, grid_positions
+    cfg = MMDiTConfig.tiny()
+    m = MMDiTModel(cfg, MMDiTWeights(cfg, "cpu", torch.float32, 3))
+    g = torch.Generator().manual_seed(1)
+    img = torch.randn(2, 16, cfg.in_channels, generator=g)
+    txt = torch.randn(2, 8, cfg.txt_dim, generator=g)
+    t = torch.tensor([0.7, 0.2])
+    pos = grid_positions(4, 4, "cpu")
+    both = m.forward(img, txt, t, pos)
+    for b in range(2):
+        one = m.forward(img[b:b + 1], txt[b:b + 1], t[b:b + 1], pos)
+        assert torch.allclose(both[b:b + 1], one, atol=1e-4, rtol=1e-4)
+    calls = []
+    orig = m.forward
+    m.forward = lambda *a, **k: (calls.append(float(a[2][0])), orig(*a, **k))[1]
+    out = denoise(m, img, txt, pos, steps=3)
+    assert out.shape == img.shape and torch.isfinite(out).all()
+    assert calls == pytest.approx([1.0, 2.0 / 3.0, 1.0 / 3.0])
+    assert m.flops_per_forward(1, 4096, 512) > 0
+
+
+def test_no_comm_control_skips_collectives():
+    from barlink_sm86_b200.parallel import TPComm
+    c = TPComm.single()
+    c.world, c.no_comm = 2, True           # a two-rank communicator whose collectives are switched off
+    x = torch.ones(4, 8)
+    assert c.all_reduce(x) is x and c.ar_calls == 0
+    normed, res = c.allreduce_rmsnorm(x, torch.zeros_like(x), torch.ones(8), 1e-6)
+    assert torch.allclose(res, x) and normed.shape == x.shape
