@@ -61,3 +61,15 @@ def test_tensor_parallel_model(world):
     if world not in _worlds():
         pytest.skip("needs %d GPUs" % world)
     print(_run_ranks("_tp_worker.py", world))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_single_process_mode_on_real_gpus(world):
+    """One process drives N GPUs (the reference's original mode: bl.init(devices, pool_mb))."""
+    if world not in _worlds():
+        pytest.skip("needs %d GPUs" % world)
+    import subprocess
+    import sys
+    p = subprocess.run([sys.executable, os.path.join(HERE, "_sp_worker.py"), str(world)], capture_output=True,
+                       text=True, timeout=300)
+    assert p.returncode == 0 and "single-process mode" in p.stdout, p.stdout[-2000:] + p.stderr[-3000:]
