@@ -640,24 +640,26 @@ struct QkvSrc {
   const __nv_bfloat16* bias;
   int width;
 };
-// elements (col, col + 1) of row `row`; col even
-__device__ __forceinline__ float2 qkv_pair(const QkvSrc& s, int row, int col) {
+// element `col` of row `row`.  Slabs are added in split order (four loads in flight at a time),
+// then the bias, then the sum is rounded to bf16: the same bits as k_rope_kv_write produces.
+__device__ __forceinline__ float qkv_elem(const QkvSrc& s, int row, int col) {
   if (s.slabs) {
-    const size_t e = size_t(row) * s.width + col;
-    float a = 0.f, c = 0.f;
-    for (int sp = 0; sp < s.nsplit; ++sp) {
-      const float2 v = __ldcg(reinterpret_cast<const float2*>(s.slabs + sp * s.slab + e));
-      a += v.x;
-      c += v.y;
+    const float* p = s.slabs + size_t(row) * s.width + col;
+    float acc = 0.f;
+    int sp = 0;
+    for (; sp + 4 <= s.nsplit; sp += 4) {
+      const float a0 = __ldcg(p + size_t(sp) * s.slab), a1 = __ldcg(p + size_t(sp + 1) * s.slab),
+                  a2 = __ldcg(p + size_t(sp + 2) * s.slab), a3 = __ldcg(p + size_t(sp + 3) * s.slab);
+      acc += a0;
+      acc += a1;
+      acc += a2;
+      acc += a3;
     }
-    if (s.bias) {
-      const float2 bb = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(s.bias + col));
-      a += bb.x;
-      c += bb.y;
-    }
-    return unpack_bf16x2(pack_bf16x2(a, c));
+    for (; sp < s.nsplit; ++sp) acc += __ldcg(p + size_t(sp) * s.slab);
+    if (s.bias) acc += __bfloat162float(s.bias[col]);
+    return __bfloat162float(__float2bfloat16(acc));
   }
-  return unpack_bf16x2(*reinterpret_cast<const uint32_t*>(s.qkv + size_t(row) * s.q_stride + col));
+  return __bfloat162float(s.qkv[size_t(row) * s.q_stride + col]);
 }
 
 // k_paged_attn_decode with the kernel before it folded in: the query heads and
@@ -724,6 +726,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   }
   // cos / sin of this sequence's position for the 64 rotation pairs
   __shared__ float2 s_cs[kHd / 2];
+  __shared__ __align__(16) __nv_bfloat16 s_q[16][kHd];   // rotated query heads of this group (rows < G)
   __shared__ __align__(16) __nv_bfloat16 s_new[2][kHd];  // rotated key, value of the new token
   const float pos = float(positions[b]);
   if (threadIdx.x < kHd / 2) {
@@ -735,58 +738,48 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   __syncthreads();
   const int last_page = n_pages - 1;
   const bool owns_last = last_page >= p0 && last_page < p1;
-  if (owns_last && warp == 0) {
-    // new key (rotated) and value of KV head h: lane l owns dims 2l, 2l+1 and 64+2l, 65+2l
-    const int kcol = (nq + h) * kHd, vcol = (nq + nkv + h) * kHd;
-    const float2 lo = qkv_pair(src, b, kcol + 2 * lane), hi = qkv_pair(src, b, kcol + 64 + 2 * lane);
-    const float2 c0 = s_cs[2 * lane], c1 = s_cs[2 * lane + 1];
-    const uint32_t klo = pack_bf16x2(lo.x * c0.x - hi.x * c0.y, lo.y * c1.x - hi.y * c1.y);
-    const uint32_t khi = pack_bf16x2(hi.x * c0.x + lo.x * c0.y, hi.y * c1.x + lo.y * c1.y);
-    const float2 v0 = qkv_pair(src, b, vcol + 2 * lane), v1 = qkv_pair(src, b, vcol + 64 + 2 * lane);
-    const uint32_t vlo = pack_bf16x2(v0.x, v0.y), vhi = pack_bf16x2(v1.x, v1.y);
-    reinterpret_cast<uint32_t*>(s_new[0])[lane] = klo;
-    reinterpret_cast<uint32_t*>(s_new[0])[32 + lane] = khi;
-    reinterpret_cast<uint32_t*>(s_new[1])[lane] = vlo;
-    reinterpret_cast<uint32_t*>(s_new[1])[32 + lane] = vhi;
-    const int slot = slots[b];
-    if (slot >= 0) {
-      const size_t row = (size_t(slot / kPageTokens) * nkv + h) * kPageTokens + slot % kPageTokens;
-      uint32_t* kc = reinterpret_cast<uint32_t*>(k_cache + row * kHd);
-      uint32_t* vc = reinterpret_cast<uint32_t*>(v_cache + row * kHd);
-      kc[lane] = klo;
-      kc[32 + lane] = khi;
-      vc[lane] = vlo;
-      vc[32 + lane] = vhi;
+  {
+    // one rotation pair (i, i + 64) per thread and step, consecutive threads on consecutive
+    // columns: rows 0..G-1 are the query heads, G the new key, G + 1 the new value
+    const int rows = owns_last ? G + 2 : G;
+    for (int p = threadIdx.x; p < rows * (kHd / 2); p += blockDim.x) {
+      const int hh = p / (kHd / 2), i = p % (kHd / 2);
+      const int col = hh < G ? (h * G + hh) * kHd : hh == G ? (nq + h) * kHd : (nq + nkv + h) * kHd;
+      const float x1 = qkv_elem(src, b, col + i), x2 = qkv_elem(src, b, col + i + kHd / 2);
+      __nv_bfloat16 o1, o2;
+      if (hh <= G) {
+        const float2 cs = s_cs[i];
+        o1 = __float2bfloat16(x1 * cs.x - x2 * cs.y);
+        o2 = __float2bfloat16(x2 * cs.x + x1 * cs.y);
+      } else {
+        o1 = __float2bfloat16(x1);
+        o2 = __float2bfloat16(x2);
+      }
+      __nv_bfloat16* dst = hh < G ? s_q[hh] : s_new[hh - G];
+      dst[i] = o1;
+      dst[i + kHd / 2] = o2;
     }
   }
   __syncthreads();
-
-  // Q fragments (rows = heads of this group, zero beyond G), rotated: the partner of
-  // dim d < 64 is d + 64, i.e. the same thread's fragment four k-steps further on
-  uint32_t qa[kHd / 16][4];
-  {
-    const int qcol = h * G * kHd;
-#pragma unroll
-    for (int ks = 0; ks < kHd / 32; ++ks) {
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {          // columns c and c + 8
-        const int c = ks * 16 + 2 * t + half * 8;      // < 64
-        const float2 c0 = s_cs[c], c1 = s_cs[c + 1];
-#pragma unroll
-        for (int rr = 0; rr < 2; ++rr) {               // rows g and g + 8
-          const int r = g + rr * 8;
-          uint32_t lo_o = 0u, hi_o = 0u;
-          if (r < G) {
-            const float2 lo = qkv_pair(src, b, qcol + r * kHd + c);
-            const float2 hi = qkv_pair(src, b, qcol + r * kHd + c + 64);
-            lo_o = pack_bf16x2(lo.x * c0.x - hi.x * c0.y, lo.y * c1.x - hi.y * c1.y);
-            hi_o = pack_bf16x2(hi.x * c0.x + lo.x * c0.y, hi.y * c1.x + lo.y * c1.y);
-          }
-          qa[ks][half * 2 + rr] = lo_o;
-          qa[ks + 4][half * 2 + rr] = hi_o;
-        }
-      }
+  if (owns_last && warp == 0) {
+    // the block that owns the last page stores the new row to the cache (8 bytes per lane)
+    const int slot = slots[b];
+    if (slot >= 0) {
+      const size_t row = (size_t(slot / kPageTokens) * nkv + h) * kPageTokens + slot % kPageTokens;
+      reinterpret_cast<uint2*>(k_cache + row * kHd)[lane] = reinterpret_cast<const uint2*>(s_new[0])[lane];
+      reinterpret_cast<uint2*>(v_cache + row * kHd)[lane] = reinterpret_cast<const uint2*>(s_new[1])[lane];
     }
+  }
+
+  // Q fragments (rows = heads of this group, zero beyond G)
+  uint32_t qa[kHd / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < kHd / 16; ++ks) {
+    const int c = ks * 16 + 2 * t;
+    qa[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(&s_q[g][c]) : 0u;
+    qa[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(&s_q[g + 8][c]) : 0u;
+    qa[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(&s_q[g][c + 8]) : 0u;
+    qa[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(&s_q[g + 8][c + 8]) : 0u;
   }
   float o[kHd / 8][4];
 #pragma unroll
