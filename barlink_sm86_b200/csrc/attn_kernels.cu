@@ -4,7 +4,9 @@
 // text+image attention of the MMDiT blocks (non-causal): one CTA per 64-query
 // tile and head, K/V streamed in 64-key tiles through a cp.async double
 // buffer, QK^T and PV on tensor cores with an online softmax.  Sequences are
-// packed and described by cumulative lengths.  The reference takes this op
+// packed and described by cumulative lengths.  This mma.sync kernel is the
+// fallback (BL_ATTN_TC=0, or callers that do not pass the longest key length);
+// attn_tc_kernels.cu is the tcgen05 kernel used otherwise.  The reference takes this op
 // from HF transformers / diffusers attention (demos/flux2_tp/worker.py:96-123,
 // demos/qwen_tp/qwen38_int8/worker.py:282-291).
 #include <stdio.h>
