@@ -116,11 +116,29 @@ def _randn(shape, seed, device, dtype, std=0.02):
     return (torch.randn(shape, generator=g, device=device, dtype=torch.float32) * std).to(dtype)
 
 
+class RandomSource:
+    """Full (unsharded) tensors of a seeded random-init model: N(0, 0.02) weights and biases,
+    unit norm weights.  Every tensor has its own generator seed, so any rank can draw any
+    tensor without drawing the others."""
+
+    def __init__(self, seed, device, dtype):
+        self.base, self.device, self.dtype = seed * 1000003, device, dtype
+
+    def weight(self, name, layer, shape, slot):
+        off = self.base + layer * 64 + slot if layer >= 0 else self.base + slot
+        return _randn(shape, off, self.device, self.dtype)
+
+    def norm(self, name, layer, n):
+        return torch.ones(n, dtype=self.dtype, device=self.device)
+
+
 class Qwen2Weights:
-    """Per-rank shards of a seeded random-init model."""
+    """Per-rank shards of a model: seeded random-init by default, or the tensors of `source`
+    (an object with `weight(name, layer, shape, slot)` and `norm(name, layer, n)` that returns
+    FULL tensors, e.g. `utils.checkpoint.SafetensorsSource`)."""
 
     def __init__(self, cfg: Qwen2Config, tp: int, rank: int, device, dtype, seed: int = 0,
-                 layers: Optional[int] = None, tiled: Optional[bool] = None, quant: str = "none"):
+                 layers: Optional[int] = None, tiled: Optional[bool] = None, quant: str = "none", source=None):
         """quant: "none" (bf16), "w8a16" (every linear int8 per-channel, the
         reference's INT8 demo, demos/qwen_tp/qwen38_int8/worker.py:97-150) or
         "w4a16" (MLP int4 group-128, the rest int8: demos/qwen_tp/worker.py:1-25).
@@ -139,39 +157,38 @@ class Qwen2Weights:
         self.plan = head_plan(cfg.n_heads, cfg.n_kv_heads, tp, rank)
         n_layers = cfg.layers if layers is None else layers
         self.layers = []
-        base = seed * 1000003
+        src = source if source is not None else RandomSource(seed, device, dtype)
         unit = tp * (128 if quant == "w4a16" else 8)  # shards stay 16-byte multiples (int4: whole groups)
         inter_pad = -(-cfg.intermediate // unit) * unit
         self.inter_local = inter_pad // tp
         for l in range(n_layers):
-            s = base + l * 64
-            wq = _randn((cfg.n_heads * hd, H), s + 1, device, dtype)
-            wk = _randn((cfg.n_kv_heads * hd, H), s + 2, device, dtype)
-            wv = _randn((cfg.n_kv_heads * hd, H), s + 3, device, dtype)
+            wq = src.weight("q_proj.weight", l, (cfg.n_heads * hd, H), 1)
+            wk = src.weight("k_proj.weight", l, (cfg.n_kv_heads * hd, H), 2)
+            wv = src.weight("v_proj.weight", l, (cfg.n_kv_heads * hd, H), 3)
             wqkv = torch.cat([gather_heads(wq, self.plan.q_heads, hd),
                               gather_heads(wk, self.plan.kv_heads, hd),
                               gather_heads(wv, self.plan.kv_heads, hd)], 0).contiguous()
             del wq, wk, wv
             bqkv = None
             if cfg.qkv_bias:
-                bq = _randn((cfg.n_heads * hd,), s + 4, device, dtype)
-                bk = _randn((cfg.n_kv_heads * hd,), s + 5, device, dtype)
-                bv = _randn((cfg.n_kv_heads * hd,), s + 6, device, dtype)
+                bq = src.weight("q_proj.bias", l, (cfg.n_heads * hd,), 4)
+                bk = src.weight("k_proj.bias", l, (cfg.n_kv_heads * hd,), 5)
+                bv = src.weight("v_proj.bias", l, (cfg.n_kv_heads * hd,), 6)
                 bqkv = torch.cat([gather_heads(bq[:, None], self.plan.q_heads, hd)[:, 0],
                                   gather_heads(bk[:, None], self.plan.kv_heads, hd)[:, 0],
                                   gather_heads(bv[:, None], self.plan.kv_heads, hd)[:, 0]]).contiguous()
-            wo_full = _randn((H, cfg.n_heads * hd), s + 7, device, dtype)
+            wo_full = src.weight("o_proj.weight", l, (H, cfg.n_heads * hd), 7)
             wo = gather_head_cols(wo_full, self.plan.q_heads, hd).contiguous()
             wo_scale = ops.ref.quantize_w8(wo_full)[1] if quant != "none" else None
             del wo_full
-            gate = _randn((cfg.intermediate, H), s + 8, device, dtype)
-            up = _randn((cfg.intermediate, H), s + 9, device, dtype)
+            gate = src.weight("gate_proj.weight", l, (cfg.intermediate, H), 8)
+            up = src.weight("up_proj.weight", l, (cfg.intermediate, H), 9)
             if inter_pad != cfg.intermediate:
                 z = torch.zeros(inter_pad - cfg.intermediate, H, dtype=dtype, device=device)
                 gate, up = torch.cat([gate, z], 0), torch.cat([up, z], 0)
             wgu = interleave_gate_up(shard_rows(gate, tp, rank), shard_rows(up, tp, rank))
             del gate, up
-            down = _randn((H, cfg.intermediate), s + 10, device, dtype)
+            down = src.weight("down_proj.weight", l, (H, cfg.intermediate), 10)
             if inter_pad != cfg.intermediate:
                 down = torch.cat([down, torch.zeros(H, inter_pad - cfg.intermediate, dtype=dtype,
                                                     device=device)], 1)
@@ -188,11 +205,11 @@ class Qwen2Weights:
                 wqkv, wo, wgu, wdown = (ops.tile_weight(t) for t in (wqkv, wo, wgu, wdown))
             self.layers.append(dict(
                 wqkv=wqkv, bqkv=bqkv, wo=wo, wgu=wgu, wdown=wdown,
-                ln1=torch.ones(H, dtype=dtype, device=device),
-                ln2=torch.ones(H, dtype=dtype, device=device)))
-        self.embed = _randn((cfg.vocab, H), base + 900001, device, dtype)
+                ln1=src.norm("input_layernorm.weight", l, H),
+                ln2=src.norm("post_attention_layernorm.weight", l, H)))
+        self.embed = src.weight("embed_tokens.weight", -1, (cfg.vocab, H), 900001)
         vocab_pad = -(-cfg.vocab // tp) * tp
-        head = _randn((cfg.vocab, H), base + 900002, device, dtype)
+        head = src.weight("lm_head.weight", -1, (cfg.vocab, H), 900002)
         if vocab_pad != cfg.vocab:
             head = torch.cat([head, torch.zeros(vocab_pad - cfg.vocab, H, dtype=dtype, device=device)], 0)
         self.vocab_local = vocab_pad // tp
@@ -202,7 +219,7 @@ class Qwen2Weights:
             self.lm_head = W8Weight(self.lm_head)
         elif tiled:
             self.lm_head = ops.tile_weight(self.lm_head)
-        self.ln_f = torch.ones(H, dtype=dtype, device=device)
+        self.ln_f = src.norm("norm.weight", -1, H)
 
     @staticmethod
     def dense(w):
@@ -243,7 +260,7 @@ class PagedKV:
 
 class Qwen2Model:
     def __init__(self, cfg: Qwen2Config, comm: Optional[TPComm] = None, device="cpu",
-                 dtype=torch.float32, seed=0, layers=None, quant="none", shard_of=None):
+                 dtype=torch.float32, seed=0, layers=None, quant="none", shard_of=None, source=None):
         """shard_of=(tp, rank): hold that rank's shard of a tp-way split while
         running alone (collectives are no-ops, results are partial sums): the
         per-rank compute of a larger tensor-parallel job, for tuning on one GPU."""
@@ -251,7 +268,7 @@ class Qwen2Model:
         self.comm = comm or TPComm(None)
         self.device, self.dtype = torch.device(device), dtype
         tp, rank = shard_of if shard_of is not None else (self.comm.world, self.comm.rank)
-        self.w = Qwen2Weights(cfg, tp, rank, self.device, dtype, seed, layers, quant=quant)
+        self.w = Qwen2Weights(cfg, tp, rank, self.device, dtype, seed, layers, quant=quant, source=source)
         self.nq, self.nkv, self.hd = self.w.plan.nq, self.w.plan.nkv, cfg.head_dim
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
 

@@ -35,6 +35,9 @@ sys.path.insert(0, ROOT)
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="qwen25_7b", choices=["qwen25_7b", "qwen25_32b", "tiny"])
+    ap.add_argument("--checkpoint", default=None,
+                    help="directory with a Hugging Face style Qwen2 checkpoint (safetensors + config.json); "
+                         "overrides --model, every rank streams and shards it")
     ap.add_argument("--quant", default="none", choices=["none", "w8a16", "w4a16"])
     ap.add_argument("--backend", default="barlink", choices=["barlink", "nccl", "gloo"])
     ap.add_argument("--batch", type=int, default=1)
@@ -80,7 +83,12 @@ def main():
            "tiny": Qwen2Config.tiny}[a.model]()
     dtype = torch.float32 if cpu else torch.bfloat16
     t0 = time.time()
-    model = Qwen2Model(cfg, comm, dev, dtype, seed=0, layers=a.layers or None, quant=a.quant)
+    source = None
+    if a.checkpoint:
+        from barlink_sm86_b200.utils import SafetensorsSource
+        source = SafetensorsSource(a.checkpoint, dev, dtype)
+        cfg = source.config()
+    model = Qwen2Model(cfg, comm, dev, dtype, seed=0, layers=a.layers or None, quant=a.quant, source=source)
     load_s = time.time() - t0
 
     g = torch.Generator().manual_seed(a.seed)

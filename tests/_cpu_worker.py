@@ -82,6 +82,34 @@ elif mode == "tiny":
         cos = torch.cosine_similarity(b.flatten(), ref_l.flatten(), dim=0).item()
         print("tiny %s TP=%d max abs logit error %.2e, cosine vs unquantised %.4f" % (quant, world, err, cos))
         assert err < 1e-3 and cos > (0.99 if quant == "w8a16" else 0.9), (quant, err, cos)
+elif mode == "checkpoint":
+    # export a random model as a Hugging Face style checkpoint (rank 0), load it back sharded on every rank
+    import tempfile
+    from barlink_sm86_b200.models import Qwen2Config, Qwen2Model
+    from barlink_sm86_b200.parallel import TPComm
+    from barlink_sm86_b200.utils import SafetensorsSource, save_qwen2_safetensors
+    cfg = Qwen2Config.tiny()
+    one = Qwen2Model(cfg, TPComm.single(), "cpu", torch.float32, seed=4)
+    for L in one.w.layers:  # norm weights other than one, so that a swapped norm would show
+        L["ln1"].uniform_(0.5, 1.5, generator=torch.Generator().manual_seed(1))
+        L["ln2"].uniform_(0.5, 1.5, generator=torch.Generator().manual_seed(2))
+    d = os.path.join(tempfile.gettempdir(), "bl-ckpt-test-%d" % port)
+    if rank == 0:
+        save_qwen2_safetensors(one, d, shard_bytes=4 << 20)   # several shards
+    dist.barrier()
+    src = SafetensorsSource(d, "cpu", torch.float32)
+    c2 = src.config()
+    assert (c2.hidden, c2.layers, c2.n_heads, c2.n_kv_heads, c2.head_dim, c2.intermediate, c2.vocab, c2.qkv_bias) == \
+        (cfg.hidden, cfg.layers, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.intermediate, cfg.vocab, cfg.qkv_bias)
+    tp = Qwen2Model(c2, TPComm(dist.group.WORLD), "cpu", torch.float32, source=src)
+    ids = torch.randint(0, cfg.vocab, (2, 24), generator=torch.Generator().manual_seed(3), dtype=torch.int32)
+    err = (tp.logits(tp.prefill(ids)) - one.logits(one.prefill(ids))).abs().max().item()
+    print("checkpoint round trip TP=%d max abs logit error %.2e" % (world, err))
+    assert err < 1e-4, err
+    dist.barrier()
+    if rank == 0:
+        import shutil
+        shutil.rmtree(d, ignore_errors=True)
 elif mode == "mmdit":
     from barlink_sm86_b200.models import MMDiTConfig, MMDiTModel, MMDiTWeights, grid_positions
     from barlink_sm86_b200.parallel import TPComm

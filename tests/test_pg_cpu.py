@@ -59,6 +59,12 @@ def test_tiny_qwen2_tp8_replicated_kv_heads():
     assert all(rc == 0 for rc, _ in res), "\n".join(o for _, o in res)
 
 
+def test_checkpoint_export_and_sharded_load():
+    res = _run("checkpoint", 2)
+    assert all(rc == 0 for rc, _ in res), "\n".join(o for _, o in res)
+    assert "checkpoint round trip" in res[0][1]
+
+
 def test_tiny_mmdit_tp2_matches_single_rank():
     res = _run("mmdit", 2)
     assert all(rc == 0 for rc, _ in res), "\n".join(o for _, o in res)
