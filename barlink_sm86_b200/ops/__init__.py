@@ -239,6 +239,12 @@ def attention(q, k, v, cu_q, cu_k, max_q, scale, causal, max_k=0):
 
 
 def w8a16_linear(x, wq, scale, bias=None, silu_mul=False):
+    """scale [n]: per output channel, the tcgen05 kernel that widens int8 in its main loop.
+    scale [n, k/group]: per-group scales cannot be folded into the epilogue; the weight is
+    widened once (scaled per group) and the bf16 GEMM runs on it."""
+    if x.is_cuda and scale.dim() == 2:
+        w = ref.w8_dequant(wq, scale).to(torch.bfloat16)
+        return linear(x, w, bias, silu_mul=silu_mul)
     if x.is_cuda:
         _count()
         return _C().w8a16_linear(x, wq, scale, bias, silu_mul)

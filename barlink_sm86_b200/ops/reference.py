@@ -192,10 +192,34 @@ def quantize_w8(weight):
     return wq, scale
 
 
+def w8_dequant(wq, scale):
+    """int8 [n, k] with per-channel scales [n] or per-group scales [n, k/group] -> fp32 [n, k]."""
+    if scale.dim() == 1:
+        return wq.float() * scale.float()[:, None]
+    n, k = wq.shape
+    g = scale.shape[1]
+    return (wq.float().view(n, g, k // g) * scale.float()[:, :, None]).view(n, k)
+
+
+def quantize_w8_grouped(weight, group=128):
+    """Symmetric int8 with one scale per (output channel, group of `group` inputs): the
+    granularity of the reference's kernel (torch_ext/barlink_sm86/w8a16.cu:13-24)."""
+    w = weight.float()
+    n, k = w.shape
+    wg = w.view(n, k // group, group)
+    scale = (wg.abs().amax(2).clamp_min(1e-12) / 127.0).to(torch.bfloat16)
+    wq = torch.round(wg / scale.float()[:, :, None]).clamp(-127, 127).to(torch.int8).view(n, k)
+    return wq, scale
+
+
 def w8a16_linear(x, wq, scale, bias=None, silu_mul=False):
-    """y = x @ (wq * scale[:, None]).T: bf16 activations, int8 weights widened
-    exactly to bf16, fp32 accumulation, per-channel scale applied at the end."""
-    y = (x.float() @ wq.float().t()) * scale.float()[None, :]
+    """y = x @ (wq * scale).T: bf16 activations, int8 weights widened exactly to
+    bf16, fp32 accumulation; scale per output channel [n] (applied at the end) or
+    per group [n, k/group] (applied to the weights)."""
+    if scale.dim() == 2:
+        y = x.float() @ w8_dequant(wq, scale).t()
+    else:
+        y = (x.float() @ wq.float().t()) * scale.float()[None, :]
     if bias is not None:
         y = y + bias.float()
     if silu_mul:

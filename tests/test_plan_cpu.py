@@ -136,3 +136,19 @@ def test_no_comm_control_skips_collectives():
     assert c.all_reduce(x) is x and c.ar_calls == 0
     normed, res = c.allreduce_rmsnorm(x, torch.zeros_like(x), torch.ones(8), 1e-6)
     assert torch.allclose(res, x) and normed.shape == x.shape
+
+
+def test_w8_group_scales_match_dense_product():
+    g = torch.Generator().manual_seed(2)
+    w = torch.randn(48, 256, generator=g) * 0.05
+    w[:, :128] *= 8.0                       # groups with very different ranges: where group scales matter
+    x = torch.randn(5, 256, generator=g)
+    wq, sg = ref.quantize_w8_grouped(w, 128)
+    assert wq.dtype == torch.int8 and sg.shape == (48, 2)
+    yg = ref.w8a16_linear(x, wq, sg)
+    wq1, s1 = ref.quantize_w8(w)
+    y1 = ref.w8a16_linear(x, wq1, s1)
+    want = x @ w.t()
+    eg, e1 = (yg - want).norm() / want.norm(), (y1 - want).norm() / want.norm()
+    assert eg < 1e-2 and eg < e1            # finer scales, smaller error
+    assert torch.allclose(ref.w8_dequant(wq, sg), w, atol=float(sg.float().max()) * 0.51)
