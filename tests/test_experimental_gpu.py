@@ -80,3 +80,26 @@ def test_paired_cta_gemm_matches_fp32():
     env = dict(os.environ, BL_GEMM_PAIR="1")
     p = subprocess.run([sys.executable, "-c", PAIR_SCRIPT % root], capture_output=True, text=True, timeout=120, env=env)
     assert p.returncode == 0 and "PAIR OK" in p.stdout, p.stdout[-1500:] + p.stderr[-3000:]
+
+
+@pytest.mark.parametrize("nq,nkv", [(4, 1), (3, 3)])
+def test_tensor_core_attention_causal_with_longer_keys(ext, nq, nkv):
+    """Causal attention where the keys start before the queries (a later chunk of a chunked
+    prefill): the last query sees the last key, both kernels against the fp32 statement."""
+    from barlink_sm86_b200.ops import reference as ref
+    hd = 128
+    lens_q = [70, 1, 129, 300]
+    lens_k = [200, 64, 129, 813]
+    g = torch.Generator(device="cuda").manual_seed(nq)
+    cu_q = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32, device="cuda")
+    cu_k = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int32, device="cuda")
+    q = torch.randn(sum(lens_q), nq, hd, device="cuda", generator=g).bfloat16()
+    k = torch.randn(sum(lens_k), nkv, hd, device="cuda", generator=g).bfloat16()
+    v = torch.randn(sum(lens_k), nkv, hd, device="cuda", generator=g).bfloat16()
+    scale = 1.0 / math.sqrt(hd)
+    want = ref.attention(q, k, v, cu_q.cpu(), cu_k.cpu(), scale, True)
+    got_tc = ext.attn_fwd(q, k, v, cu_q, cu_k, max(lens_q), scale, True, max(lens_k))
+    got_mma = ext.attn_fwd(q, k, v, cu_q, cu_k, max(lens_q), scale, True)
+    assert ext.attn_error_flag(0) == 0
+    assert rel_l2(got_tc, want) < 1e-2
+    assert rel_l2(got_mma, want) < 1e-2
