@@ -69,7 +69,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt", type=int, default=1024)
+    ap.add_argument("--limit", type=int, default=240,
+                    help="seconds after which the process dumps its stacks and exits: a stuck collective "
+                         "must not hold the GPUs (this script once stopped making progress at 4 ranks "
+                         "inside a captured graph; the cause is not known)")
     args = ap.parse_args()
+    import faulthandler
+    faulthandler.dump_traceback_later(args.limit, exit=True)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     lr = int(os.environ.get("LOCAL_RANK", "0"))
