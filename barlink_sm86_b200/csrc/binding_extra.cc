@@ -197,7 +197,11 @@ at::Tensor w8a16_linear(const at::Tensor& x, const at::Tensor& wq, const at::Ten
     at::Tensor w = at::empty({n, k}, x.options());
     BL_CHECK(bl_w8_dequant(wq.data_ptr(), scale.data_ptr(), w.data_ptr(), n, k, st, err, errlen));
     py::object lin = py::module_::import("barlink_sm86_b200").attr("load_extension")().attr("linear");
-    return lin(x, w, bias ? py::cast(*bias) : py::none(), py::none(), silu_mul).cast<at::Tensor>();
+    // `w` was written by the kernel just launched: the GEMM must not fetch weight tiles ahead of
+    // that kernel's completion (its producer otherwise requests them before griddepcontrol.wait)
+    using namespace pybind11::literals;
+    return lin(x, w, bias ? py::cast(*bias) : py::none(), py::none(), silu_mul, "dynamic_weights"_a = true)
+        .cast<at::Tensor>();
   }
   W8Scratch& s = w8_scratch(dev);
   blW8A16Args a;

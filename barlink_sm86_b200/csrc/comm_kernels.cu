@@ -121,7 +121,7 @@ __device__ __forceinline__ bool block_sync_peers(const Comm& c, int proto, int s
 // The last block of this rank to arrive advances the epoch.  All blocks have
 // read the epoch before they arrive, so none can see the new value.
 __device__ __forceinline__ void finish_epoch(const Comm& c, int proto, uint32_t e, uint32_t aux,
-                                             bool set_aux) {
+                                             bool set_aux, bool staged = false) {
   __syncthreads();
   if (threadIdx.x == 0) {
     uint32_t* s = sig_of(c, c.rank);
@@ -130,10 +130,18 @@ __device__ __forceinline__ void finish_epoch(const Comm& c, int proto, uint32_t 
     if (t == gridDim.x - 1) {
       s[sig_ticket(proto)] = 0;
       if (set_aux) s[sig_aux(proto)] = aux;
+      if (staged) s[kSigStageSeq] = s[kSigStageSeq] + 1u;  // every block read it before it arrived here
       __threadfence();
       *reinterpret_cast<volatile uint32_t*>(&s[sig_epoch(proto)]) = e + 1;
     }
   }
+}
+
+// Offset of the staging buffer this call uses (see kSigStageSeq); same on every rank because
+// every rank issues the same sequence of staged collectives.
+__device__ __forceinline__ size_t stage_buf_off(const Comm& c) {
+  const uint32_t seq = ld_volatile_u32(sig_of(c, c.rank) + kSigStageSeq);
+  return c.stage_off + size_t(seq & 1u) * (2 * size_t(c.world) * c.stage_slice);
 }
 
 // ---- element semantics ------------------------------------------------------
@@ -533,7 +541,8 @@ __global__ void __launch_bounds__(kThreads) k_staged(CollArgs a) {
     size_t b = size_t(r) * sv;
     return b >= total ? 0 : (total - b < sv ? total - b : sv);
   };
-  char* my_stage = c.base[rank] + c.stage_off;
+  const size_t sbuf = stage_buf_off(c);
+  char* my_stage = c.base[rank] + sbuf;
   const size_t half = size_t(world) * c.stage_slice;  // inbox half, then outbox half
   bool ok = true;
 
@@ -543,7 +552,7 @@ __global__ void __launch_bounds__(kThreads) k_staged(CollArgs a) {
       int p = rank + k;
       if (p >= world) p -= world;
       const size_t len = slice_len(p);
-      char* dst = c.base[p] + c.stage_off + size_t(rank) * c.stage_slice;
+      char* dst = c.base[p] + sbuf + size_t(rank) * c.stage_slice;
       for (size_t j = first; j < len; j += stride) st_v4(dst + j * 16, in[size_t(p) * bs + j]);
     }
     ok = block_sync_peers(c, proto, blockIdx.x, e * 4 + 1);
@@ -566,7 +575,7 @@ __global__ void __launch_bounds__(kThreads) k_staged(CollArgs a) {
           for (int k = 1; k < world; ++k) {
             int p = rank + k;
             if (p >= world) p -= world;
-            st_v4(c.base[p] + c.stage_off + half + size_t(rank) * c.stage_slice + j * 16, res);
+            st_v4(c.base[p] + sbuf + half + size_t(rank) * c.stage_slice + j * 16, res);
           }
         }
       }
@@ -578,7 +587,7 @@ __global__ void __launch_bounds__(kThreads) k_staged(CollArgs a) {
       for (int k = 1; k < world; ++k) {
         int p = rank + k;
         if (p >= world) p -= world;
-        st_v4(c.base[p] + c.stage_off + half + size_t(rank) * c.stage_slice + j * 16, v);
+        st_v4(c.base[p] + sbuf + half + size_t(rank) * c.stage_slice + j * 16, v);
       }
     }
   } else {
@@ -588,7 +597,7 @@ __global__ void __launch_bounds__(kThreads) k_staged(CollArgs a) {
         for (int k = 1; k < world; ++k) {
           int p = rank + k;
           if (p >= world) p -= world;
-          st_v4(c.base[p] + c.stage_off + half + size_t(rank) * c.stage_slice + j * 16, v);
+          st_v4(c.base[p] + sbuf + half + size_t(rank) * c.stage_slice + j * 16, v);
         }
       }
   }
@@ -610,7 +619,7 @@ __global__ void __launch_bounds__(kThreads) k_staged(CollArgs a) {
       }
     }
   }
-  finish_epoch(c, proto, e, 0, false);
+  finish_epoch(c, proto, e, 0, false, true);
 }
 
 // ---------------------------------------------------------------------------
@@ -640,8 +649,9 @@ __global__ void __launch_bounds__(kThreads) k_nvls(CollArgs a) {
     size_t b = size_t(r) * sv;
     return b >= total ? 0 : (total - b < sv ? total - b : sv);
   };
-  char* stage = c.base[rank] + c.stage_off;
-  char* mstage = c.mc + c.stage_off;
+  const size_t sbuf = stage_buf_off(c);
+  char* stage = c.base[rank] + sbuf;
+  char* mstage = c.mc + sbuf;
   for (int r = 0; r < world; ++r) {
     const size_t len = slice_len(r);
     for (size_t j = first; j < len; j += stride)
@@ -665,7 +675,7 @@ __global__ void __launch_bounds__(kThreads) k_nvls(CollArgs a) {
       for (size_t j = first; j < len; j += stride)
         out[size_t(r) * sv + j] = ld_volatile_v4(stage + (size_t(r) * sv + j) * 16);
     }
-  finish_epoch(c, P_NVLS, e, 0, false);
+  finish_epoch(c, P_NVLS, e, 0, false, true);
 }
 
 // ---------------------------------------------------------------------------
@@ -765,12 +775,13 @@ __global__ void __launch_bounds__(kThreads) k_verify(CollArgs a) {
   const size_t stride = size_t(gridDim.x) * blockDim.x;
   const size_t first = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   const size_t half = size_t(world) * c.stage_slice;
+  const size_t sbuf = stage_buf_off(c);
   for (int p = 0; p < world; ++p) {
-    char* dst = c.base[p] + c.stage_off + size_t(rank) * c.stage_slice;
+    char* dst = c.base[p] + sbuf + size_t(rank) * c.stage_slice;
     for (size_t i = first; i < a.nvec; i += stride) st_v4(dst + i * 16, pat_vec(rank, p, i, a.seed));
   }
   if (c.mc) {
-    char* dst = c.mc + c.stage_off + half + size_t(rank) * c.stage_slice;
+    char* dst = c.mc + sbuf + half + size_t(rank) * c.stage_slice;
     for (size_t i = first; i < a.nvec; i += stride)
       multimem_st_v4(dst + i * 16, pat_vec(rank, 255, i, a.seed));
     __threadfence_system();
@@ -779,11 +790,11 @@ __global__ void __launch_bounds__(kThreads) k_verify(CollArgs a) {
   unsigned long long bad = 0;
   if (ok) {
     for (int r = 0; r < world; ++r) {
-      const char* src = c.base[rank] + c.stage_off + size_t(r) * c.stage_slice;
+      const char* src = c.base[rank] + sbuf + size_t(r) * c.stage_slice;
       for (size_t i = first; i < a.nvec; i += stride)
         bad += bad_bytes(ld_volatile_v4(src + i * 16), pat_vec(r, rank, i, a.seed));
       if (c.mc) {
-        const char* m = c.base[rank] + c.stage_off + half + size_t(r) * c.stage_slice;
+        const char* m = c.base[rank] + sbuf + half + size_t(r) * c.stage_slice;
         for (size_t i = first; i < a.nvec; i += stride)
           bad += bad_bytes(ld_volatile_v4(m + i * 16), pat_vec(r, 255, i, a.seed));
       }
@@ -794,7 +805,7 @@ __global__ void __launch_bounds__(kThreads) k_verify(CollArgs a) {
   if (bad) atomicAdd_system(a.bad, bad);
   // nobody may start the next pattern before everyone has checked this one
   if (ok) block_sync_peers(c, P_VERIFY, blockIdx.x, e * 4 + 2);
-  finish_epoch(c, P_VERIFY, e, 0, false);
+  finish_epoch(c, P_VERIFY, e, 0, false, true);
 }
 
 __global__ void k_probe(CollArgs a, unsigned long long* res) {

@@ -137,8 +137,10 @@ Layout compute_layout(size_t pool_bytes, int world) {
   L.lamport_slice =
       round_down(std::min<size_t>(std::max<size_t>(pool_bytes / 256, K64 / 2), 1u << 20), 4096);
   L.lamport_off = round_down(L.p2p_off - 3 * size_t(world) * L.lamport_slice, K64);
-  L.stage_slice = round_down(pool_bytes / 4 / (2 * size_t(world)), 4096);
-  L.stage_off = round_down(L.lamport_off - 2 * size_t(world) * L.stage_slice, K64);
+  // two staging buffers (taken in turn by successive staged collectives), each with an inbox
+  // half and an outbox half of world slices
+  L.stage_slice = round_down(pool_bytes / 4 / (4 * size_t(world)), 4096);
+  L.stage_off = round_down(L.lamport_off - 4 * size_t(world) * L.stage_slice, K64);
   L.user_bytes = L.stage_off;
   return L;
 }

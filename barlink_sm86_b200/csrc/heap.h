@@ -49,6 +49,11 @@ enum Proto : int {
 
 // word indices inside the pad
 constexpr int kSigAbort = 0;
+// Count of collectives of this rank that went through the staging zone (any protocol).  Call n
+// uses staging buffer n & 1: a rank can only be two staged calls ahead of a peer after that
+// peer has left the earlier one (every staged kernel waits for all peers at least once), so a
+// buffer is never written while a peer still reads the previous call's data from it.
+constexpr int kSigStageSeq = 1;
 __host__ __device__ constexpr int sig_epoch(int proto) { return 16 + proto; }
 __host__ __device__ constexpr int sig_ticket(int proto) { return 48 + proto; }
 __host__ __device__ constexpr int sig_aux(int proto) { return 80 + proto; }
@@ -66,7 +71,8 @@ struct Comm {
   char* base[kMaxRanks];  // every rank's arena as mapped in this process
   char* mc;               // multicast mapping of the arenas, or nullptr
   size_t sig_off;         // signal pad
-  size_t stage_off;       // staging zone: world slices of stage_slice bytes, twice
+  size_t stage_off;       // staging zone: two buffers of (inbox half, outbox half), each half
+                          // world slices of stage_slice bytes
   size_t stage_slice;     // capacity per source rank
   size_t lamport_off;     // 3 buffers of world * lamport_slice bytes
   size_t lamport_slice;

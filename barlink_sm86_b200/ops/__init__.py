@@ -74,16 +74,19 @@ def _w(weight):
     return weight, 0, 0
 
 
-def linear(x, weight, bias=None, residual=None, silu_mul=False, out=None, gate_tokens=0, gelu=False):
+def linear(x, weight, bias=None, residual=None, silu_mul=False, out=None, gate_tokens=0, gelu=False,
+           dynamic_weights=False):
     """y = x @ weight.T (+ bias) (tanh-GELU if `gelu`) (+ residual).
     gate_tokens > 0: x is the all-gather buffer of the fused tensor-parallel
-    path; the kernel waits for the peers' rows before it reads x."""
+    path; the kernel waits for the peers' rows before it reads x.
+    dynamic_weights: `weight` was written by a kernel earlier in this stream
+    (not at load time), so its tiles must not be fetched ahead of that kernel."""
     if x.is_cuda:
         _count()
         x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
         w, tn, tk = _w(weight)
         y = _C().linear(x2, w, bias, residual, silu_mul, out, gate_tokens=gate_tokens, tiled_n=tn,
-                        tiled_k=tk, gelu=gelu)
+                        tiled_k=tk, gelu=gelu, dynamic_weights=dynamic_weights)
         return y if x.dim() == 2 else y.view(*x.shape[:-1], y.shape[-1])
     y = ref.linear(x, weight, bias, residual, silu_mul, gelu)
     if out is not None:
@@ -244,7 +247,7 @@ def w8a16_linear(x, wq, scale, bias=None, silu_mul=False):
     widened once (scaled per group) and the bf16 GEMM runs on it."""
     if x.is_cuda and scale.dim() == 2:
         w = ref.w8_dequant(wq, scale).to(torch.bfloat16)
-        return linear(x, w, bias, silu_mul=silu_mul)
+        return linear(x, w, bias, silu_mul=silu_mul, dynamic_weights=True)
     if x.is_cuda:
         _count()
         return _C().w8a16_linear(x, wq, scale, bias, silu_mul)

@@ -69,10 +69,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt", type=int, default=1024)
+    ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--limit", type=int, default=240,
                     help="seconds after which the process dumps its stacks and exits: a stuck collective "
-                         "must not hold the GPUs (this script once stopped making progress at 4 ranks "
-                         "inside a captured graph; the cause is not known)")
+                         "must not hold the GPUs")
     args = ap.parse_args()
     import faulthandler
     faulthandler.dump_traceback_later(args.limit, exit=True)
@@ -156,13 +156,32 @@ def main():
     for _ in range(args.warmup):
         graph.replay()
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        graph.replay()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
+    # same timing procedure as bench.py: sampler first, about a second of untimed stepping, then
+    # the K-step region `--reps` times from the same context length, median reported
+    from barlink_sm86_b200.utils import ClockSampler
+    import statistics
+    sampler = ClockSampler(lr)
+    sampler.start()
+    t_load = time.perf_counter()
+    while time.perf_counter() - t_load < 1.0:
+        pos.fill_(S)
+        for _ in range(8):
+            graph.replay()
+        torch.cuda.synchronize()
+    rep_ms = []
+    for _ in range(max(1, args.reps)):
+        pos.fill_(S)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record()
+        barrier()
+        rep_ms.append(e0.elapsed_time(e1))
+    clocks = sampler.stop()
+    ms = statistics.median(rep_ms)
+    pos.fill_(S)
     h_in = torch.zeros(B, dtype=torch.long).pin_memory()
     h_out = torch.zeros(B, dtype=torch.long).pin_memory()
     t0 = time.perf_counter()
@@ -189,8 +208,22 @@ def main():
             "e2e": {"value": round(B * args.steps / (e2e / 1e3), 1), "unit": "tokens/s",
                     "ms_per_step": round(e2e / args.steps, 4), "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8},
             "all_reduce_calls_per_step": ar_calls[0] // max(1, 4),
+            "clocks": clocks, "rep_ms_per_step": [round(x / args.steps, 4) for x in rep_ms],
+            "nccl_nvls": os.environ.get("NCCL_NVLS_ENABLE", "default (on when the fabric supports it)"),
         }))
     if world > 1:
+        # The captured graph holds NCCL kernels of this communicator: release it (and let every
+        # replay finish) before the communicator goes away.  Destroying the process group with
+        # the graph still alive left the ranks stuck after the result line at 4 GPUs.
+        dist.barrier()
+        torch.cuda.synchronize()
+        graph.reset()
+        del graph
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        faulthandler.cancel_dump_traceback_later()
+        faulthandler.dump_traceback_later(30, exit=True)  # a teardown that still sticks ends here
         dist.destroy_process_group()
     return 0
 

@@ -14,7 +14,7 @@ MB = 1 << 20
 def test_layout_zones_are_ordered_aligned_and_disjoint(world, pool_mb):
     L = C.layout_of(pool_mb * MB, world)
     assert 0 < L["user_bytes"] == L["stage_off"]
-    stage_end = L["stage_off"] + 2 * world * L["stage_slice"]
+    stage_end = L["stage_off"] + 4 * world * L["stage_slice"]
     lamport_end = L["lamport_off"] + 3 * world * L["lamport_slice"]
     p2p_end = L["p2p_off"] + world * L["p2p_slice"]
     assert stage_end <= L["lamport_off"] and lamport_end <= L["p2p_off"] and p2p_end <= L["sig_off"] < L["pool_bytes"]

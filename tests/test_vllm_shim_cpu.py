@@ -87,3 +87,27 @@ def test_shim_off_and_step_selection(fake_vllm, monkeypatch):
     _fresh_shim()
     assert dist.init_process_group is sentinel  # steps 1, 2 off
     assert fake_vllm["vllm.platforms.cuda"].CudaPlatformBase.dist_backend == "barlink"
+
+
+def test_entry_trampoline_installs_the_hook_in_the_child(tmp_path):
+    """`entry.py script.py` must leave torch.distributed.init_process_group wrapped in the
+    re-executed interpreter (and unwrapped with BL_SHIM_OFF=1)."""
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "probe.py"
+    script.write_text(
+        "import os, torch.distributed as dist\n"
+        "print('WRAPPED=%d SHIM=%s' % (int(getattr(dist.init_process_group, '_barlink_wrapped', False)),"
+        " os.environ.get('BL_SHIM', '')))\n")
+    env = {k: v for k, v in os.environ.items() if not k.startswith("BL_SHIM") and k != "PYTHONPATH"}
+    entry = os.path.join(root, "vllm_barlink", "entry.py")
+    out = subprocess.run([sys.executable, entry, str(script)], env=env, capture_output=True, text=True,
+                         timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert "WRAPPED=1 SHIM=1" in out.stdout, out.stdout + out.stderr
+    env["BL_SHIM_OFF"] = "1"
+    out = subprocess.run([sys.executable, entry, str(script)], env=env, capture_output=True, text=True,
+                         timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert "WRAPPED=0" in out.stdout, out.stdout + out.stderr
