@@ -20,6 +20,7 @@ SOURCES = [
     "heap.cc",
     "comm_kernels.cu",
     "gemm_kernels.cu",
+    "dlin_kernels.cu",
     "ops_kernels.cu",
     "attn_kernels.cu",
     "attn_tc_kernels.cu",

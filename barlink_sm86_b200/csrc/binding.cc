@@ -425,7 +425,7 @@ py::dict stats() {
 // compute ops
 // ---------------------------------------------------------------------------
 struct Scratch {
-  at::Tensor ws, counters, err_flag, attn;
+  at::Tensor ws, counters, err_flag, attn, attn_counters;
 };
 Scratch& scratch_for(int dev) {
   static std::map<int, Scratch> m;
@@ -437,6 +437,7 @@ Scratch& scratch_for(int dev) {
   s.counters = at::zeros({16384}, o.dtype(at::kInt));
   s.err_flag = at::zeros({4}, o.dtype(at::kInt));
   s.attn = at::empty({int64_t(64) << 20}, o.dtype(at::kByte));
+  s.attn_counters = at::zeros({65536}, o.dtype(at::kInt));
   return m.emplace(dev, s).first->second;
 }
 
@@ -852,12 +853,32 @@ void decode_advance(const at::Tensor& positions, const at::Tensor& ctx_lens, con
                              int(block_tables.size(1)), block_size, stream_of(positions), err, errlen));
 }
 
-at::Tensor argmax_merge(const at::Tensor& pairs) {
+// per-slice (value, index bits) pairs of every row: float32 [chunks, rows, 2]
+at::Tensor argmax_parts(const at::Tensor& logits, int offset, c10::optional<at::Tensor> out_opt) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kBFloat16 && logits.dim() == 2 &&
+                  logits.stride(1) == 1,
+              "barlink: argmax needs 2-D bfloat16 CUDA logits");
+  const int rows = int(logits.size(0)), n = int(logits.size(1));
+  at::Tensor parts = out_opt ? *out_opt
+                             : at::empty({bl_argmax_chunks(), rows, 2}, logits.options().dtype(at::kFloat));
+  TORCH_CHECK(parts.is_cuda() && parts.is_contiguous() && parts.scalar_type() == at::kFloat &&
+                  parts.numel() == int64_t(bl_argmax_chunks()) * rows * 2,
+              "barlink: argmax_parts out must be contiguous float32 [chunks, rows, 2]");
+  c10::cuda::CUDAGuard guard(logits.device());
+  if (rows > 0)
+    BL_CHECK(bl_argmax_parts(logits.data_ptr(), rows, n, int(logits.stride(0)), offset, parts.data_ptr(),
+                             stream_of(logits), err, errlen));
+  return parts;
+}
+
+at::Tensor argmax_merge(const at::Tensor& pairs, c10::optional<at::Tensor> out_opt) {
   TORCH_CHECK(pairs.is_cuda() && pairs.scalar_type() == at::kFloat && pairs.dim() == 3 &&
                   pairs.size(2) == 2 && pairs.is_contiguous(),
               "barlink: argmax_merge needs float32 [world, rows, 2] (value, index bits)");
   const int world = int(pairs.size(0)), rows = int(pairs.size(1));
-  at::Tensor idx = at::empty({rows}, pairs.options().dtype(at::kInt));
+  at::Tensor idx = out_opt ? *out_opt : at::empty({rows}, pairs.options().dtype(at::kInt));
+  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kInt && idx.is_contiguous() && idx.numel() == rows,
+              "barlink: argmax_merge out must be contiguous int32 [rows]");
   c10::cuda::CUDAGuard guard(pairs.device());
   BL_CHECK(bl_argmax_merge(pairs.data_ptr(), world, rows, idx.data_ptr<int>(), stream_of(pairs), err,
                            errlen));
@@ -900,7 +921,8 @@ at::Tensor paged_attn_decode(const at::Tensor& qkv, const at::Tensor& k_cache,
 at::Tensor rope_attn_decode(const at::Tensor& qkv, const c10::optional<at::Tensor>& bias,
                             const at::Tensor& positions, const at::Tensor& slots, at::Tensor& k_cache,
                             at::Tensor& v_cache, const at::Tensor& block_tables, const at::Tensor& ctx_lens,
-                            int nq, int nkv, int hd, double theta, double scale, int splits) {
+                            int nq, int nkv, int hd, double theta, double scale, int splits,
+                            bool merge_in_kernel) {
   const bool slabs = qkv.scalar_type() == at::kFloat && qkv.dim() == 3;
   TORCH_CHECK(qkv.is_cuda() && qkv.is_contiguous() &&
                   (slabs || (qkv.scalar_type() == at::kBFloat16 && qkv.dim() == 2)),
@@ -932,7 +954,9 @@ at::Tensor rope_attn_decode(const at::Tensor& qkv, const c10::optional<at::Tenso
                                  slots.data_ptr<int>(), float(theta), k_cache.data_ptr(), v_cache.data_ptr(),
                                  block_tables.data_ptr<int>(), ctx_lens.data_ptr<int>(), out.data_ptr(), batch,
                                  nq, nkv, hd, int(k_cache.size(2)), int(block_tables.size(1)), float(scale),
-                                 splits, s.attn.data_ptr(), size_t(s.attn.nbytes()), stream_of(qkv), err, errlen));
+                                 splits, s.attn.data_ptr(), size_t(s.attn.nbytes()),
+                                 merge_in_kernel ? s.attn_counters.data_ptr() : nullptr, stream_of(qkv), err,
+                                 errlen));
   return out;
 }
 
@@ -1001,13 +1025,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding", &embedding, py::arg("ids"), py::arg("table"), py::arg("vocab_lo") = 0,
         py::arg("out") = py::none());
   m.def("argmax", &argmax, py::arg("logits"), py::arg("offset") = 0);
-  m.def("argmax_merge", &argmax_merge);
+  m.def("argmax_merge", &argmax_merge, py::arg("pairs"), py::arg("out") = py::none());
+  m.def("argmax_parts", &argmax_parts, py::arg("logits"), py::arg("offset") = 0, py::arg("out") = py::none());
   m.def("decode_advance", &decode_advance, py::arg("positions"), py::arg("ctx_lens"), py::arg("slots"),
         py::arg("block_tables"), py::arg("ids"), py::arg("sampled") = py::none(),
         py::arg("block_size") = 16);
   m.def("rope_attn_decode", &rope_attn_decode, py::arg("qkv"), py::arg("bias"), py::arg("positions"),
         py::arg("slots"), py::arg("k_cache"), py::arg("v_cache"), py::arg("block_tables"), py::arg("ctx_lens"),
-        py::arg("nq"), py::arg("nkv"), py::arg("hd"), py::arg("theta"), py::arg("scale"), py::arg("splits") = 0);
+        py::arg("nq"), py::arg("nkv"), py::arg("hd"), py::arg("theta"), py::arg("scale"), py::arg("splits") = 0,
+        py::arg("merge_in_kernel") = true);
   m.def("paged_attn_decode", &paged_attn_decode, py::arg("qkv"), py::arg("k_cache"),
         py::arg("v_cache"), py::arg("block_tables"), py::arg("ctx_lens"), py::arg("nq"),
         py::arg("nkv"), py::arg("hd"), py::arg("scale"), py::arg("splits") = 0,

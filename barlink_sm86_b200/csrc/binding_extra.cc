@@ -8,6 +8,8 @@
 #include <torch/csrc/utils/pybind.h>
 #include <torch/extension.h>
 
+#include <map>
+
 #include "backend.h"
 #include "bl_core.h"
 #include "bl_ops.h"
@@ -178,8 +180,22 @@ W8Scratch& w8_scratch(int dev) {
 // y = x @ (wq * scale[:, None]).T (+ bias): bf16 activations, int8 per-channel
 // weights widened to bf16 inside the tcgen05 main loop (<= 256 tokens); more
 // tokens widen the weight once and use the bf16 GEMM.
+// bf16 group scales [n, groups] -> (row_max bf16 [n], rel fp16 [n, groups]): done once per weight
+std::tuple<at::Tensor, at::Tensor> w8_group_scales(const at::Tensor& scales) {
+  check_bf16x(scales, "scales");
+  TORCH_CHECK(scales.dim() == 2, "barlink: group scales must be [n, groups]");
+  const int n = int(scales.size(0)), groups = int(scales.size(1));
+  at::Tensor row = at::empty({n}, scales.options());
+  at::Tensor rel = at::empty({n, groups}, scales.options().dtype(at::kHalf));
+  c10::cuda::CUDAGuard guard(scales.device());
+  void* st = at::cuda::getCurrentCUDAStream(scales.device().index()).stream();
+  BL_CHECK(bl_w8_group_scales(scales.data_ptr(), n, groups, row.data_ptr(), rel.data_ptr(), st, err, errlen));
+  return {row, rel};
+}
+
 at::Tensor w8a16_linear(const at::Tensor& x, const at::Tensor& wq, const at::Tensor& scale,
-                        const c10::optional<at::Tensor>& bias, bool silu_mul, int splits) {
+                        const c10::optional<at::Tensor>& bias, bool silu_mul, int splits,
+                        const c10::optional<at::Tensor>& group_rel) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
               "barlink: x must be a 2-D bfloat16 CUDA tensor with unit inner stride");
   TORCH_CHECK(wq.is_cuda() && wq.is_contiguous() && wq.scalar_type() == at::kChar && wq.dim() == 2 &&
@@ -193,6 +209,12 @@ at::Tensor w8a16_linear(const at::Tensor& x, const at::Tensor& wq, const at::Ten
   void* st = at::cuda::getCurrentCUDAStream(dev).stream();
   at::Tensor out = at::empty({m, silu_mul ? n / 2 : n}, x.options());
   if (m == 0) return out;
+  if (group_rel) {
+    TORCH_CHECK(group_rel->is_cuda() && group_rel->is_contiguous() && group_rel->scalar_type() == at::kHalf &&
+                    group_rel->dim() == 2 && group_rel->size(0) == n && k % group_rel->size(1) == 0,
+                "barlink: group_rel must be contiguous float16 [n, k / group] (see w8_group_scales)");
+    TORCH_CHECK(m <= 256, "barlink: in-kernel group scales take at most 256 tokens");
+  }
   if (m > 256) {
     at::Tensor w = at::empty({n, k}, x.options());
     BL_CHECK(bl_w8_dequant(wq.data_ptr(), scale.data_ptr(), w.data_ptr(), n, k, st, err, errlen));
@@ -213,6 +235,10 @@ at::Tensor w8a16_linear(const at::Tensor& x, const at::Tensor& wq, const at::Ten
   a.n = n;
   a.k = k;
   a.scale = scale.data_ptr();
+  if (group_rel) {
+    a.group_rel = group_rel->data_ptr();
+    a.group_k = k / int(group_rel->size(1));
+  }
   if (bias) {
     check_bf16x(*bias, "bias");
     TORCH_CHECK(bias->numel() == n, "barlink: bias must have n entries");
@@ -376,6 +402,139 @@ void gate_residual(const at::Tensor& x, const at::Tensor& y, const at::Tensor& g
 }
 
 // ---- host-only internals, exposed so that they can be unit-tested without a GPU ----
+
+// ---- decode linears with the collective folded in (dlin_kernels.cu) ----------------------
+struct DlinScratch {
+  at::Tensor sync, err_flag;
+};
+DlinScratch& dlin_scratch(int dev) {
+  static std::map<int, DlinScratch> m;
+  auto it = m.find(dev);
+  if (it != m.end()) return it->second;
+  auto o = at::TensorOptions().device(at::kCUDA, dev).dtype(at::kInt);
+  DlinScratch s;
+  s.sync = at::zeros({4}, o);
+  s.err_flag = at::zeros({4}, o);
+  return m.emplace(dev, s).first->second;
+}
+int dlin_error_flag(int dev) { return dlin_scratch(dev).err_flag.cpu()[0].item<int>(); }
+
+// a one-rank stand-in for the link in ordinary device memory (single-GPU runs of the same kernels)
+at::Tensor dlin_local_link(int tokens, int hidden, int dev) {
+  c10::cuda::CUDAGuard guard(c10::Device(at::kCUDA, dev));
+  at::Tensor buf = at::empty({int64_t(bl_dlin_local_link_bytes(tokens, hidden))},
+                             at::TensorOptions().device(at::kCUDA, dev).dtype(at::kByte));
+  void* st = at::cuda::getCurrentCUDAStream(dev).stream();
+  BL_CHECK(bl_dlin_local_link_init(buf.data_ptr(), tokens, hidden, st, err, errlen));
+  return buf;
+}
+
+void dlin_fill_common(blDlinArgs& a, const at::Tensor& x, int hidden, const c10::optional<at::Tensor>& link,
+                      int dev) {
+  a.x = x.data_ptr();
+  a.tokens = int(x.size(0));
+  a.ldx = int(x.stride(0));
+  a.hidden = hidden;
+  if (link) {
+    TORCH_CHECK(link->is_cuda() && link->is_contiguous() &&
+                    size_t(link->nbytes()) >= bl_dlin_local_link_bytes(a.tokens, hidden),
+                "barlink: the local link buffer is too small for ", a.tokens, " x ", hidden);
+    a.local_link = link->data_ptr();
+  }
+  a.err_flag = dlin_scratch(dev).err_flag.data_ptr();
+}
+
+// pro: "none" | "gather_norm";  epi: "store" | "silu_mul" | "push"
+// gather_norm: x is written first (RMSNorm(residual + all-reduced rows) * gamma), residual is
+// updated in place.  push: returns nothing useful (the rows are in every rank's inbox).
+at::Tensor dlin(const at::Tensor& x, const at::Tensor& w, const std::string& pro, const std::string& epi,
+                const c10::optional<at::Tensor>& out_opt, const c10::optional<at::Tensor>& bias,
+                const c10::optional<at::Tensor>& residual, const c10::optional<at::Tensor>& gamma, double eps,
+                int hidden, const c10::optional<at::Tensor>& link, int cluster, bool first,
+                const c10::optional<at::Tensor>& trace) {
+  check_bf16x(w, "weight");
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 &&
+                  w.dim() == 2 && w.stride(1) == 1 && w.size(1) == x.size(1),
+              "barlink: dlin needs bf16 x [tokens, k] and w [n, k] with unit inner strides");
+  const int dev = x.device().index();
+  c10::cuda::CUDAGuard guard(x.device());
+  void* st = at::cuda::getCurrentCUDAStream(dev).stream();
+  blDlinArgs a;
+  memset(&a, 0, sizeof(a));
+  a.w = w.data_ptr();
+  a.n = int(w.size(0));
+  a.k = int(w.size(1));
+  a.ldw = int(w.stride(0));
+  a.pro = pro == "gather_norm" ? 1 : 0;
+  TORCH_CHECK(a.pro == 1 || pro == "none", "barlink: dlin prologue must be none or gather_norm");
+  a.epi = epi == "store" ? 0 : epi == "silu_mul" ? 1 : epi == "push" ? 2 : -1;
+  TORCH_CHECK(a.epi >= 0, "barlink: dlin epilogue must be store, silu_mul or push");
+  dlin_fill_common(a, x, hidden > 0 ? hidden : a.k, link, dev);
+  if (a.pro == 1) {
+    TORCH_CHECK(residual && gamma, "barlink: gather_norm needs residual and gamma");
+    check_bf16x(*residual, "residual");
+    check_bf16x(*gamma, "gamma");
+    TORCH_CHECK(residual->numel() == x.numel() && x.is_contiguous() && gamma->numel() == a.k,
+                "barlink: residual must match x, gamma must have k entries");
+    a.residual_in = first ? nullptr : residual->data_ptr();
+    a.residual_out = residual->data_ptr();
+    a.gamma = gamma->data_ptr();
+    a.eps = float(eps);
+    a.sync = dlin_scratch(dev).sync.data_ptr();
+  }
+  at::Tensor out;
+  if (a.epi != 2) {
+    const int64_t cols = a.epi == 1 ? a.n / 2 : a.n;
+    out = out_opt ? *out_opt : at::empty({x.size(0), cols}, x.options());
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kBFloat16 && out.dim() == 2 && out.size(0) == x.size(0) &&
+                    out.size(1) == cols && out.stride(1) == 1,
+                "barlink: dlin out must be bf16 [tokens, ", cols, "]");
+    a.out = out.data_ptr();
+    a.ldo = int(out.stride(0));
+    if (bias) {
+      check_bf16x(*bias, "bias");
+      TORCH_CHECK(bias->numel() == a.n, "barlink: bias must have n entries");
+      a.bias = bias->data_ptr();
+    }
+  }
+  a.cluster = cluster;
+  if (trace) {
+    TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == at::kLong && trace->is_contiguous() &&
+                    trace->numel() >= 12 * 8 * ((a.n + 127) / 128),
+                "barlink: trace must be a contiguous int64 CUDA tensor of 12 words per CTA");
+    a.trace = trace->data_ptr();
+  }
+  blCtx* c = link ? nullptr : blpg::global_ctx();
+  {
+    py::gil_scoped_release nogil;
+    BL_CHECK(bl_dlin(c, &a, st, err, errlen));
+  }
+  return a.epi == 2 ? x : out;
+}
+
+// x = RMSNorm(residual + all-reduced inbox rows) * gamma, residual updated in place
+void gather_norm(const at::Tensor& x, const at::Tensor& residual, const at::Tensor& gamma, double eps,
+                 const c10::optional<at::Tensor>& link, bool first) {
+  check_bf16x(residual, "residual");
+  check_bf16x(gamma, "gamma");
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.is_contiguous() &&
+                  residual.numel() == x.numel() && gamma.numel() == x.size(1),
+              "barlink: gather_norm needs contiguous bf16 x [tokens, hidden], residual of that shape, gamma [hidden]");
+  const int dev = x.device().index();
+  c10::cuda::CUDAGuard guard(x.device());
+  void* st = at::cuda::getCurrentCUDAStream(dev).stream();
+  blDlinArgs a;
+  memset(&a, 0, sizeof(a));
+  dlin_fill_common(a, x, int(x.size(1)), link, dev);
+  a.residual_in = first ? nullptr : residual.data_ptr();
+  a.residual_out = residual.data_ptr();
+  a.gamma = gamma.data_ptr();
+  a.eps = float(eps);
+  blCtx* c = link ? nullptr : blpg::global_ctx();
+  py::gil_scoped_release nogil;
+  BL_CHECK(bl_gather_norm(c, &a, st, err, errlen));
+}
+
 py::dict layout_of(size_t pool_bytes, int world) {
   const bl::Layout L = bl::compute_layout(pool_bytes, world);
   py::dict d;
@@ -430,8 +589,20 @@ void bind_extra(py::module_& m) {
   m.def("gate_residual", &gate_residual, py::arg("x"), py::arg("y"), py::arg("gate"),
         py::arg("rows_per_batch"));
   m.def("w8a16_linear", &w8a16_linear, py::arg("x"), py::arg("wq"), py::arg("scale"),
-        py::arg("bias") = py::none(), py::arg("silu_mul") = false, py::arg("splits") = 0);
+        py::arg("bias") = py::none(), py::arg("silu_mul") = false, py::arg("splits") = 0,
+        py::arg("group_rel") = py::none());
+  m.def("w8_group_scales", &w8_group_scales, py::arg("scales"));
   m.def("w8_error_flag", &w8_error_flag, py::arg("device") = 0);
+  m.def("dlin", &dlin, py::arg("x"), py::arg("weight"), py::arg("pro") = "none", py::arg("epi") = "store",
+        py::arg("out") = py::none(), py::arg("bias") = py::none(), py::arg("residual") = py::none(),
+        py::arg("gamma") = py::none(), py::arg("eps") = 1e-6, py::arg("hidden") = 0, py::arg("link") = py::none(),
+        py::arg("cluster") = 0, py::arg("first") = false, py::arg("trace") = py::none());
+  m.def("gather_norm", &gather_norm, py::arg("x"), py::arg("residual"), py::arg("gamma"), py::arg("eps") = 1e-6,
+        py::arg("link") = py::none(), py::arg("first") = false);
+  m.def("dlin_local_link", &dlin_local_link, py::arg("tokens"), py::arg("hidden"), py::arg("device") = 0);
+  m.def("dlin_error_flag", &dlin_error_flag, py::arg("device") = 0);
+  m.def("dlin_cluster", [](int n, int k, int tokens, int want) { return bl_dlin_cluster(n, k, tokens, want); },
+        py::arg("n"), py::arg("k"), py::arg("tokens") = 64, py::arg("want") = 0);
   m.def("w8a16_quant_act", &w8a16_quant_act);
   m.def("w8a16_gemm", &w8a16_gemm, py::arg("xq"), py::arg("xs"), py::arg("wq_t"), py::arg("sw_t"),
         py::arg("N"), py::arg("K"), py::arg("S"));

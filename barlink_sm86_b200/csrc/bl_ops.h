@@ -118,7 +118,15 @@ typedef struct blW8A16Args {
   void* partial_out;
   size_t partial_stride;
   int partial_splits;
+  /* per-group scales applied inside the main loop: group_rel is fp16 [n][k / group_k], each row's
+   * group scales divided by that row's largest one, and `scale` then holds the row's largest
+   * scale (see bl_w8_group_scales).  group_k must be a multiple of 64.  null = per channel only */
+  const void* group_rel;
+  int group_k;
 } blW8A16Args;
+/* scales bf16 [n][groups] -> row_max bf16 [n] and rel fp16 [n][groups] = scale / row_max */
+int bl_w8_group_scales(const void* scales, int n, int groups, void* row_max, void* rel, void* stream, char* err,
+                       size_t errlen);
 /* returns -2 (and launches nothing) for more than 256 tokens */
 int bl_w8a16_linear(const blW8A16Args* a, void* stream, char* err, size_t errlen);
 /* out[n x k] bf16 = wq[n x k] int8 * scale[n]: the prefill path widens once and
@@ -172,12 +180,14 @@ int bl_paged_attn_decode(const void* q, int q_stride, const void* k_cache, const
                          void* scratch, size_t scratch_bytes, void* stream, char* err,
                          size_t errlen);
 /* RoPE + KV write + paged attention in one launch (decode).  qkv: bf16 rows, or null with
- * slabs = nsplit_in fp32 slabs of the QKV linear `slab` floats apart (+ bias). */
+ * slabs = nsplit_in fp32 slabs of the QKV linear `slab` floats apart (+ bias).
+ * counters: batch * nkv zeroed u32 words (left zero); with them the splits are merged by the
+ * last block of each (sequence, KV head) inside the kernel, without them by a second kernel. */
 int bl_rope_attn_decode(const void* qkv, int q_stride, const void* slabs, int nsplit_in, size_t slab,
                         const void* bias, const int* positions, const int* slots, float theta, void* k_cache,
                         void* v_cache, const int* block_tables, const int* ctx_lens, void* out, int batch, int nq,
                         int nkv, int hd, int block_size, int max_blocks, float scale, int splits, void* scratch,
-                        size_t scratch_bytes, void* stream, char* err, size_t errlen);
+                        size_t scratch_bytes, void* counters, void* stream, char* err, size_t errlen);
 /* Dense attention (prefill / joint attention): q [tq x nq x hd], k, v
  * [tk x nkv x hd] per sequence, sequences given by cu_seqlens (batch+1);
  * causal aligns the last query with the last key. */
@@ -197,6 +207,12 @@ int bl_attn_fwd_tc(const void* q, const void* k, const void* v, void* out, const
  * value (fp32); `offset` is added to the index (vocab-parallel shards). */
 int bl_argmax(const void* logits, int rows, int n, int ld, int offset, int* idx, float* val,
               void* scratch, size_t scratch_bytes, void* stream, char* err, size_t errlen);
+/* first stage only: parts[bl_argmax_chunks()][rows] (value, index bits) pairs, one per slice of a
+ * row -- the layout bl_argmax_merge reads, so per-rank parts of a vocabulary-parallel head can be
+ * all-gathered and merged without any repacking */
+int bl_argmax_parts(const void* logits, int rows, int n, int ld, int offset, void* parts, void* stream,
+                    char* err, size_t errlen);
+int bl_argmax_chunks(void);
 /* merge [parts x rows] (value, index bits) pairs: highest value, lowest index */
 int bl_argmax_merge(const void* pairs, int parts, int rows, int* idx, void* stream, char* err,
                     size_t errlen);
@@ -263,6 +279,47 @@ int bl_rs_finish(blCtx* ctx, const blRsFinishArgs* a, void* stream, char* err, s
 /* tiles x splits that bl_gemm_bf16 will use for a peer-sink linear (the
  * `units` of bl_rs_finish and the slab count the inbox must hold) */
 int bl_tp_units(int n, int k_local, int tokens, int* splits_out);
+
+/* ---- decode linears with the surrounding collective folded in (dlin_kernels.cu) ----------
+ * y[tokens, n] = x[tokens, k] @ w[n, k]^T for 1..64 tokens.  A cluster of CTAs shares one
+ * 128-row tile of w and sums its k-split partials through distributed shared memory.
+ *   pro = 1: x is first produced by this kernel as RMSNorm(residual_in + sum over ranks of the
+ *            rows in this GPU's one-shot inbox) * gamma; the new residual goes to residual_out,
+ *            the rows to x (k must be the hidden size).  This is the second half of an
+ *            all-reduce whose first half is the epi = 2 epilogue of the linear before.
+ *   epi = 0: out[tokens, ldo] = y (+ bias); 1: rows of w are interleaved (gate, up) pairs and
+ *            out[tokens, n/2] = SiLU(gate) * up; 2: y is rounded to bf16 and stored into every
+ *            rank's inbox as this rank's partial of a [tokens, hidden] all-reduce.
+ * The inboxes are the link's (ctx in peer mode) or, for a single GPU, a buffer of
+ * bl_dlin_local_link_bytes() prepared once by bl_dlin_local_link_init().  sync: 4 zeroed u32
+ * words that belong to this call site family (any number of launches may share them as long
+ * as they are in one stream).  cluster = 0 chooses the cluster size. */
+typedef struct blDlinArgs {
+  const void* w;
+  int n, k, ldw;
+  const void* x; /* [tokens, k] bf16, pitch ldx; written first when pro = 1 */
+  int tokens, ldx;
+  int pro, epi;
+  int hidden;    /* row length of the all-reduced tensor (pro = 1: == k; epi = 2: >= n) */
+  const void* residual_in; /* pro = 1; null = no residual */
+  void* residual_out;
+  const void* gamma;
+  float eps;
+  void* sync;
+  void* out;
+  int ldo;
+  const void* bias;
+  int cluster;
+  void* local_link;
+  void* err_flag;
+  void* trace; /* debug: u64[12 * grid] global-timer stamps per CTA, or null */
+} blDlinArgs;
+int bl_dlin(blCtx* ctx, const blDlinArgs* a, void* stream, char* err, size_t errlen);
+/* the prologue of pro = 1 as a kernel of its own (in front of a linear that keeps its kernel) */
+int bl_gather_norm(blCtx* ctx, const blDlinArgs* a, void* stream, char* err, size_t errlen);
+int bl_dlin_cluster(int n, int k, int tokens, int want);
+size_t bl_dlin_local_link_bytes(int tokens, int hidden);
+int bl_dlin_local_link_init(void* buf, int tokens, int hidden, void* stream, char* err, size_t errlen);
 
 #ifdef __cplusplus
 }

@@ -58,6 +58,11 @@ struct GemmShape {
   // activation tile is requested, each of gate_n flag words must have reached
   // *gate_cum + gate_add (peers add 1 per finished row block with a release at
   // system scope); the last CTA to finish moves *gate_cum forward.
+  // W8 only: per-(row, k-group) scales relative to the row's largest one, fp16 [ra][gs_groups],
+  // applied while widening (the row's largest scale is applied by the epilogue); null = none
+  const __half* gscale;
+  int gs_groups;
+  int gs_kblocks;           // k-blocks of 64 per scale group (group size / 64)
   const uint32_t* gate_flags;
   uint32_t* gate_cum;
   uint32_t* gate_ticket;
@@ -80,14 +85,14 @@ struct GemmSmem {
   static constexpr int kStageBytes = W8 ? kStageB + kStageRaw : kStageA + kStageB;
   static constexpr int kOffB = W8 ? 0 : kStageA;
   static constexpr int kOffRaw = kStageB;
-  static constexpr int kA16Stages = W8 ? 3 : 0;
+  static constexpr int kA16Stages = W8 ? (BN <= 64 ? 4 : 3) : 0;
   static constexpr int kTxBytes = kStageBytes;  // bytes TMA delivers per stage
   static constexpr int kConvThreads = W8 ? 256 : 0;
   static constexpr int kThreads = kGemmThreads + kConvThreads;
   // narrow tiles (decode): 4 stages so that two CTAs share an SM -- the same
   // bytes in flight per SM, but a CTA of the next kernel can move in and
   // prefetch weights while one of this kernel is still in its epilogue
-  static constexpr int kStages = W8 ? (BN <= 16 ? 16 : BN <= 32 ? 14 : BN <= 64 ? 10 : BN <= 128 ? 7 : 4)
+  static constexpr int kStages = W8 ? (BN <= 16 ? 16 : BN <= 32 ? 13 : BN <= 64 ? 10 : BN <= 128 ? 7 : 4)
                                     : (CPS == 2) ? 4 : (BN <= 64 ? 8 : (BN <= 128 ? 6 : 4));
   static constexpr int kCtasPerSm = CPS;
   static constexpr int kBarBytes = 1024;
@@ -112,6 +117,20 @@ __device__ __forceinline__ void s8x4_to_bf16x4(uint32_t w, uint32_t& lo, uint32_
   const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - bias;
   lo = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
   hi = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+}
+
+// four int8 in one word times a scale -> two bf16x2 words (round to nearest).  The scale rides
+// on the subtraction that removes the conversion bias, so it costs no instruction: with
+// scale = 1 the result is the exact integer.
+__device__ __forceinline__ void s8x4_to_bf16x4_scaled(uint32_t w, float sc, uint32_t& lo, uint32_t& hi) {
+  const uint32_t u = w ^ 0x80808080u;  // biased to 0..255
+  const float nb = -(8388608.f + 128.f) * sc;
+  const float f0 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)), sc, nb);
+  const float f1 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)), sc, nb);
+  const float f2 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)), sc, nb);
+  const float f3 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)), sc, nb);
+  lo = pack_bf16x2(f0, f1);
+  hi = pack_bf16x2(f2, f3);
 }
 
 template <int BN, int CPS, bool W8, class Sink>
@@ -358,8 +377,10 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
       const int tile = u / g.splits, sp = u - tile * g.splits;
       const int kb0 = sp * kb_per;
       const int kb1 = min(g.kblocks, kb0 + kb_per);
-      (void)tile;
+      const int grow = (tile / g.tiles_b) * kTileA + row;
+      const __half* gs = (g.gscale && grow < g.ra) ? g.gscale + size_t(grow) * g.gs_groups : nullptr;
       for (int kb = kb0; kb < kb1; ++kb) {
+        const float sc = gs ? __half2float(gs[kb / g.gs_kblocks]) : 1.f;
         if (!mbar_wait_bounded(&full_bar[stage], phase, s_abort) ||
             !mbar_wait_bounded(&afree_bar[astage], aphase ^ 1u, s_abort)) {
           ok = false;
@@ -374,10 +395,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
                        : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
                        : "r"(src + qd * 16));
           uint32_t o0, o1, o2, o3, o4, o5, o6, o7;
-          s8x4_to_bf16x4(w0, o0, o1);
-          s8x4_to_bf16x4(w1, o2, o3);
-          s8x4_to_bf16x4(w2, o4, o5);
-          s8x4_to_bf16x4(w3, o6, o7);
+          if (g.gscale) {
+            s8x4_to_bf16x4_scaled(w0, sc, o0, o1);
+            s8x4_to_bf16x4_scaled(w1, sc, o2, o3);
+            s8x4_to_bf16x4_scaled(w2, sc, o4, o5);
+            s8x4_to_bf16x4_scaled(w3, sc, o6, o7);
+          } else {
+            s8x4_to_bf16x4(w0, o0, o1);
+            s8x4_to_bf16x4(w1, o2, o3);
+            s8x4_to_bf16x4(w2, o4, o5);
+            s8x4_to_bf16x4(w3, o6, o7);
+          }
           const int c0 = half * 4 + qd * 2, c1 = c0 + 1;
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + (((c0 ^ (row & 7))) << 4)),
                        "r"(o0), "r"(o1), "r"(o2), "r"(o3)

@@ -11,6 +11,8 @@
 
 #include <mutex>
 
+#include <stdlib.h>
+
 #include "bl_ops.h"
 #include "heap.h"
 #include "launch.h"
@@ -675,26 +677,34 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
                        __nv_bfloat16* __restrict__ v_cache,
                         const int* __restrict__ block_tables, const int* __restrict__ ctx_lens,
                         __nv_bfloat16* __restrict__ out, float* __restrict__ scratch, int nq,
-                        int nkv, int max_blocks, float scale_log2) {
+                        int nkv, int max_blocks, float scale_log2, uint32_t* __restrict__ counters) {
   extern __shared__ __align__(16) uint8_t smem[];
   pdl_launch_dependents();
-  pdl_wait();
   const int h = blockIdx.x, b = blockIdx.y, sp = blockIdx.z, nsplit = gridDim.z;
   const int G = nq / nkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int ctx = ctx_lens[b];
-  const int n_pages = (ctx + kPageTokens - 1) / kPageTokens;
-  const int per = (n_pages + nsplit - 1) / nsplit;
-  const int p0 = sp * per;
-  const int p1 = min(n_pages, p0 + per);
   const int* table = block_tables + size_t(b) * max_blocks;
-
-  // the first pages are requested before anything else, so that the preparation of q and of the
-  // new key/value below overlaps their flight
   const uint32_t wbase = smem_u32(smem) + warp * kWarpSmem;
-  // pages of this warp: p0 + warp + i * kAttnWarps, i in [0, count)
-  const int count = p1 > p0 + warp ? (p1 - p0 - warp + kAttnWarps - 1) / kAttnWarps : 0;
+
+  // The pages of earlier tokens were written by earlier steps, so their copies may start before
+  // the kernels ahead of this one have finished; only the context length could still be the
+  // previous step's.  The range of pages is therefore computed from a first read, the first
+  // pages are requested, and after the wait the length is read again: in the rare case that the
+  // page count changed in between, the requests are drained and issued again.
+  int ctx = *reinterpret_cast<const volatile int*>(ctx_lens + b);
+  int n_pages, p0, p1, count;
+  auto set_range = [&]() {
+    n_pages = (ctx + kPageTokens - 1) / kPageTokens;
+    if (n_pages > max_blocks) n_pages = max_blocks;
+    if (n_pages < 0) n_pages = 0;
+    const int per = (n_pages + nsplit - 1) / nsplit;
+    p0 = sp * per;
+    p1 = min(n_pages, p0 + per);
+    // pages of this warp: p0 + warp + i * kAttnWarps, i in [0, count)
+    count = p1 > p0 + warp ? (p1 - p0 - warp + kAttnWarps - 1) / kAttnWarps : 0;
+  };
+  set_range();
   int tbl = 0;        // lane l holds the table entry of page index (chunk * 32 + l)
   int tbl_chunk = -1;
   auto issue = [&](int i, int buf) {
@@ -717,12 +727,29 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
       cp_async16(vd + r * kRowPitch + cc * 16, vs + c * 16);
     }
   };
-
   // prologue: kAttnStages - 1 pages in flight (one commit group per slot, empty when past the end)
+  auto prologue = [&]() {
 #pragma unroll
-  for (int i = 0; i < kAttnStages - 1; ++i) {
-    if (i < count) issue(i, i);
-    cp_async_commit();
+    for (int i = 0; i < kAttnStages - 1; ++i) {
+      if (i < count) issue(i, i);
+      cp_async_commit();
+    }
+  };
+  prologue();
+  pdl_wait();
+  {
+    const int pages_before = n_pages;
+    ctx = *reinterpret_cast<const volatile int*>(ctx_lens + b);
+    const int now = min(max_blocks, (ctx + kPageTokens - 1) / kPageTokens);
+    if (now != pages_before) {
+      cp_async_wait<0>();
+      __syncwarp();
+      set_range();
+      tbl_chunk = -1;
+      prologue();
+    } else {
+      set_range();
+    }
   }
   // cos / sin of this sequence's position for the 64 rotation pairs
   __shared__ float2 s_cs[kHd / 2];
@@ -947,6 +974,37 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
       }
     }
   }
+  // Splits are merged by the block of this (sequence, KV head) that finishes last: no second
+  // kernel.  The counter goes back to zero for the next launch.
+  if (nsplit > 1 && counters) {
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t old = atomicAdd(&counters[b * nkv + h], 1u);
+      s_last = old == uint32_t(nsplit - 1);
+      if (s_last) counters[b * nkv + h] = 0u;
+    }
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      for (int e = threadIdx.x; e < G * kHd; e += blockDim.x) {
+        const int r = e / kHd, d = e % kHd;
+        const int head = h * G + r;
+        const float* base = scratch + (size_t(b) * nq + head) * nsplit * (kHd + 2);
+        float M = -INFINITY;
+        for (int s2 = 0; s2 < nsplit; ++s2) M = fmaxf(M, __ldcg(base + s2 * (kHd + 2) + kHd));
+        float L = 0.f, acc = 0.f;
+        for (int s2 = 0; s2 < nsplit; ++s2) {
+          const float mw = __ldcg(base + s2 * (kHd + 2) + kHd);
+          const float sc = mw == -INFINITY ? 0.f : exp2f(mw - M);
+          L += __ldcg(base + s2 * (kHd + 2) + kHd + 1) * sc;
+          acc += __ldcg(base + s2 * (kHd + 2) + d) * sc;
+        }
+        out[size_t(b) * nq * kHd + size_t(head) * kHd + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
+      }
+    }
+  }
 }
 
 __global__ void __launch_bounds__(kHd) k_attn_merge(const float* __restrict__ scratch,
@@ -1123,6 +1181,19 @@ extern "C" int bl_argmax(const void* logits, int rows, int n, int ld, int offset
   return 0;
 }
 
+extern "C" int bl_argmax_parts(const void* logits, int rows, int n, int ld, int offset, void* parts, void* stream,
+                               char* err, size_t errlen) {
+  if (!parts || (reinterpret_cast<uintptr_t>(parts) & 7u)) {
+    set_err(err, errlen, "barlink: argmax_parts needs an 8-byte aligned output of %d x rows pairs", kArgmaxChunks);
+    return -1;
+  }
+  launch_k(k_argmax, dim3(rows, kArgmaxChunks), dim3(256), 0, static_cast<cudaStream_t>(stream),
+           static_cast<const __nv_bfloat16*>(logits), n, ld, offset, static_cast<float2*>(parts), rows);
+  OPS_LAUNCH_CHECK("argmax_parts");
+  return 0;
+}
+extern "C" int bl_argmax_chunks(void) { return kArgmaxChunks; }
+
 extern "C" int bl_decode_advance(int* positions, int* ctx_lens, int* slots, const int* block_tables,
                                  int* ids, const int* sampled, int batch, int max_blocks,
                                  int block_size, void* stream, char* err, size_t errlen) {
@@ -1204,8 +1275,8 @@ extern "C" int bl_rope_attn_decode(const void* qkv, int q_stride, const void* sl
                                    float theta, void* k_cache, void* v_cache, const int* block_tables,
                                    const int* ctx_lens, void* out, int batch, int nq, int nkv,
                                     int hd, int block_size, int max_blocks, float scale, int splits,
-                                    void* scratch, size_t scratch_bytes, void* stream, char* err,
-                                    size_t errlen) {
+                                    void* scratch, size_t scratch_bytes, void* counters, void* stream,
+                                    char* err, size_t errlen) {
   if (hd != kHd || block_size != kPageTokens) {
     set_err(err, errlen, "barlink: paged attention is built for head_dim %d and block size %d", kHd,
             kPageTokens);
@@ -1214,6 +1285,20 @@ extern "C" int bl_rope_attn_decode(const void* qkv, int q_stride, const void* sl
   if (nkv < 1 || nq % nkv || nq / nkv > 16) {
     set_err(err, errlen, "barlink: paged attention needs nq %% nkv == 0 and at most 16 query heads per KV head");
     return -1;
+  }
+  if (batch * nkv > 65536) counters = nullptr;
+  if (splits <= 0 && counters) {
+    // the merge is done inside the kernel, so a split costs no launch: fill the resident slots
+    // (two CTAs of this kernel fit on an SM)
+    static const int env_splits = [] {
+      const char* v = getenv("BL_ATTN_SPLITS");
+      return (v && *v) ? atoi(v) : 0;
+    }();
+    const int want = env_splits > 0 ? env_splits : (2 * sm_count()) / (batch * nkv);
+    const int by_len = max_blocks / (2 * kAttnWarps) > 0 ? max_blocks / (2 * kAttnWarps) : 1;
+    splits = want < by_len ? want : by_len;
+    if (splits > 32) splits = 32;
+    if (splits < 1) splits = 1;
   }
   if (splits <= 0) {
     // enough CTAs to fill the GPU once; more splits only add merge traffic.  From 64 CTAs
@@ -1257,9 +1342,9 @@ extern "C" int bl_rope_attn_decode(const void* qkv, int q_stride, const void* sl
       slots, log2f(theta), static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache),
       block_tables, ctx_lens,
       static_cast<__nv_bfloat16*>(out), static_cast<float*>(scratch), nq, nkv, max_blocks,
-      scale_log2);
+      scale_log2, static_cast<uint32_t*>(counters));
   OPS_LAUNCH_CHECK("rope_attn_decode");
-  if (splits > 1) {
+  if (splits > 1 && !counters) {
     launch_k(k_attn_merge, dim3(batch * nq), dim3(kHd), 0, st, static_cast<const float*>(scratch),
                                              static_cast<__nv_bfloat16*>(out), splits);
     OPS_LAUNCH_CHECK("attn_merge");

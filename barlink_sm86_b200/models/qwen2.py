@@ -367,6 +367,70 @@ class Qwen2Model:
 
         return self._run_layers(ids, positions, attn_factory, split_k=True)
 
+    # ---- decode with one kernel per linear and the collectives folded in ----------
+    def dlin_ok(self, tokens):
+        """The decode step built from `_C.dlin` kernels: every linear is one cluster split-K
+        kernel; o_proj / down store their bf16 partial rows straight into every rank's one-shot
+        inbox, and the linear after them (QKV, gate/up) gathers, reduces, adds the residual and
+        normalises in its prologue while its weights stream.  Five launches per layer.  Default
+        with more than one rank; BL_DLIN=1 selects it on one GPU too (inboxes in local memory),
+        BL_DLIN=0 turns it off."""
+        import os
+        c = self.comm
+        mode = os.environ.get("BL_DLIN", "auto")
+        if mode == "0" or self.device.type != "cuda" or self.w.quant != "none" or self.dtype != torch.bfloat16:
+            return False
+        if tokens > 64 or self.cfg.hidden % 8 or self.cfg.hidden > 8192 or self.w.tiled:
+            return False
+        if c.world > 1 and c.no_comm:
+            return mode != "0"  # timing control: same kernels, inboxes in local memory, nothing crosses NVLink
+        if c.world > 1:
+            return bool(c.use_link) and tokens * self.cfg.hidden * 2 <= c.oneshot_max
+        return mode == "1"
+
+    def _dlin_buffers(self, tokens):
+        key = ("dlin", tokens, self.comm.no_comm)
+        if getattr(self, "_dbuf_key", None) != key:
+            from .. import load_extension
+            H = self.cfg.hidden
+            res = torch.zeros(tokens, H, dtype=self.dtype, device=self.device)
+            xn = torch.zeros(tokens, H, dtype=self.dtype, device=self.device)
+            link = None
+            if self.comm.world == 1 or self.comm.no_comm:
+                link = load_extension().dlin_local_link(tokens, H, self.device.index or 0)
+            self._dbuf, self._dbuf_key = (res, xn, link), key
+        return self._dbuf
+
+    def decode_hidden_dlin(self, ids, positions, slots, ctx_lens, cache: PagedKV, splits=0):
+        """Same result as decode_hidden (same roundings: each rank's partial row is rounded to
+        bf16 before the sum, the sum before the residual add)."""
+        from .. import load_extension
+        C = load_extension()
+        cfg, c, w = self.cfg, self.comm, self.w
+        nq, nkv, hd = self.nq, self.nkv, self.hd
+        H = cfg.hidden
+        res, xn, link = self._dlin_buffers(ids.shape[0])
+        ops.embedding(ids, w.embed, out=res)
+        ops.rmsnorm(res, w.layers[0]["ln1"], cfg.eps, out=xn)
+        for li, L in enumerate(w.layers):
+            ops._count(5)
+            if li == 0:
+                qkv = C.dlin(xn, L["wqkv"], epi="store", bias=L["bqkv"])
+            else:
+                qkv = C.dlin(xn, L["wqkv"], pro="gather_norm", epi="store", bias=L["bqkv"], residual=res,
+                             gamma=L["ln1"], eps=cfg.eps, link=link)
+            a = C.rope_attn_decode(qkv, None, positions, slots, cache.k[li], cache.v[li], cache.block_tables,
+                                   ctx_lens, nq, nkv, hd, cfg.theta, self.scale, splits)
+            C.dlin(a, L["wo"], epi="push", hidden=H, link=link)
+            act = C.dlin(xn, L["wgu"], pro="gather_norm", epi="silu_mul", residual=res, gamma=L["ln2"],
+                         eps=cfg.eps, link=link)
+            C.dlin(act, L["wdown"], epi="push", hidden=H, link=link)
+            c.ar_calls += 2 if c.world > 1 else 0
+            c.ar_bytes += (2 * xn.numel() * 2) if c.world > 1 else 0
+        ops._count()
+        C.gather_norm(xn, res, w.ln_f, cfg.eps, link=link)
+        return xn
+
     # ---- decode with the fused tensor-parallel linears -------------------------
     def fused_ok(self, tokens):
         """Row-parallel GEMM->reduce-scatter and all-gather->column-parallel GEMM
@@ -449,9 +513,9 @@ class Qwen2Model:
         full = self.comm.all_gather_cols(self.logits_local(hidden))
         return full[:, : self.cfg.vocab]
 
-    def next_tokens(self, hidden):
-        """Greedy next token per row (local arg max + 8-byte-per-row exchange)."""
-        return self.comm.argmax_vocab_parallel(self.logits_local(hidden), self.w.vocab_local)
+    def next_tokens(self, hidden, out=None):
+        """Greedy next token per row (local arg max + a few bytes per row exchanged)."""
+        return self.comm.argmax_vocab_parallel(self.logits_local(hidden), self.w.vocab_local, out)
 
 
 class DecodeEngine:
@@ -513,16 +577,21 @@ class DecodeEngine:
         return nxt
 
     def _step_body(self):
-        if self.m.fused_ok(self.batch):
+        if self.m.dlin_ok(self.batch):
+            hidden = self.m.decode_hidden_dlin(self.ids, self.positions, self.slots, self.ctx_lens,
+                                               self.cache, self.attn_splits)
+            nxt = self.m.next_tokens(hidden, self.out_ids)
+        elif self.m.fused_ok(self.batch):
             hidden, gate = self.m.decode_hidden_fused(self.ids, self.positions, self.slots,
                                                       self.ctx_lens, self.cache, self.attn_splits)
             logits = ops.linear(hidden, self.m.w.lm_head, gate_tokens=gate)
-            nxt = self.m.comm.argmax_vocab_parallel(logits, self.m.w.vocab_local)
+            nxt = self.m.comm.argmax_vocab_parallel(logits, self.m.w.vocab_local, self.out_ids)
         else:
             hidden = self.m.decode_hidden(self.ids, self.positions, self.slots, self.ctx_lens,
                                           self.cache, self.attn_splits)
-            nxt = self.m.next_tokens(hidden)
-        self.out_ids.copy_(nxt)
+            nxt = self.m.next_tokens(hidden, self.out_ids)
+        if nxt is not self.out_ids:
+            self.out_ids.copy_(nxt)
         if self.m.device.type == "cuda":
             # one kernel: position, context length, KV slot and next input id
             from .. import load_extension

@@ -224,7 +224,7 @@ def rope_attn_decode(qkv, bias, positions, slots, k_cache, v_cache, block_tables
     qkv: bf16 [batch, width] or the fp32 k-split slabs of the QKV linear
     (+ bias).  Same result as rope_kv_write followed by paged_attn_decode."""
     if k_cache.is_cuda:
-        _count(2 if splits != 1 else 1)
+        _count()  # the splits are merged inside the kernel
         return _C().rope_attn_decode(qkv, bias, positions, slots, k_cache, v_cache, block_tables, ctx_lens,
                                      nq, nkv, hd, theta, scale, splits)
     rot = rope_kv_write(qkv, positions, slots, k_cache, v_cache, nq, nkv, hd, block_size, theta, bias)
@@ -241,20 +241,52 @@ def attention(q, k, v, cu_q, cu_k, max_q, scale, causal, max_k=0):
     return ref.attention(q, k, v, cu_q, cu_k, scale, causal)
 
 
+class W8GroupScales:
+    """Per-group int8 scales [n, k/group] in the form the W8A16 kernel applies inside its main
+    loop: `row` bf16 [n] (each row's largest scale, applied by the epilogue) and `rel` fp16
+    [n, groups] (the group scales divided by it, applied while the int8 tile is widened).
+    Build once per weight with `prepare_w8_scales`."""
+    __slots__ = ("row", "rel", "group")
+
+    def __init__(self, row, rel, group):
+        self.row, self.rel, self.group = row, rel, group
+
+
+def prepare_w8_scales(scale, k):
+    """bf16 group scales [n, k/group] on a CUDA device -> W8GroupScales."""
+    row, rel = _C().w8_group_scales(scale.contiguous())
+    return W8GroupScales(row, rel, k // scale.shape[1])
+
+
 def w8a16_linear(x, wq, scale, bias=None, silu_mul=False):
-    """scale [n]: per output channel, the tcgen05 kernel that widens int8 in its main loop.
-    scale [n, k/group]: per-group scales cannot be folded into the epilogue; the weight is
-    widened once (scaled per group) and the bf16 GEMM runs on it."""
-    if x.is_cuda and scale.dim() == 2:
-        w = ref.w8_dequant(wq, scale).to(torch.bfloat16)
-        return linear(x, w, bias, silu_mul=silu_mul, dynamic_weights=True)
+    """scale [n]: per output channel.  scale [n, k/group] or a W8GroupScales: per group, the
+    reference's granularity (torch_ext/barlink_sm86/w8a16.cu:119-142 applies group scales inside
+    its K loop; so does the tcgen05 kernel here, in the warps that widen the int8 tile).  Group
+    sizes that are not multiples of 64, and more than 256 tokens, widen the weight once and run
+    the bf16 GEMM."""
     if x.is_cuda:
+        k = wq.shape[1]
+        gs = scale if isinstance(scale, W8GroupScales) else None
+        if gs is None and scale.dim() == 2:
+            if (k // scale.shape[1]) % 64 == 0 and x.shape[0] <= 256:
+                _count()
+                gs = prepare_w8_scales(scale, k)
+            else:
+                w = ref.w8_dequant(wq, scale).to(torch.bfloat16)
+                return linear(x, w, bias, silu_mul=silu_mul, dynamic_weights=True)
         _count()
+        if gs is not None:
+            if x.shape[0] > 256:
+                w = (ref.w8_dequant(wq, gs.rel.float() * gs.row.float()[:, None])).to(torch.bfloat16)
+                return linear(x, w, bias, silu_mul=silu_mul, dynamic_weights=True)
+            return _C().w8a16_linear(x, wq, gs.row, bias, silu_mul, group_rel=gs.rel)
         return _C().w8a16_linear(x, wq, scale, bias, silu_mul)
+    if isinstance(scale, W8GroupScales):
+        scale = scale.rel.float() * scale.row.float()[:, None]
     return ref.w8a16_linear(x, wq, scale, bias, silu_mul)
 
 
 __all__ = [
     "linear", "linear_split", "k_splits", "TiledWeight", "tile_weight", "untile_weight", "rmsnorm", "rope_kv_write", "rope", "silu_mul", "embedding", "argmax",
-    "paged_attn_decode", "rope_attn_decode", "attention", "w8a16_linear", "w4a16_linear", "qknorm_rope", "layernorm_modulate", "gate_residual", "ref",
+    "paged_attn_decode", "rope_attn_decode", "attention", "w8a16_linear", "W8GroupScales", "prepare_w8_scales", "w4a16_linear", "qknorm_rope", "layernorm_modulate", "gate_residual", "ref",
 ]

@@ -42,6 +42,33 @@ class TPComm:
         # demos/qwen_tp/qwen38_int8/worker.py:157-183): every collective is
         # skipped, results are wrong, the step time is compute only
         self.no_comm = False
+        self._init_timing()
+
+    def _init_timing(self):
+        # per-collective device timing (the reference brackets every hooked all_reduce with CUDA
+        # events and reports their sum, demos/qwen_tp/qwen38_int8/worker.py:157-183, 630-637):
+        # eager steps only, never while a stream is being captured
+        self.time_collectives = False
+        self._timed = []
+
+    def _timed_call(self, fn):
+        if not self.time_collectives or not torch.cuda.is_available() or torch.cuda.is_current_stream_capturing():
+            return fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        r = fn()
+        b.record()
+        self._timed.append((a, b))
+        return r
+
+    def collective_ms(self, reset=True):
+        """(calls, total device ms) of the collectives timed since the last reset."""
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        n, ms = len(self._timed), sum(a.elapsed_time(b) for a, b in self._timed)
+        if reset:
+            self._timed = []
+        return n, ms
 
     @classmethod
     def single(cls):
@@ -50,6 +77,7 @@ class TPComm:
         c.group, c.world, c.rank = None, 1, 0
         c.use_link, c.oneshot_max, c.ar_calls, c.ar_bytes, c.max_chunk = False, 0, 0, 0, 0
         c.no_comm = False
+        c._init_timing()
         return c
 
     # ---- collectives -----------------------------------------------------
@@ -64,7 +92,7 @@ class TPComm:
             nbytes = x.numel() * x.element_size()
             if nbytes <= self.max_chunk:
                 _ops._count()
-                load_extension().allreduce_into(x, x)
+                self._timed_call(lambda: load_extension().allreduce_into(x, x))
             else:
                 flat = x.view(-1)
                 step = (self.max_chunk // 16 * 16) // x.element_size()
@@ -73,7 +101,7 @@ class TPComm:
                     part = flat[i:i + step]
                     load_extension().allreduce_into(part, part)
             return x
-        dist.all_reduce(x, group=self.group)
+        self._timed_call(lambda: dist.all_reduce(x, group=self.group))
         return x
 
     def all_gather_cols(self, x):
@@ -121,7 +149,8 @@ class TPComm:
             self.ar_calls += 1
             self.ar_bytes += nbytes
             _ops._count()
-            normed, res = load_extension().allreduce_rmsnorm(x, residual, gamma, eps, None, residual)
+            normed, res = self._timed_call(
+                lambda: load_extension().allreduce_rmsnorm(x, residual, gamma, eps, None, residual))
             return normed, res
         self.all_reduce(x)
         if residual is None:
@@ -129,10 +158,25 @@ class TPComm:
             return normed, x
         return _ops.rmsnorm(x, gamma, eps, residual)
 
-    def argmax_vocab_parallel(self, logits_local, vocab_per_rank):
-        """Global arg max over vocab-parallel logits [rows, vocab_per_rank]."""
+    def argmax_vocab_parallel(self, logits_local, vocab_per_rank, out=None):
+        """Global arg max over vocab-parallel logits [rows, vocab_per_rank] (int32 [rows], written
+        to `out` when given).  On the link: the arg max kernel leaves (value, index) pairs per slice
+        of a row in the layout the merge kernel reads, the pairs of all ranks are all-gathered as
+        they are, and one merge kernel picks -- three launches, no repacking in between."""
+        if logits_local.is_cuda and self.use_link and self.world > 1 and not self.no_comm:
+            C = load_extension()
+            parts = C.argmax_parts(logits_local, self.rank * vocab_per_rank)       # [chunks, rows, 2]
+            if parts.numel() * 4 % 16 == 0:
+                allp = torch.empty(self.world * parts.shape[0], parts.shape[1], 2, dtype=torch.float32,
+                                   device=parts.device)
+                _ops._count(3)
+                C.allgather_into(allp.view(-1), parts.view(-1))
+                return C.argmax_merge(allp, out)
         idx, val = _ops.argmax(logits_local, self.rank * vocab_per_rank)
         if self.world == 1 or self.no_comm:
+            if out is not None:
+                out.copy_(idx)
+                return out
             return idx
         pairs = torch.stack([val, idx.view(torch.float32) if idx.dtype == torch.int32 else idx.float()], -1)
         if logits_local.is_cuda and self.use_link:
@@ -143,7 +187,11 @@ class TPComm:
             allp = torch.empty(self.world, rows + pad, 2, dtype=torch.float32, device=pairs.device)
             _ops._count(2)
             load_extension().allgather_into(allp.view(-1), pairs.contiguous().view(-1))
-            return load_extension().argmax_merge(allp[:, :rows].contiguous())
+            r = load_extension().argmax_merge(allp[:, :rows].contiguous())
+            if out is not None:
+                out.copy_(r)
+                return out
+            return r
         vals = [torch.empty_like(val) for _ in range(self.world)]
         idxs = [torch.empty_like(idx) for _ in range(self.world)]
         dist.all_gather(vals, val.contiguous(), group=self.group)
@@ -153,7 +201,11 @@ class TPComm:
         # highest value, lowest index on ties
         best = v.max(0).values
         cand = torch.where(v == best[None], i, torch.full_like(i, 2 ** 31 - 1))
-        return cand.min(0).values.to(torch.int32)
+        r = cand.min(0).values.to(torch.int32)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
 
     def barrier(self):
         if self.world > 1:

@@ -210,6 +210,17 @@ def main():
                 "kv_cache": "paged, block 16", "parallelism": "tp%d" % args.gpus,
                 "prefill": args.prefill,
                 "cuda_graph": eng.graph is not None,
+                # which decode path ran: "folded" = one cluster split-K kernel per linear, the row-parallel
+                # linears store their partial rows into every rank's inbox from the epilogue and the next
+                # linear reduces + normalises them in its prologue (no collective kernel, no library call);
+                # "fused_rs_ag" = GEMM->reduce-scatter / all-gather->GEMM pair; "allreduce" = k-split GEMM
+                # + one-shot all-reduce+RMSNorm kernel
+                "decode_path": ("folded" if model.dlin_ok(B) else "fused_rs_ag" if model.fused_ok(B)
+                                else "allreduce"),
+                "fused_linear": bool(model.dlin_ok(B) or model.fused_ok(B)),
+                "ar_algo": os.environ.get("BL_AR_ALGO", "auto"),
+                "pdl": os.environ.get("BL_PDL", "1") != "0",
+                "quant": "none",
                 "l2": "each step streams %.1f GB of weights plus the KV cache per GPU, far above the 126 MB L2"
                       % (model.w.nbytes() / 1e9),
             },
@@ -227,6 +238,7 @@ def main():
             "prefill_s": round(prefill_s, 2),
             "link_status": status.get("code", 0),
             "gemm_error_flag": gemm_err,
+            "dlin_error_flag": bl.load_extension().dlin_error_flag(local_rank),
         }
         line = json.dumps(out)
         print(line)

@@ -46,6 +46,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=10, help="untimed decode steps")
     ap.add_argument("--no-graph", action="store_true", help="eager step instead of a CUDA graph")
     ap.add_argument("--no-comm", action="store_true", help="control run: skip every collective (wrong results)")
+    ap.add_argument("--time-collectives", type=int, default=0, metavar="STEPS",
+                    help="after the timed region, run STEPS eager steps on the all-reduce path (one collective "
+                         "kernel per row-parallel linear) with CUDA events around every collective and report "
+                         "their device time per step")
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers")
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--tag", default=None)
@@ -139,6 +143,34 @@ def main():
           % (world, rank, mode, cfg.name, a.quant, load_s, prefill_ms, a.gen, a.batch, ms_tok, tps,
              eng.launches_per_step, "eager" if eng.graph is None else "one graph replay", mem), flush=True)
 
+    # device time of the collectives themselves, call by call (eager, unfused path)
+    coll = {"calls_per_step": 0, "device_ms_per_step": 0.0, "steps": 0}
+    if a.time_collectives > 0 and world > 1 and not cpu and not a.no_comm:
+        saved = os.environ.get("BL_DLIN")
+        os.environ["BL_DLIN"] = "0"
+        eng2 = DecodeEngine(model, a.batch, total, use_graph=False)
+        eng2.cache = eng.cache
+        eng2.set_context(a.prompt_len)
+        eng2.ids.copy_(first)
+        for _ in range(2):
+            eng2.step()
+        comm.time_collectives = True
+        comm.collective_ms()
+        for _ in range(a.time_collectives):
+            eng2.step()
+        n, ms = comm.collective_ms()
+        comm.time_collectives = False
+        if saved is None:
+            os.environ.pop("BL_DLIN", None)
+        else:
+            os.environ["BL_DLIN"] = saved
+        ms = max_over_ranks(ms, device=dev)
+        coll = {"calls_per_step": n // a.time_collectives, "device_ms_per_step": ms / a.time_collectives,
+                "steps": a.time_collectives}
+        if rank == 0:
+            print("[tp=%d] collectives on the all-reduce path: %d calls/step, %.3f ms of device time per step "
+                  "(eager, max over ranks)" % (world, coll["calls_per_step"], coll["device_ms_per_step"]), flush=True)
+
     tag = a.tag or ("tp%d%s" % (world, "" if a.quant == "none" else "_" + a.quant))
     if rank == 0:
         os.makedirs(a.out, exist_ok=True)
@@ -151,6 +183,9 @@ def main():
                        "prefill_ms": prefill_ms, "decode_ms_per_token": ms_tok, "tokens_per_s": tps,
                        "kernels_per_step": eng.launches_per_step,
                        "allreduce_calls_timed": comm.ar_calls - ar0, "peak_mem_gib": mem,
+                       "decode_path": ("folded" if model.dlin_ok(a.batch) else "fused_rs_ag" if model.fused_ok(a.batch)
+                                       else "allreduce"),
+                       "collectives_eager": coll,
                        "weight_gib": model.w.nbytes() / (1 << 30), "link": link_stats()}, f, indent=2)
     if world > 1:
         # captured graphs hold references to the communicator's kernels: drop them first

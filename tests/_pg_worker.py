@@ -83,6 +83,42 @@ for algo in algos:
         bl.allreduce_into(out, x, algo)
         assert torch.equal(out.cpu(), expect_sum(n, torch.bfloat16)), (algo, nbytes)
 log("all_reduce algorithms ok: %s" % algos)
+if info["multicast"]:
+    # in-switch reduction on a bandwidth-sized message, integer-valued so that the sum is exact
+    for nbytes, dtype in ((64 << 20, torch.bfloat16), (16 << 20, torch.float32)):
+        n = nbytes // torch.empty(0, dtype=dtype).element_size()
+        x = seeded(rank, n, dtype).to(dev)
+        out = torch.empty_like(x)
+        bl.allreduce_into(out, x, "nvls")
+        assert torch.equal(out.cpu(), expect_sum(n, dtype)), ("nvls", nbytes, dtype)
+    log("nvls large messages ok")
+
+# back-to-back staged collectives with a different pattern per call, while one rank's SMs are
+# also busy with an unrelated stream: a call must never overwrite staging data that a slower
+# peer has not consumed yet
+side = torch.cuda.Stream()
+busy_a = torch.randn(2048, 2048, device=dev)
+stop_at = 120
+n = 96 << 10
+mine_all = [seeded(rank, n, torch.float32).add(i).to(dev) for i in range(4)]
+for it in range(stop_at):
+    if rank == 1 and it % 4 == 0:
+        with torch.cuda.stream(side):
+            for _ in range(6):
+                busy_a = (busy_a @ busy_a).clamp_(-1, 1)
+    mine = mine_all[it % 4]
+    out = torch.empty(world * n, dtype=torch.float32, device=dev)
+    dist.all_gather_into_tensor(out, mine)
+    big = out  # every rank now holds the same [world * n] tensor
+    part = torch.empty(n, dtype=torch.float32, device=dev)
+    dist.reduce_scatter_tensor(part, big)
+    if it % 10 == 0 or it == stop_at - 1:
+        want_g = torch.cat([seeded(r, n, torch.float32).add(it % 4) for r in range(world)])
+        assert torch.equal(out.cpu(), want_g), ("all_gather", it)
+        assert torch.equal(part.cpu(), want_g[rank * n:(rank + 1) * n] * world), ("reduce_scatter", it)
+torch.cuda.synchronize()
+assert bl.status()["code"] == 0
+log("back-to-back all_gather / reduce_scatter ok (%d rounds)" % stop_at)
 
 # staged paths: odd size, unaligned view, non-contiguous
 t = seeded(rank, 1001, torch.float32).to(dev)
@@ -178,6 +214,63 @@ if peer < world:
             dist.send(t, peer)
     log("p2p ok")
 
+# every pair, several dtypes: rank r sends to r + d and receives from r - d (the reference's
+# matrix for two ranks, torch_ext/tests/test_pg_p2p.py:143-206, over all distances of N ranks)
+for d in range(1, world):
+    to, frm = (rank + d) % world, (rank - d) % world
+    for dtype, n in ((torch.float16, 4096), (torch.uint8, 40000), (torch.int64, 777), (torch.float32, 2 << 20)):
+        a = seeded(rank, n, torch.float32, 0, 100).to(dtype).to(dev)
+        b = torch.empty(n, dtype=dtype, device=dev)
+        reqs = [dist.isend(a, to), dist.irecv(b, frm)]
+        for r in reqs:
+            r.wait()
+        assert torch.equal(b.cpu(), seeded(frm, n, torch.float32, 0, 100).to(dtype)), (d, dtype)
+# interleaved outstanding sends of mixed sizes, then the receives, with all-reduces in between
+to, frm = (rank + 1) % world, (rank - 1) % world
+sizes = (10, 70000, 3, 1 << 20)
+outs = [seeded(rank, n, torch.float32).add(i).to(dev) for i, n in enumerate(sizes)]
+ins = [torch.empty(n, dtype=torch.float32, device=dev) for n in sizes]
+pend = []
+for i, o in enumerate(outs):
+    pend.append(dist.isend(o, to))
+    if i == 1:
+        t = torch.ones(2560, dtype=torch.bfloat16, device=dev)
+        dist.all_reduce(t)
+        assert torch.all(t == world)
+for i, buf in enumerate(ins):
+    pend.append(dist.irecv(buf, frm))
+    if i == 2:
+        t = torch.ones(1 << 20, device=dev)
+        dist.all_reduce(t)
+        assert torch.all(t == world)
+for r in pend:
+    r.wait()
+for i, (buf, n) in enumerate(zip(ins, sizes)):
+    assert torch.equal(buf.cpu(), seeded(frm, n, torch.float32).add(i)), ("mixed", i)
+# a message far above the p2p slice goes in chunks, full duplex (reference: repro_p2p_big.py:23-71)
+for mb in (48, 128):
+    n = (mb << 20) // 4
+    a = torch.arange(n, dtype=torch.int32, device=dev).mul_(rank + 3)
+    b = torch.empty(n, dtype=torch.int32, device=dev)
+    reqs = [dist.isend(a, to), dist.irecv(b, frm)]
+    for r in reqs:
+        r.wait()
+    assert torch.equal(b, torch.arange(n, dtype=torch.int32, device=dev).mul_(frm + 3)), mb
+# host tensors and a strided view take the staged fallback
+hs = seeded(rank, 500, torch.float32)
+hr = torch.empty(500)
+reqs = [dist.isend(hs, to), dist.irecv(hr, frm)]
+for r in reqs:
+    r.wait()
+assert torch.equal(hr, seeded(frm, 500, torch.float32))
+base = seeded(rank, 4000, torch.float32).to(dev)
+rb = torch.zeros(4000, device=dev)
+reqs = [dist.isend(base[::2], to), dist.irecv(rb[::2], frm)]
+for r in reqs:
+    r.wait()
+assert torch.equal(rb[::2].cpu(), seeded(frm, 4000, torch.float32)[::2]) and torch.all(rb[1::2] == 0)
+log("p2p matrix ok (all distances, fp16/u8/int64/fp32, mixed with all-reduce, 48 and 128 MB, host and strided)")
+
 # ---- fused all-reduce + residual + RMSNorm ------------------------------------------------
 from barlink_sm86_b200.ops import reference as ref  # noqa: E402
 for rows, hidden in ((1, 3584), (8, 3584), (64, 3584), (3, 5120)):
@@ -267,8 +360,11 @@ log("error paths ok")
 # ---- a wait that runs out: status, no trap, link usable again after reset ----------------------
 host_barrier()
 torch.cuda.synchronize()
-bl.set_wait_timeout_ms(200)
-if rank == 0 and world >= 2:
+# (not with arenas bound to a multicast object: failure cases run with plain peer memory only)
+run_timeout_case = not info["multicast"]
+if run_timeout_case:
+    bl.set_wait_timeout_ms(200)
+if run_timeout_case and rank == 0 and world >= 2:
     t = torch.zeros(64, device=dev)
     bl.recv_into(t, 1)  # rank 1 never sends this message
     torch.cuda.synchronize()
@@ -280,8 +376,9 @@ if rank == 0 and world >= 2:
     except RuntimeError:
         pass
 host_barrier()
-bl.reset()
-bl.set_wait_timeout_ms(2000)
+if run_timeout_case:
+    bl.reset()
+    bl.set_wait_timeout_ms(2000)
 host_barrier()
 t = torch.ones(64, device=dev)
 dist.all_reduce(t)

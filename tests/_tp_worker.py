@@ -47,16 +47,25 @@ def generate(model):
     return torch.stack(seq, 1)
 
 
+# default: one kernel per linear with the all-reduce halves folded into epilogue and prologue
+assert tp.dlin_ok(B), "the folded-collective decode path should be available for this shape"
+tok_tp = generate(tp)
+os.environ["BL_DLIN"] = "0"
 os.environ["BL_FUSED_LINEAR"] = "1"
 assert tp.fused_ok(B), "the fused TP linears should be available for this shape"
-tok_tp = generate(tp)
+tok_rs = generate(tp)
 os.environ["BL_FUSED_LINEAR"] = "0"
 tok_unfused = generate(tp)
+os.environ["BL_DLIN"] = "auto"
 tok_1 = generate(one)
 m_fu = (tok_tp == tok_unfused).float().mean().item()
+m_rs = (tok_rs == tok_unfused).float().mean().item()
 if rank == 0:
-    print("[tp] fused vs all-reduce path token match %.0f%%" % (m_fu * 100), flush=True)
+    print("[tp] token match with the all-reduce path: folded %.0f%%, reduce-scatter/all-gather %.0f%%"
+          % (m_fu * 100, m_rs * 100), flush=True)
 assert m_fu >= 0.7, m_fu
+assert m_rs >= 0.7, m_rs
+assert bl.load_extension().dlin_error_flag(rank) == 0
 gathered = [torch.empty_like(tok_tp) for _ in range(world)]
 dist.all_gather(gathered, tok_tp)
 for g in gathered:

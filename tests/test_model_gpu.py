@@ -85,3 +85,35 @@ def test_graph_replay_matches_eager(ext):
         h.copy_(eng.step_host(h))
         seq.append(h.clone())
     assert torch.equal(torch.stack(seq, 1), outs[0].cpu())
+
+
+def test_folded_collective_decode_path_matches_default(ext, monkeypatch):
+    """BL_DLIN=1 (one kernel per linear, all-reduce halves folded into epilogue and prologue,
+    RoPE + KV write + attention + split merge in one kernel) yields the same tokens as the
+    default single-GPU path; both run the captured graph for several steps."""
+    from barlink_sm86_b200.models import DecodeEngine, Qwen2Model
+    from barlink_sm86_b200.parallel import TPComm
+
+    def run(flag):
+        monkeypatch.setenv("BL_DLIN", flag)
+        cfg = _cfg()
+        m = Qwen2Model(cfg, TPComm.single(), "cuda:0", torch.bfloat16, seed=5)
+        eng = DecodeEngine(m, batch=6, max_len=96, use_graph=True)
+        g = torch.Generator().manual_seed(7)
+        ids = torch.randint(0, cfg.vocab, (6, 40), generator=g, dtype=torch.int32).cuda()
+        first = eng.prefill(ids)
+        eng.ids.copy_(first)
+        eng.capture()
+        toks = [first.clone()]
+        for _ in range(8):
+            toks.append(eng.step().clone())
+        torch.cuda.synchronize()
+        assert ext.gemm_error_flag(0) == 0 and ext.dlin_error_flag(0) == 0
+        return torch.stack(toks), eng.launches_per_step
+
+    want, l0 = run("0")
+    got, l1 = run("1")
+    assert l1 < l0
+    # greedy tokens of a random-init model are near ties now and then: allow a late divergence
+    agree = (want == got).float().mean().item()
+    assert torch.equal(want[:3], got[:3]) and agree > 0.9, (agree, want, got)

@@ -20,10 +20,11 @@ def _free_port():
     return p
 
 
-def _run_ranks(script, world, timeout=600):
+def _run_ranks(script, world, timeout=600, extra_env=None):
     port = _free_port()
     env = dict(os.environ)
     env["NCCL_NVLS_ENABLE"] = "0"
+    env.update(extra_env or {})
     env.setdefault("BL_PG_ID", "t%d" % port)
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, script), str(r), str(world), str(port)],
                               env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
@@ -54,6 +55,19 @@ def test_process_group_over_the_link(world):
     if world not in _worlds():
         pytest.skip("needs %d GPUs" % world)
     print(_run_ranks("_pg_worker.py", world))
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_process_group_with_in_switch_reduction(world):
+    """The same worker with the arenas bound to an NVSwitch multicast object (BL_NVLS=1): the
+    multimem all-reduce is exercised bit-exactly; the worker leaves out its timed-out-wait case
+    and every rank exits through barrier -> shutdown."""
+    if world not in _worlds():
+        pytest.skip("needs %d GPUs" % world)
+    out = _run_ranks("_pg_worker.py", world, extra_env={"BL_NVLS": "1"})
+    print(out)
+    if "multicast=True" in out:
+        assert "nvls large messages ok" in out
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])

@@ -70,3 +70,43 @@ def test_reference_api_pair(ext, M, S):
     part = (xq.double().view(M, K // 128, 128)[:, :, None, :] * wq.double().view(N, K // 128, 128).permute(1, 0, 2)[None]).sum(-1)
     want = (part * sw.double()[None]).sum(1) * xs.double()[:, None]
     assert rel_l2(y, want) < 2e-2
+
+
+@pytest.mark.parametrize("m,n,k,group", [(1, 512, 3072, 128), (16, 5120, 5120, 128), (64, 3456, 5120, 128),
+                                         (200, 640, 1024, 64), (8, 384, 1536, 256)])
+def test_group_scales_inside_the_kernel(ext, m, n, k, group):
+    """Per-group scales (the reference kernel's granularity) applied while the tile is widened:
+    against fp64 on the quantised operands, the reference's criterion."""
+    from barlink_sm86_b200 import ops
+    from barlink_sm86_b200.ops import reference as ref
+    g = torch.Generator(device="cuda").manual_seed(11)
+    w = torch.randn(n, k, device="cuda", generator=g) * 0.02
+    w[:, : k // 2] *= 7.0   # groups of one row differ by an order of magnitude
+    wq, scale = ref.quantize_w8_grouped(w, group)
+    x = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    gs = ops.prepare_w8_scales(scale, k)
+    got = ops.w8a16_linear(x, wq, gs)
+    got2 = ops.w8a16_linear(x, wq, scale)   # raw 2-D scales: prepared on the fly, same kernel
+    torch.cuda.synchronize()
+    assert ext.w8_error_flag(0) == 0
+    want = x.double() @ ref.w8_dequant(wq, scale).double().t()
+    assert rel_l2(got, want) < 2e-2, (m, n, k, group)
+    assert torch.equal(got, got2)
+
+
+def test_prefill_dequant_then_gemm_has_no_weight_prefetch_race(ext):
+    """More than 256 tokens: the weight is widened into a fresh buffer and the bf16 GEMM runs on
+    it.  The GEMM must not request weight tiles before the widening kernel has finished: a large
+    weight on a reused, garbage-filled buffer, many times."""
+    from barlink_sm86_b200.ops import reference as ref
+    n, k, m = 18944, 3584, 512
+    wq, scale = _quant(n, k, 21)
+    x = torch.randn(m, k, device="cuda", generator=torch.Generator("cuda").manual_seed(22)).to(torch.bfloat16)
+    want = ref.w8a16_linear(x, wq, scale)
+    for it in range(6):
+        junk = torch.full((n, k), float("nan"), dtype=torch.bfloat16, device="cuda")  # the allocator hands this block back
+        del junk
+        got = ext.w8a16_linear(x, wq, scale)
+        torch.cuda.synchronize()
+        assert torch.isfinite(got.float()).all(), it
+        assert rel_l2(got, want) < 1.5e-2, it
