@@ -4,6 +4,9 @@
 // core (CUDA tensors) or onto an inner gloo backend (CPU tensors).
 // See backend.h for the contract kept from the reference's Python backend
 // (torch_ext/barlink_sm86/process_group.py:134-520).
+#include <stdio.h>
+#include <stdlib.h>
+
 #include "backend.h"
 
 #include <ATen/cuda/CUDAContext.h>
@@ -129,7 +132,13 @@ void BarlinkBackend::allreduce_cuda(at::Tensor& t) {
       BL_CALL(bl_allreduce_into_peer(c, p + off, p + off, len, code, BL_ALGO_AUTO, st, err, errlen));
     }
   };
-  if (aligned_ok(t)) {
+  // ablation / debug switches of the reference's backend (torch_ext/barlink_sm86/process_group.py:
+  // 137-148 BL_AR_TRACE, :185 BL_AR_NO_ZC): force the staged path; print a checksum per call
+  static const bool no_zc = getenv("BL_AR_NO_ZC") && getenv("BL_AR_NO_ZC")[0] != '0';
+  static const bool trace = getenv("BL_AR_TRACE") && getenv("BL_AR_TRACE")[0] != '0';
+  double before = 0.0;
+  if (trace) before = t.to(at::kDouble).sum().item<double>();
+  if (aligned_ok(t) && !no_zc) {
     ++n_zero_copy;
     run(static_cast<char*>(t.data_ptr()), t.nbytes());
   } else {
@@ -137,6 +146,13 @@ void BarlinkBackend::allreduce_cuda(at::Tensor& t) {
     at::Tensor tmp = padded_copy(t);
     run(static_cast<char*>(tmp.data_ptr()), tmp.nbytes());
     t.copy_(tmp.narrow(0, 0, t.numel()).view(t.sizes()));
+  }
+  if (trace) {
+    // synchronises: a debugging aid, never on in a timed run
+    const double after = t.to(at::kDouble).sum().item<double>();
+    fprintf(stderr, "[barlink rank %d] all_reduce #%llu %s %lld elements: checksum %.6g -> %.6g (%s)\n", getRank(),
+            (unsigned long long)(n_zero_copy + n_staged), c10::toString(t.scalar_type()), (long long)t.numel(),
+            before, after, (aligned_ok(t) && !no_zc) ? "zero-copy" : "staged");
   }
 }
 

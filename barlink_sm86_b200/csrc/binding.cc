@@ -523,6 +523,62 @@ at::Tensor linear(const at::Tensor& x, const at::Tensor& w, const c10::optional<
   return out;
 }
 
+// Row-parallel linear whose epilogue scatters the output tiles into the owners' staging inboxes
+// (first half of a two-shot all-reduce over a [total_rows, n] tensor; this call covers rows
+// row0 .. row0 + x.shape[0]).  Returns the arrival count to pass to allreduce_pushed.
+int linear_push(const at::Tensor& x, const at::Tensor& w, const c10::optional<at::Tensor>& bias,
+                const c10::optional<at::Tensor>& residual, bool gelu, int total_rows, int row0) {
+  check_bf16(w, "weight");
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1 &&
+                  w.dim() == 2 && w.size(1) == x.size(1),
+              "barlink: linear_push needs bf16 x [rows, k] and w [n, k]");
+  const int rows = int(x.size(0)), k = int(x.size(1)), n = int(w.size(0));
+  TORCH_CHECK(rows > 128 && n >= 256 && row0 >= 0 && row0 + rows <= total_rows,
+              "barlink: linear_push is for token-major products (more than 128 rows, n >= 256) inside total_rows");
+  const int dev = x.device().index();
+  c10::cuda::CUDAGuard guard(x.device());
+  Scratch& s = scratch_for(dev);
+  blRowPush push;
+  BL_CHECK(bl_gemm_push_setup(ctx_or_throw(), total_rows, n, row0, &push, err, errlen));
+  blGemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.a = x.data_ptr(); a.ra = rows; a.lda = int(x.stride(0));
+  a.b = w.data_ptr(); a.rb = n; a.ldb = k;
+  a.k = k;
+  a.ldo = n;
+  a.push = &push;
+  if (bias) {
+    check_bf16(*bias, "bias");
+    TORCH_CHECK(bias->numel() == n, "barlink: bias must have n elements");
+    a.bias = bias->data_ptr();
+  }
+  if (residual) {
+    check_bf16(*residual, "residual");
+    TORCH_CHECK(residual->dim() == 2 && residual->size(0) == rows && residual->size(1) == n,
+                "barlink: residual must be [rows, n]");
+    a.residual = residual->data_ptr();
+  }
+  a.gelu = gelu ? 1 : 0;
+  a.err_flag = s.err_flag.data_ptr();
+  void* st = at::cuda::getCurrentCUDAStream(dev).stream();
+  {
+    py::gil_scoped_release nogil;
+    BL_CHECK(bl_gemm_bf16(&a, st, err, errlen));
+  }
+  return bl_gemm_push_units(rows, n);
+}
+
+// second half: out [total_rows, n] bf16 receives the all-reduced tensor on every rank
+void allreduce_pushed(const at::Tensor& out, int units) {
+  check_bf16(out, "out");
+  TORCH_CHECK(out.dim() == 2, "barlink: allreduce_pushed needs a [rows, n] output");
+  c10::cuda::CUDAGuard guard(out.device());
+  void* st = at::cuda::getCurrentCUDAStream(out.device().index()).stream();
+  py::gil_scoped_release nogil;
+  BL_CHECK(bl_allreduce_pushed(ctx_or_throw(), out.data_ptr(), int(out.size(0)), int(out.size(1)), units, st, err,
+                               errlen));
+}
+
 int gemm_splits(int n, int k, int tokens) { return bl_gemm_splits(n, k, tokens); }
 
 // [n, k] bf16 -> flat buffer of 16 KiB tiles in the swizzled shared-memory image
@@ -1001,6 +1057,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("force_swap") = -1, py::arg("bn") = 0, py::arg("splits") = 0,
         py::arg("dynamic_weights") = false, py::arg("trace") = py::none(), py::arg("gate_tokens") = 0,
         py::arg("tiled_n") = 0, py::arg("tiled_k") = 0, py::arg("gelu") = false);
+  m.def("linear_push", &linear_push, py::arg("x"), py::arg("weight"), py::arg("bias") = py::none(),
+        py::arg("residual") = py::none(), py::arg("gelu") = false, py::arg("total_rows"), py::arg("row0") = 0);
+  m.def("allreduce_pushed", &allreduce_pushed, py::arg("out"), py::arg("units"));
   m.def("gemm_error_flag", &gemm_error_flag, py::arg("device") = 0);
   m.def("rmsnorm", &rmsnorm, py::arg("x"), py::arg("gamma"), py::arg("eps"),
         py::arg("residual") = py::none(), py::arg("out") = py::none());

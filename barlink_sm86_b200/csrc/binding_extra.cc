@@ -413,7 +413,7 @@ DlinScratch& dlin_scratch(int dev) {
   if (it != m.end()) return it->second;
   auto o = at::TensorOptions().device(at::kCUDA, dev).dtype(at::kInt);
   DlinScratch s;
-  s.sync = at::zeros({4}, o);
+  s.sync = at::zeros({16 + 64 * 8}, o);  // counters, then the segment sums of the gather prologue
   s.err_flag = at::zeros({4}, o);
   return m.emplace(dev, s).first->second;
 }

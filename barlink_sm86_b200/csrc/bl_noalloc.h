@@ -2,12 +2,11 @@
  *
  * Arg max without any allocation.  This entry point has no counterpart in the
  * reference; it exists for callers of this library that are not allowed to
- * allocate device memory at the moment they call: code running while a stream
- * is being captured into a CUDA graph, code inside another framework's
- * allocator callback or memory-pool critical section, and embedders that hand
- * the library a fixed memory budget up front and forbid cudaMalloc afterwards
- * (cudaMalloc synchronises the device and can fail at an unpredictable
- * point).
+ * allocate device memory at the moment they call: code inside another
+ * framework's allocator callback or memory-pool critical section, and
+ * embedders that hand the library a fixed memory budget up front and forbid
+ * cudaMalloc afterwards (cudaMalloc synchronises the device and can fail at an
+ * unpredictable point).
  *
  * bl_argmax (bl_ops.h) needs a scratch buffer from its caller for the
  * per-slice partial results of its first kernel.  bl_argmax_noalloc runs the

@@ -30,6 +30,19 @@ typedef struct blPeerSink {
   int world, rank, tokens_per_rank;
 } blPeerSink;
 
+/* Token-major row-parallel linear whose epilogue is the scatter half of a two-shot all-reduce:
+ * output row m (global index row0 + m of a [total_rows x n] tensor) is stored, as bf16 16-byte
+ * vectors, straight into the staging inbox of the rank that owns that row (rank (row0 + m) /
+ * rows_per_rank), and every finished tile bumps the owners' arrival counters.  bl_allreduce_pushed
+ * then reduces this rank's rows and hands the sums to every rank.  Filled by bl_gemm_push_setup. */
+typedef struct blRowPush {
+  void* arena[BL_MAX_RANKS];   /* every rank's arena as mapped here */
+  void* flag[BL_MAX_RANKS];    /* each owner's arrival word for this source rank */
+  const void* seq_word;        /* this rank's count of staged collectives (selects the staging buffer) */
+  size_t stage_off, stage_slice;
+  int world, rank, rows_per_rank, row0;
+} blRowPush;
+
 /* D[i, j] = sum_k A[i, k] * B[j, k]; A [ra x k] pitch lda, B [rb x k] pitch
  * ldb, bf16, K-major.  swap = 0: out[i, j]; swap = 1: out[j, i] (A = weight
  * rows, B = tokens: the decode orientation).  out is bf16 with pitch ldo.
@@ -69,6 +82,9 @@ typedef struct blGemmArgs {
   int partial_splits;
   /* fused reduce-scatter (swap orientation only): partial rows go to peers */
   const blPeerSink* peer;
+  /* token-major orientation: the output tile goes to the owners' staging inboxes (see blRowPush);
+   * out is ignored, ldo must be n, no k-split */
+  const blRowPush* push;
   /* fused all-gather in front: wait for gate_n words at gate_flags to reach
    * *gate_cum + gate_add before the first activation tile is requested */
   const void* gate_flags;
@@ -264,6 +280,15 @@ int bl_gate_residual(void* x, const void* y, const void* gate, int rows, int hid
  * Offsets are into the symmetric arena (bl_pool_offset). */
 int bl_tp_peer_sink(blCtx* ctx, size_t inbox_off, int tokens, blPeerSink* out, char* err,
                     size_t errlen);
+/* rows of a [total_rows x n] bf16 all-reduce that a linear starting at row0 will push; fails when
+ * total_rows is not a multiple of the ranks or a rank's rows do not fit its staging slice */
+int bl_gemm_push_setup(blCtx* ctx, int total_rows, int n, int row0, blRowPush* out, char* err, size_t errlen);
+/* tiles (arrival counts per owner) that bl_gemm_bf16 will produce for a pushed linear of `rows` rows */
+int bl_gemm_push_units(int rows, int n);
+/* second half: wait for `units` arrivals from every rank, reduce this rank's rows in rank order in
+ * fp32, give the sums to every rank and write the whole [total_rows x n] result to out */
+int bl_allreduce_pushed(blCtx* ctx, void* out, int total_rows, int n, int units, void* stream, char* err,
+                        size_t errlen);
 int bl_tp_gate(blCtx* ctx, int tokens, blGemmArgs* a, char* err, size_t errlen);
 typedef struct blRsFinishArgs {
   size_t inbox_off;        /* fp32 [world][splits][tokens/world][n] in my arena */
@@ -291,8 +316,8 @@ int bl_tp_units(int n, int k_local, int tokens, int* splits_out);
  *            out[tokens, n/2] = SiLU(gate) * up; 2: y is rounded to bf16 and stored into every
  *            rank's inbox as this rank's partial of a [tokens, hidden] all-reduce.
  * The inboxes are the link's (ctx in peer mode) or, for a single GPU, a buffer of
- * bl_dlin_local_link_bytes() prepared once by bl_dlin_local_link_init().  sync: 4 zeroed u32
- * words that belong to this call site family (any number of launches may share them as long
+ * bl_dlin_local_link_bytes() prepared once by bl_dlin_local_link_init().  sync: 528 zeroed u32
+ * words (counters, then per-segment sums of squares) that belong to this call site family (any number of launches may share them as long
  * as they are in one stream).  cluster = 0 chooses the cluster size. */
 typedef struct blDlinArgs {
   const void* w;

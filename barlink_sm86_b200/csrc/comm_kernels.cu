@@ -252,6 +252,9 @@ __global__ void __launch_bounds__(kThreads) k_lamport(CollArgs a) {
 //   mode 1 reduce-scatter     (in: world slices of nvec, out: nvec)
 //   mode 2 all-gather         (in: nvec, out: world slices of nvec)
 //   mode 3 broadcast from root (in == out, nvec)
+//   mode 4 all-reduce whose scatter was done by the GEMM that produced the data (its epilogue
+//          stored every tile into the owners' inboxes and bumped their arrival counters): wait
+//          for a.iters arrivals from every rank, then reduce + all-gather as in mode 0
 // Block b owns, inside every slice, the vector indices (b + k*grid)*T + t.
 // A block only ever consumes what block b of a peer produced, so blocks
 // synchronise with their namesakes only (slot = blockIdx.x).
@@ -263,7 +266,8 @@ __global__ void __launch_bounds__(kThreads) k_staged(CollArgs a) {
   const int y = a.pack.emu ? blockIdx.y : 0;
   const int rank = c.rank, world = c.world;
   const int mode = a.mode;
-  const int proto = mode == 0 ? P_TWOSHOT : mode == 1 ? P_REDSCAT : mode == 2 ? P_ALLGATHER : P_BCAST;
+  const int proto = mode == 0 ? P_TWOSHOT : mode == 1 ? P_REDSCAT : mode == 2 ? P_ALLGATHER
+                    : mode == 3 ? P_BCAST : P_ROWPUSH;
   uint32_t* s = sig_of(c, rank);
   const uint32_t e = ld_volatile_u32(&s[sig_epoch(proto)]);
   const uint4* in = static_cast<const uint4*>(a.in[y]);
@@ -273,14 +277,14 @@ __global__ void __launch_bounds__(kThreads) k_staged(CollArgs a) {
   // slice geometry
   size_t sv;  // vectors per slice
   size_t total;
-  if (mode == 0) {
+  if (mode == 0 || mode == 4) {
     total = a.nvec;
     sv = (a.nvec + world - 1) / world;
   } else {
     sv = a.nvec;
     total = a.nvec * world;
   }
-  const size_t bs = (mode == 0 || a.slice_stride == 0) ? sv : a.slice_stride;  // big-operand pitch
+  const size_t bs = (mode == 0 || mode == 4 || a.slice_stride == 0) ? sv : a.slice_stride;  // big-operand pitch
   auto slice_len = [&](int r) -> size_t {
     size_t b = size_t(r) * sv;
     return b >= total ? 0 : (total - b < sv ? total - b : sv);
@@ -290,7 +294,35 @@ __global__ void __launch_bounds__(kThreads) k_staged(CollArgs a) {
   const size_t half = size_t(world) * c.stage_slice;  // inbox half, then outbox half
   bool ok = true;
 
-  if (mode == 0 || mode == 1) {
+  uint32_t push_cum = 0;
+  if (mode == 4) {
+    // the producers' tiles: every rank's arrival word must reach the running total
+    __shared__ int s_ok4;
+    push_cum = ld_volatile_u32(&s[sig_aux(P_ROWPUSH)]);
+    if (threadIdx.x == 0) s_ok4 = 1;
+    __syncthreads();
+    if (threadIdx.x < world &&
+        !wait_flag(c, s + sig_flag(P_ROWPUSH, kMaxSlots - 1, threadIdx.x), push_cum + uint32_t(a.iters), P_ROWPUSH, threadIdx.x))
+      s_ok4 = 0;
+    __syncthreads();
+    ok = s_ok4 != 0;
+    if (ok) {
+      const size_t len = slice_len(rank);
+      for (size_t j = first; j < len; j += stride) {
+        typename E::acc_t acc[E::N];
+#pragma unroll
+        for (int q = 0; q < E::N; ++q) acc[q] = 0;
+        for (int r = 0; r < world; ++r) acc_add<DT>(acc, ld_volatile_v4(my_stage + size_t(r) * c.stage_slice + j * 16));
+        const uint4 res = E::pack(acc);
+        out[size_t(rank) * sv + j] = res;
+        for (int k = 1; k < world; ++k) {
+          int p = rank + k;
+          if (p >= world) p -= world;
+          st_v4(c.base[p] + sbuf + half + size_t(rank) * c.stage_slice + j * 16, res);
+        }
+      }
+    }
+  } else if (mode == 0 || mode == 1) {
     // scatter: slice p of my input goes to rank p's inbox [rank]
     for (int k = 1; k < world; ++k) {
       int p = rank + k;
@@ -355,7 +387,7 @@ __global__ void __launch_bounds__(kThreads) k_staged(CollArgs a) {
       } else {
         for (int r = 0; r < world; ++r) {
           if (r == rank) continue;
-          const size_t len = mode == 0 ? slice_len(r) : sv;
+          const size_t len = (mode == 0 || mode == 4) ? slice_len(r) : sv;
           const char* src = my_stage + half + size_t(r) * c.stage_slice;
           for (size_t j = first; j < len; j += stride)
             out[size_t(r) * bs + j] = ld_volatile_v4(src + j * 16);
@@ -363,7 +395,7 @@ __global__ void __launch_bounds__(kThreads) k_staged(CollArgs a) {
       }
     }
   }
-  finish_epoch(c, proto, e, 0, false, true);
+  finish_epoch(c, proto, e, push_cum + uint32_t(a.iters), mode == 4, true);
 }
 
 // ---------------------------------------------------------------------------
@@ -869,6 +901,19 @@ static int launch_local(blCtx* ctx, K kernel, CollArgs base, const PerRank* pr, 
       kernel<<<dim3(grid_x, 1, 1), threads, 0, static_cast<cudaStream_t>(pr[0].stream)>>>(a);
     }
     RT_TRY(cudaGetLastError(), "collective launch");
+    // BL_CAPDBG=1 (the reference's per-launch error bisect, torch_ext/barlink_sm86/core.cu:2726-2736):
+    // wait for every collective kernel and report the first one that fails; off while capturing
+    static const bool capdbg = env_flag_set("BL_CAPDBG");
+    if (capdbg) {
+      cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+      cudaStream_t st = static_cast<cudaStream_t>(pr[0].stream);
+      if (cudaStreamIsCapturing(st, &cs) == cudaSuccess && cs == cudaStreamCaptureStatusNone) {
+        const cudaError_t e = cudaStreamSynchronize(st);
+        fprintf(stderr, "[barlink capdbg] rank %d collective kernel (grid %d): %s\n", ctx->rank, grid_x,
+                cudaGetErrorString(e));
+        RT_TRY(e, "collective kernel");
+      }
+    }
     return 0;
   }
   int cur = 0;
@@ -1762,4 +1807,75 @@ extern "C" int bl_rs_finish(blCtx* ctx, const blRsFinishArgs* a, void* stream, c
   ctx->stats[BL_STAT_OPS]++;
   ctx->stats[BL_STAT_FUSED_NORM]++;
   return 0;
+}
+
+// ---------------------------------------------------------------------------
+// all-reduce whose scatter half is the epilogue of the GEMM that produced the data
+// ---------------------------------------------------------------------------
+extern "C" int bl_gemm_push_setup(blCtx* ctx, int total_rows, int n, int row0, blRowPush* out, char* err,
+                                  size_t errlen) {
+  if (!ctx || !ctx->peer_mode || !out) {
+    set_err(err, errlen, "barlink: a pushed linear needs an SPMD context (init_peer)");
+    return -1;
+  }
+  if (total_rows < ctx->world || total_rows % ctx->world || n < 8 || (n & 7) || row0 < 0 || row0 >= total_rows) {
+    set_err(err, errlen, "barlink: pushed all-reduce needs rows that are a multiple of the %d ranks and n %% 8 == 0 (rows %d, n %d)",
+            ctx->world, total_rows, n);
+    return -1;
+  }
+  const size_t per_rank = size_t(total_rows / ctx->world) * size_t(n) * 2;
+  if (per_rank > ctx->layout.stage_slice) {
+    set_err(err, errlen, "barlink: %zu B per rank exceed the %zu B staging slice (raise BL_POOL_MB or split the rows)",
+            per_rank, ctx->layout.stage_slice);
+    return -1;
+  }
+  if (check_health(ctx, err, errlen) != 0) return -1;
+  memset(out, 0, sizeof(*out));
+  out->world = ctx->world;
+  out->rank = ctx->rank;
+  out->rows_per_rank = total_rows / ctx->world;
+  out->row0 = row0;
+  out->stage_off = ctx->layout.stage_off;
+  out->stage_slice = ctx->layout.stage_slice;
+  char* mine = reinterpret_cast<char*>(ctx->arena[ctx->rank].va);
+  out->seq_word = reinterpret_cast<uint32_t*>(mine + ctx->layout.sig_off) + kSigStageSeq;
+  for (int r = 0; r < ctx->world; ++r) {
+    char* base = reinterpret_cast<char*>(ctx->arena[r].va);
+    out->arena[r] = base;
+    out->flag[r] = reinterpret_cast<uint32_t*>(base + ctx->layout.sig_off) + sig_flag(P_ROWPUSH, kMaxSlots - 1, ctx->rank);  // the last slot: the blocks' own syncs use slots < 128
+  }
+  return 0;
+}
+
+extern "C" int bl_allreduce_pushed(blCtx* ctx, void* out, int total_rows, int n, int units, void* stream, char* err,
+                                   size_t errlen) {
+  if (!ctx || !ctx->peer_mode) {
+    set_err(err, errlen, "barlink: allreduce_pushed needs an SPMD context (init_peer)");
+    return -1;
+  }
+  if (!out || !aligned16(out) || total_rows % ctx->world || units < 1) {
+    set_err(err, errlen, "barlink: allreduce_pushed needs a 16-byte aligned output, rows that split over the ranks and units >= 1");
+    return -1;
+  }
+  if (check_health(ctx, err, errlen) != 0) return -1;
+  const size_t bytes = size_t(total_rows) * size_t(n) * 2;
+  if (bytes / size_t(ctx->world) > ctx->layout.stage_slice) {
+    set_err(err, errlen, "barlink: %zu B per rank exceed the staging slice", bytes / size_t(ctx->world));
+    return -1;
+  }
+  CollArgs a;
+  memset(&a, 0, sizeof(a));
+  a.nvec = bytes / 16;
+  a.mode = 4;
+  a.iters = units;
+  PerRank pr;
+  pr.in = out;
+  pr.out = out;
+  pr.stream = stream;
+  const int grid = pick_grid(ctx, (a.nvec + ctx->world - 1) / ctx->world, kThreads, 128);
+  const int rc = launch_local(ctx, k_staged<BL_DTYPE_BF16>, a, &pr, grid, kThreads, err, errlen);
+  ctx->stats[BL_STAT_TWOSHOT]++;
+  ctx->stats[BL_STAT_OPS]++;
+  ctx->stats[BL_STAT_BYTES] += bytes;
+  return rc;
 }

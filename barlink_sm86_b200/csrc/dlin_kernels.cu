@@ -61,7 +61,9 @@ struct DlinParams {
   const uint4* gamma;
   uint4* xnorm;   // the activation operand, [tokens][k] bf16, written here and read back by TMA
   float eps;
-  uint32_t* sync; // [0] rows published so far (all launches), [1] that count at launch, [2] exit ticket
+  uint32_t* sync; // [0] row segments published so far (all launches), [1] that count at launch, [2] exit ticket
+  float* ss_part; // [tokens][nseg] sums of squares of the row segments (nseg = ceil(k / 1024))
+  int pro_ctas;   // CTAs that share the gather: the first ones of the grid, all resident together
   // epilogue
   __nv_bfloat16* out;
   int ldo;
@@ -72,88 +74,25 @@ struct DlinParams {
   Comm c;         // the link (or its one-rank stand-in in local memory)
 };
 
-template <int BN>
+// CPS = CTAs per SM.  1: a deep operand ring and an exchange buffer of its own.  2: half the
+// shared memory, so that the CTAs of the next linear are already resident (barriers, TMEM and the
+// first weight tiles in place) while this one finishes; the exchange buffer then reuses the ring,
+// which costs one more cluster barrier (nobody may write into a ring that is still being read).
+template <int BN, int CPS>
 struct DlinSmem {
   static constexpr int kStageA = kTileA * kTileK * 2;
   static constexpr int kStageB = BN * kTileK * 2;
   static constexpr int kStageBytes = kStageA + kStageB;
-  static constexpr int kStages = BN >= 64 ? 7 : 8;
+  static constexpr int kStages = CPS == 2 ? 4 : (BN >= 64 ? 7 : 8);
   static constexpr int kXbufBytes = BN >= 64 ? 52224 : 32768;  // checked against the cluster shape at launch
+  static constexpr int kStageTileOff = CPS == 2 ? 65536 : 0;    // bf16 staging tile of the push epilogue
   static constexpr int kBarBytes = 1024;
-  static constexpr int kBytes = kBarBytes + 1024 + kStages * kStageBytes + kXbufBytes;
+  static constexpr int kBytes = kBarBytes + 1024 + kStages * kStageBytes + (CPS == 2 ? 0 : kXbufBytes);
   static constexpr int kTmemCols = BN < 32 ? 32 : BN;
+  static_assert(CPS == 1 || kStages * kStageBytes >= kStageTileOff + BN * kTileA * 2, "staging tile must fit the ring");
 };
 
 __device__ __forceinline__ void bar_epi() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-// One token row of the fused all-reduce + residual + RMSNorm, done by the 128
-// epilogue threads of a CTA: poll the row's vectors in every rank's inbox slot
-// (buffer e % 3), sum them in rank order in fp32, round to bf16 as an all-reduce
-// would, add the residual, write the new residual, normalise, write the row of
-// the activation operand.  Returns false if a poll ran out.
-__device__ __forceinline__ bool dlin_gather_row(const DlinParams& p, int row, int et, size_t cur_off,
-                                                float* s_part) {
-  using E = Elem<BL_DTYPE_BF16>;
-  const Comm& c = p.c;
-  const int vpr = p.k / 8;
-  float x[kDlinMaxVpt][8];
-  float ss = 0.f;
-  bool ok = true;
-#pragma unroll
-  for (int v = 0; v < kDlinMaxVpt; ++v) {
-    const int i = et + v * 128;
-    if (i < vpr) {
-      const size_t g = size_t(row) * vpr + i;
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      // requests for all ranks' vectors go out together; the ones not yet landed are polled
-      uint4 got[kMaxRanks];
-#pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r)
-        if (r < c.world) got[r] = ld_volatile_v4(c.base[c.rank] + cur_off + size_t(r) * c.lamport_slice + g * 16);
-#pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r)
-        if (r < c.world) {
-          uint4 w = got[r];
-          if (!landed(w) && !poll_vec(c, c.base[c.rank] + cur_off + size_t(r) * c.lamport_slice + g * 16, w, r))
-            ok = false;
-          acc_add<BL_DTYPE_BF16>(acc, w);
-        }
-      uint4 packed = E::pack(acc);  // the all-reduce result in its storage type
-      if (p.res_in) {
-        E::unpack(packed, acc);
-        acc_add<BL_DTYPE_BF16>(acc, p.res_in[g]);
-        packed = E::pack(acc);
-      }
-      p.res_out[g] = packed;
-      E::unpack(packed, x[v]);  // the norm sees the rounded residual
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss += x[v][j] * x[v][j];
-    }
-  }
-  ss = warp_sum(ss);
-  if ((et & 31) == 0) s_part[et >> 5] = ss;
-  bar_epi();
-  const float tot = s_part[0] + s_part[1] + s_part[2] + s_part[3];
-  const float rstd = rsqrtf(tot / float(p.k) + p.eps);
-#pragma unroll
-  for (int v = 0; v < kDlinMaxVpt; ++v) {
-    const int i = et + v * 128;
-    if (i < vpr) {
-      float gm[8], o[8];
-      E::unpack(p.gamma[i], gm);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = x[v][j] * rstd;
-      // x * rstd is rounded to bf16 before the weight multiply, as a framework RMSNorm module does
-      uint4 t = E::pack(o);
-      E::unpack(t, o);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] *= gm[j];
-      p.xnorm[size_t(row) * vpr + i] = E::pack(o);
-    }
-  }
-  bar_epi();  // s_part is reused by the next row
-  return ok;
-}
 
 // Reset the inbox buffer that the call before this one used (it is written again two calls
 // from now); every CTA of the grid takes a share.
@@ -164,11 +103,97 @@ __device__ __forceinline__ void dlin_clear_prev(const Comm& c, uint32_t e, uint3
     for (int r = 0; r < c.world; ++r) st_v4(c.base[c.rank] + clr_off + size_t(r) * c.lamport_slice + i * 16, unw);
 }
 
-template <int BN>
-__global__ void __launch_bounds__(kDlinThreads, 1)
+// The in-kernel form of the same gather, spread over the whole grid: the unit of work is a
+// segment of 128 consecutive 16-byte vectors of one row (one vector per epilogue thread), dealt
+// out to the CTAs round robin, two segments in flight per thread so that all loads of a step go
+// out before the first one is needed.  A segment's thread sums the ranks' vectors, adds the
+// residual, stores the new residual, stores residual * gamma as the activation operand and the
+// block leaves the segment's sum of squares in ss_part[row][seg].  1 / rms is applied to the
+// product by the epilogue (it is a per-token scale), so no thread waits for a whole row here.
+__device__ __forceinline__ bool dlin_gather_segments(const DlinParams& p, int et, size_t cur_off, float* s_part,
+                                                     int* done_out) {
+  using E = Elem<BL_DTYPE_BF16>;
+  const Comm& c = p.c;
+  const int vpr = p.k / 8;
+  const int nseg = (vpr + 127) / 128;
+  const int total = p.tokens * nseg;
+  const char* inbox = c.base[c.rank] + cur_off;
+  bool ok = true;
+  int done = 0;
+  const int nc = p.pro_ctas;  // only CTAs that are certainly resident together may be waited for
+  for (int s0 = blockIdx.x; s0 < total && int(blockIdx.x) < nc; s0 += 2 * nc) {
+    uint4 got[2][kMaxRanks];
+    uint4 resv[2], gam[2];
+    size_t g[2];
+    bool act[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int sidx = s0 + u * nc;
+      const int row = sidx / nseg, sg = sidx - row * nseg;
+      const int i = sg * 128 + et;
+      act[u] = sidx < total && i < vpr;
+      g[u] = size_t(row) * vpr + i;
+      if (act[u]) {
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          if (r < c.world) got[u][r] = ld_volatile_v4(inbox + size_t(r) * c.lamport_slice + g[u] * 16);
+        if (p.res_in) resv[u] = __ldcg(p.res_in + g[u]);
+        gam[u] = __ldg(p.gamma + i);
+      }
+    }
+    float ss[2] = {0.f, 0.f};
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (act[u]) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          if (r < c.world) {
+            uint4 w = got[u][r];
+            if (!landed(w) && !poll_vec(c, inbox + size_t(r) * c.lamport_slice + g[u] * 16, w, r)) ok = false;
+            acc_add<BL_DTYPE_BF16>(acc, w);
+          }
+        uint4 packed = E::pack(acc);  // the all-reduce result in its storage type
+        if (p.res_in) {
+          E::unpack(packed, acc);
+          acc_add<BL_DTYPE_BF16>(acc, resv[u]);
+          packed = E::pack(acc);
+        }
+        p.res_out[g[u]] = packed;
+        float x[8], gm[8];
+        E::unpack(packed, x);
+        E::unpack(gam[u], gm);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          ss[u] += x[j] * x[j];
+          x[j] *= gm[j];
+        }
+        p.xnorm[g[u]] = E::pack(x);
+      }
+    }
+    ss[0] = warp_sum(ss[0]);
+    ss[1] = warp_sum(ss[1]);
+    if ((et & 31) == 0) {
+      s_part[et >> 5] = ss[0];
+      s_part[4 + (et >> 5)] = ss[1];
+    }
+    bar_epi();
+    if (et < 2) {
+      const int sidx = s0 + et * nc;
+      if (sidx < total) p.ss_part[sidx] = s_part[4 * et] + s_part[4 * et + 1] + s_part[4 * et + 2] + s_part[4 * et + 3];
+    }
+    bar_epi();  // s_part is reused by the next pair
+    done += (s0 < total) + (s0 + nc < total);
+  }
+  *done_out = done;
+  return ok;
+}
+
+template <int BN, int CPS>
+__global__ void __launch_bounds__(kDlinThreads, CPS)
     k_dlin(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
            const __grid_constant__ DlinParams p) {
-  using S = DlinSmem<BN>;
+  using S = DlinSmem<BN, CPS>;
   extern __shared__ uint8_t smem_raw[];
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem_raw);
   uint64_t* empty_bar = full_bar + S::kStages;
@@ -178,7 +203,7 @@ __global__ void __launch_bounds__(kDlinThreads, 1)
   volatile uint32_t* s_late = tmem_slot + 2;  // a link wait ran out: results are not valid
   float* s_part = reinterpret_cast<float*>(tmem_slot + 4);
   const uint32_t ring = (smem_u32(smem_raw) + S::kBarBytes + 1023u) & ~1023u;
-  const uint32_t xbuf = ring + S::kStages * S::kStageBytes;
+  const uint32_t xbuf = CPS == 2 ? ring : ring + S::kStages * S::kStageBytes;
 
   pdl_launch_dependents();
   unsigned long long* tr = p.trace ? p.trace + size_t(blockIdx.x) * 12 : nullptr;
@@ -193,6 +218,8 @@ __global__ void __launch_bounds__(kDlinThreads, 1)
   // columns (tokens) of the tile are dealt out to the CTAs of the cluster for the final sum
   const int ncol = p.tokens < BN ? p.tokens : BN;
   const int cpc = p.cpc, cpcp = p.cpcp;
+  const int nseg_row = (p.k / 8 + 127) / 128;       // prologue: segments per row
+  const int nseg_total = p.tokens * nseg_row;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::kStages; ++s) {
@@ -231,10 +258,10 @@ __global__ void __launch_bounds__(kDlinThreads, 1)
       if (tr) tr[2] = globaltimer_ns();
       if (p.pro) {
         // rows of the activation operand are being written by the first CTAs of this grid
-        const uint32_t want = *reinterpret_cast<volatile uint32_t*>(p.sync + 1) + uint32_t(p.tokens);
+        const uint32_t want = *reinterpret_cast<volatile uint32_t*>(p.sync + 1) + uint32_t(nseg_total);
         const uint64_t t0 = globaltimer_ns();
         uint32_t polls = 0;
-        while (int32_t(ld_acquire_sys(p.sync) - want) < 0) {
+        while (int32_t(ld_acquire_gpu(p.sync) - want) < 0) {
           if ((++polls & 63u) == 0u && globaltimer_ns() - t0 > p.c.timeout_ns + 500000000ull) {
             *s_late = 1;  // give up waiting; the product is computed on whatever is there
             break;
@@ -303,25 +330,37 @@ __global__ void __launch_bounds__(kDlinThreads, 1)
       const uint32_t prev_vecs = ld_volatile_u32(&sg[sig_aux(P_LAMPORT)]);
       const size_t cur_off = c.lamport_off + size_t(e % 3u) * (size_t(c.world) * c.lamport_slice);
       int done = 0;
-      bool ok = true;
-      for (int r = blockIdx.x; r < p.tokens; r += gridDim.x, ++done) ok = dlin_gather_row(p, r, et, cur_off, s_part) && ok;
+      const bool ok = dlin_gather_segments(p, et, cur_off, s_part, &done);
       if (!ok) *s_late = 1;
       if (done > 0) {
-        __threadfence();
+        // the barrier orders the other threads' stores before thread 0's release (cumulativity)
         bar_epi();
-        if (et == 0) red_release_sys_add(p.sync, uint32_t(done));
+        if (et == 0) red_release_gpu_add(p.sync, uint32_t(done));
       }
       dlin_clear_prev(c, e, prev_vecs, et);
       if (tr && et == 0) tr[6] = globaltimer_ns();
     }
-    // partial accumulator -> the owners' exchange buffers: xbuf[src q][row][column], rows
-    // `cpcp` floats apart (cpcp % 8 == 4: the 16-byte accesses below are conflict free).  Four
-    // consecutive columns always belong to one owner (cpc is a multiple of 4).
     if (nkb > 0 && !mbar_wait_bounded(tfull_bar, 0, s_abort)) {
       // the accumulator never became ready: nothing valid to hand over
     }
     tc_fence_after_sync();
     if (tr && et == 0) tr[7] = globaltimer_ns();
+  }
+
+  if constexpr (CPS == 2) {
+    // the exchange buffers live in the operand rings: every CTA of the cluster must be done
+    // with its main loop before anyone stores into a ring
+    __syncwarp();
+    cluster_sync_all();
+  }
+
+  if (warp >= 2) {
+    // partial accumulator -> the owners' exchange buffers: xbuf[src q][row][column], rows
+    // `cpcp` floats apart (cpcp % 8 == 4: the 16-byte accesses below are conflict free).  Four
+    // consecutive columns always belong to one owner (cpc is a multiple of 4).
+    const int et = threadIdx.x - 64;
+    const int q4 = warp & 3;
+    const int row = q4 * 32 + lane;
     const uint32_t taddr = tmem_base + (uint32_t(q4 * 32) << 16);
     const bool have = nkb > 0 && !*s_abort;
     constexpr int kChunk = BN < 32 ? 16 : 32;
@@ -371,11 +410,26 @@ __global__ void __launch_bounds__(kDlinThreads, 1)
     const uint32_t xrow = xbuf + uint32_t(row * cpcp * 4);
     const uint32_t src_stride = uint32_t(kTileA * cpcp * 4);
     const float bv = (nok && p.bias && p.epi != 2) ? __bfloat162float(p.bias[feat]) : 0.f;
+    // with the gather prologue the operand rows were residual * gamma: the missing 1 / rms of each
+    // token scales that token's column of the product
+    float* s_rstd = reinterpret_cast<float*>(smem_raw + 512);
+    if (p.pro) {
+      if (et < mine) {
+        // the segment sums were stored before the segments were published: acquire that count
+        const uint32_t want = *reinterpret_cast<volatile uint32_t*>(p.sync + 1) + uint32_t(nseg_total);
+        for (uint32_t polls = 0; int32_t(ld_acquire_gpu(p.sync) - want) < 0 && polls < (1u << 22); ++polls) {
+        }
+        float sum = 0.f;
+        for (int sg = 0; sg < nseg_row; ++sg) sum += __ldcg(p.ss_part + size_t(col0 + et) * nseg_row + sg);
+        s_rstd[et] = rsqrtf(sum / float(p.k) + p.eps);
+      }
+      bar_epi();
+    }
     // epi 2: the reduced tile goes through shared memory once more ([column][row] bf16, in the
     // operand ring, which nothing reads any more) so that it leaves as 16-byte vectors
-    const uint32_t stg = ring;
+    const uint32_t stg = ring + S::kStageTileOff;
     for (int cc = 0; cc < mine; cc += 4) {
-      float v[4] = {bv, bv, bv, bv};
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
       for (int s = 0; s < CL; ++s) {
         float4 t;
         asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];"
@@ -383,6 +437,8 @@ __global__ void __launch_bounds__(kDlinThreads, 1)
                      : "r"(xrow + uint32_t(s) * src_stride + uint32_t(cc * 4)));
         v[0] += t.x; v[1] += t.y; v[2] += t.z; v[3] += t.w;
       }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = v[j] * ((p.pro && cc + j < mine) ? s_rstd[cc + j] : 1.f) + bv;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int m = col0 + cc + j;
@@ -445,7 +501,7 @@ __global__ void __launch_bounds__(kDlinThreads, 1)
       if (t == gridDim.x - 1) {
         p.sync[2] = 0;
         __threadfence();
-        *reinterpret_cast<volatile uint32_t*>(p.sync + 1) = p.sync[1] + uint32_t(p.tokens);
+        *reinterpret_cast<volatile uint32_t*>(p.sync + 1) = p.sync[1] + uint32_t(nseg_total);
       }
     }
   }
@@ -455,21 +511,103 @@ __global__ void __launch_bounds__(kDlinThreads, 1)
   }
 }
 
-// The prologue alone: all-reduce (second half) + residual + RMSNorm in front of a
-// linear that keeps its own kernel (the vocabulary head).  One row per block.
-__global__ void __launch_bounds__(128) k_gather_norm(const __grid_constant__ DlinParams p) {
-  __shared__ float s_part[4];
+// The gather as a kernel of its own: all-reduce (second half) + residual + RMSNorm, one token row
+// per block of 256 threads.  Small (no dynamic shared memory, few registers), so it becomes
+// resident while the linear before it is still running and finishes shortly after the last
+// partial row has landed.  Every load of a batch goes out before the first one is used.
+constexpr int kGatherThreads = 256;
+__global__ void __launch_bounds__(kGatherThreads, 2) k_gather_norm(const __grid_constant__ DlinParams p) {
+  using E = Elem<BL_DTYPE_BF16>;
+  __shared__ float s_part[kGatherThreads / 32];
   pdl_launch_dependents();
-  pdl_wait();
   const Comm& c = p.c;
+  const int vpr = p.k / 8;
+  const int t = threadIdx.x;
+  pdl_wait();
   uint32_t* sg = sig_of(c, c.rank);
   const uint32_t e = ld_volatile_u32(&sg[sig_epoch(P_LAMPORT)]);
   const uint32_t prev_vecs = ld_volatile_u32(&sg[sig_aux(P_LAMPORT)]);
-  const size_t cur_off = c.lamport_off + size_t(e % 3u) * (size_t(c.world) * c.lamport_slice);
+  const char* inbox = c.base[c.rank] + c.lamport_off + size_t(e % 3u) * (size_t(c.world) * c.lamport_slice);
   bool ok = true;
-  for (int r = blockIdx.x; r < p.tokens; r += gridDim.x) ok = dlin_gather_row(p, r, threadIdx.x, cur_off, s_part) && ok;
-  if (!ok && p.err && threadIdx.x == 0) *p.err = 1u;
-  dlin_clear_prev(c, e, prev_vecs, threadIdx.x);
+  for (int row = blockIdx.x; row < p.tokens; row += gridDim.x) {
+    float ss = 0.f;
+#pragma unroll
+    for (int v0 = 0; v0 < 4; v0 += 2) {
+      uint4 got[2][kMaxRanks], resv[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int i = t + (v0 + u) * kGatherThreads;
+        if (i < vpr) {
+          const size_t g = size_t(row) * vpr + i;
+#pragma unroll
+          for (int r = 0; r < kMaxRanks; ++r)
+            if (r < c.world) got[u][r] = ld_volatile_v4(inbox + size_t(r) * c.lamport_slice + g * 16);
+          if (p.res_in) resv[u] = __ldcg(p.res_in + g);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int i = t + (v0 + u) * kGatherThreads;
+        if (i < vpr) {
+          const size_t g = size_t(row) * vpr + i;
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int r = 0; r < kMaxRanks; ++r)
+            if (r < c.world) {
+              uint4 w = got[u][r];
+              if (!landed(w) && !poll_vec(c, inbox + size_t(r) * c.lamport_slice + g * 16, w, r)) ok = false;
+              acc_add<BL_DTYPE_BF16>(acc, w);
+            }
+          uint4 packed = E::pack(acc);  // the all-reduce result in its storage type
+          if (p.res_in) {
+            E::unpack(packed, acc);
+            acc_add<BL_DTYPE_BF16>(acc, resv[u]);
+            packed = E::pack(acc);
+          }
+          p.res_out[g] = packed;
+          float x[8];
+          E::unpack(packed, x);  // the norm sees the rounded residual
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
+        }
+      }
+    }
+    ss = warp_sum(ss);
+    if ((t & 31) == 0) s_part[t >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < kGatherThreads / 32; ++w) tot += s_part[w];
+    const float rstd = rsqrtf(tot / float(p.k) + p.eps);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const int i = t + v * kGatherThreads;
+      if (i < vpr) {
+        // this thread's own store of a moment ago (kept out of registers: the kernel stays small
+        // enough to share an SM with the linears around it)
+        float gm[8], o[8], x[8];
+        E::unpack(__ldcg(p.res_out + size_t(row) * vpr + i), x);
+        E::unpack(__ldg(p.gamma + i), gm);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = x[j] * rstd;
+        // x * rstd is rounded to bf16 before the weight multiply, as a framework RMSNorm module does
+        uint4 tt = E::pack(o);
+        E::unpack(tt, o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] *= gm[j];
+        p.xnorm[size_t(row) * vpr + i] = E::pack(o);
+      }
+    }
+    __syncthreads();  // s_part is reused by the next row
+  }
+  if (!ok && p.err && t == 0) *p.err = 1u;
+  // reset the inbox buffer of the call before this one (written again two calls from now)
+  {
+    const size_t clr_off = c.lamport_off + size_t((e + 2u) % 3u) * (size_t(c.world) * c.lamport_slice);
+    const uint4 unw = make_uint4(kUnwritten, kUnwritten, kUnwritten, kUnwritten);
+    for (size_t i = size_t(blockIdx.x) * kGatherThreads + t; i < prev_vecs; i += size_t(gridDim.x) * kGatherThreads)
+      for (int r = 0; r < c.world; ++r) st_v4(c.base[c.rank] + clr_off + size_t(r) * c.lamport_slice + i * 16, unw);
+  }
   finish_epoch(c, P_LAMPORT, e, uint32_t(p.tokens) * uint32_t(p.k / 8), true);
 }
 
@@ -497,14 +635,14 @@ __global__ void k_dlin_fill(uint32_t* p, size_t n_unwritten, size_t n_zero) {
 
 // How many clusters of `cl` CTAs of k_dlin<BN> the GPU holds at once (one CTA per SM; a cluster
 // must fit inside one GPC, so this is less than SMs / cl for some sizes).  Asked once per shape.
-template <int BN>
+template <int BN, int CPS>
 static int max_active_clusters(int cl) {
   static int cache[kDlinMaxCluster + 1] = {0};
   if (cl < 1 || cl > kDlinMaxCluster) return 1;
   if (cache[cl] > 0) return cache[cl];
-  using S = DlinSmem<BN>;
+  using S = DlinSmem<BN, CPS>;
   int n = 0;
-  cudaFuncSetAttribute(k_dlin<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+  cudaFuncSetAttribute(k_dlin<BN, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(unsigned(cl * sm_count()));
@@ -517,15 +655,27 @@ static int max_active_clusters(int cl) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaOccupancyMaxActiveClusters(&n, k_dlin<BN>, &cfg) != cudaSuccess || n < 1) {
+  if (cudaOccupancyMaxActiveClusters(&n, k_dlin<BN, CPS>, &cfg) != cudaSuccess || n < 1) {
     cudaGetLastError();
-    n = sm_count() / cl;
+    n = CPS * sm_count() / cl;
   }
   cache[cl] = n > 0 ? n : 1;
   return cache[cl];
 }
+// BL_DLIN_CPS=1 keeps one CTA per SM with the deep ring
+static int dlin_cps() {
+  static const int v = [] {
+    const char* e = getenv("BL_DLIN_CPS");
+    return (e && e[0] == '1') ? 1 : 2;
+  }();
+  return v;
+}
 static int max_active_clusters_bn(int bn, int cl) {
-  return bn <= 16 ? max_active_clusters<16>(cl) : bn <= 32 ? max_active_clusters<32>(cl) : max_active_clusters<64>(cl);
+  if (dlin_cps() == 2)
+    return bn <= 16 ? max_active_clusters<16, 2>(cl) : bn <= 32 ? max_active_clusters<32, 2>(cl)
+                                                                 : max_active_clusters<64, 2>(cl);
+  return bn <= 16 ? max_active_clusters<16, 1>(cl) : bn <= 32 ? max_active_clusters<32, 1>(cl)
+                                                               : max_active_clusters<64, 1>(cl);
 }
 
 // columns per CTA (a multiple of 4) and the row pitch of the exchange buffer (== 4 mod 8 floats)
@@ -540,7 +690,7 @@ static void cluster_columns(int ncol, int cl, int* cpc, int* cpcp) {
 static bool cluster_fits(int bn, int ncol, int cl) {
   int cpc, cpcp;
   cluster_columns(ncol, cl, &cpc, &cpcp);
-  const int xbuf = bn >= 64 ? DlinSmem<64>::kXbufBytes : DlinSmem<32>::kXbufBytes;
+  const int xbuf = bn >= 64 ? DlinSmem<64, 1>::kXbufBytes : DlinSmem<32, 1>::kXbufBytes;
   return cl * kTileA * cpcp * 4 <= xbuf;
 }
 
@@ -577,13 +727,13 @@ static int pick_cluster(int tiles, int kblocks, int want, int bn, int ncol) {
   return best;
 }
 
-template <int BN>
+template <int BN, int CPS>
 static int launch_dlin(const CUtensorMap& tw, const CUtensorMap& tx, const DlinParams& p, int tiles, int cl,
                        cudaStream_t st, char* err, size_t errlen) {
-  using S = DlinSmem<BN>;
+  using S = DlinSmem<BN, CPS>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(k_dlin<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
+    cudaError_t e = cudaFuncSetAttribute(k_dlin<BN, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
     if (e != cudaSuccess) {
       set_err(err, errlen, "barlink: cannot raise shared memory to %d B: %s", S::kBytes, cudaGetErrorString(e));
       return -1;
@@ -605,7 +755,7 @@ static int launch_dlin(const CUtensorMap& tw, const CUtensorMap& tx, const DlinP
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, k_dlin<BN>, tw, tx, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, k_dlin<BN, CPS>, tw, tx, p);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_err(err, errlen, "barlink: decode linear launch failed (grid %d, cluster %d): %s", tiles * cl, cl,
@@ -687,7 +837,7 @@ extern "C" int bl_gather_norm(blCtx* ctx, const blDlinArgs* a, void* stream, cha
   if (dlin_fill_pro(a, &p, err, errlen) != 0) return -1;
   if (dlin_comm(ctx, a, &p.c, err, errlen) != 0) return -1;
   const int grid = a->tokens < 2 * sm_count() ? a->tokens : 2 * sm_count();
-  cudaError_t e = launch_k(k_gather_norm, dim3(grid), dim3(128), 0, static_cast<cudaStream_t>(stream), p);
+  cudaError_t e = launch_k(k_gather_norm, dim3(grid), dim3(kGatherThreads), 0, static_cast<cudaStream_t>(stream), p);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_err(err, errlen, "barlink: gather_norm launch failed: %s", cudaGetErrorString(e));
@@ -727,6 +877,8 @@ extern "C" int bl_dlin(blCtx* ctx, const blDlinArgs* a, void* stream, char* err,
     }
     if (dlin_fill_pro(a, &p, err, errlen) != 0) return -1;
     p.sync = static_cast<uint32_t*>(a->sync);
+    // the segment sums live behind the three counters: 64 tokens x at most 8 segments
+    p.ss_part = reinterpret_cast<float*>(static_cast<uint32_t*>(a->sync) + 16);
   }
   if (a->epi == 2) {
     if (a->hidden < a->n || (a->hidden & 7) || (a->n & 7)) {
@@ -748,13 +900,24 @@ extern "C" int bl_dlin(blCtx* ctx, const blDlinArgs* a, void* stream, char* err,
   const int tiles = (a->n + kTileA - 1) / kTileA;
   const int cl = pick_cluster(tiles, p.kblocks, a->cluster, bn, a->tokens < bn ? a->tokens : bn);
   cluster_columns(a->tokens < bn ? a->tokens : bn, cl, &p.cpc, &p.cpcp);
+  {
+    const int resident = max_active_clusters_bn(bn, cl) * cl;
+    p.pro_ctas = tiles * cl < resident ? tiles * cl : resident;
+  }
   CUtensorMap tw, tx;
   if (make_tmap_kmajor(a->w, a->n, a->k, a->ldw, kTileA, 2, &tw, err, errlen) != 0) return -1;
   if (make_tmap_kmajor(a->x, a->tokens, a->k, a->ldx, bn, 2, &tx, err, errlen) != 0) return -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dlin_cps() == 2) {
+    switch (bn) {
+      case 16: return launch_dlin<16, 2>(tw, tx, p, tiles, cl, st, err, errlen);
+      case 32: return launch_dlin<32, 2>(tw, tx, p, tiles, cl, st, err, errlen);
+      default: return launch_dlin<64, 2>(tw, tx, p, tiles, cl, st, err, errlen);
+    }
+  }
   switch (bn) {
-    case 16: return launch_dlin<16>(tw, tx, p, tiles, cl, st, err, errlen);
-    case 32: return launch_dlin<32>(tw, tx, p, tiles, cl, st, err, errlen);
-    default: return launch_dlin<64>(tw, tx, p, tiles, cl, st, err, errlen);
+    case 16: return launch_dlin<16, 1>(tw, tx, p, tiles, cl, st, err, errlen);
+    case 32: return launch_dlin<32, 1>(tw, tx, p, tiles, cl, st, err, errlen);
+    default: return launch_dlin<64, 1>(tw, tx, p, tiles, cl, st, err, errlen);
   }
 }

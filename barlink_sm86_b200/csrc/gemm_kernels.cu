@@ -40,8 +40,27 @@ struct LocalSink {
   const __nv_bfloat16* residual;
   int ldo, ra, rb, swap, epi;
   const __nv_bfloat16* scale;  // per output feature (W8A16), or null
+  // Row push (token-major only, pworld > 0): row m belongs to rank (prow0 + m) / ptpr and is stored
+  // into that rank's staging inbox slot for this rank -- the scatter half of a two-shot all-reduce
+  // done by the GEMM epilogue over NVLink, tile by tile, while the other tiles are still in the
+  // tensor cores.
+  char* parena[kMaxRanks];
+  uint32_t* pflag[kMaxRanks];
+  const uint32_t* pseq;
+  size_t pstage_off, pstage_slice;
+  int pworld, prank, ptpr, prow0;
 
-  __device__ __forceinline__ void unit_done(int) const {}
+  // every epilogue thread of the CTA calls this after a tile (nthr of them: 128 or 256)
+  template <int NTHR>
+  __device__ __forceinline__ void tile_done(int et) const {
+    if (pworld > 0) {
+      __threadfence_system();
+      if (NTHR == 128) asm volatile("bar.sync 1, 128;" ::: "memory");
+      else asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (et < pworld) red_release_sys_add(pflag[et], 1u);
+    }
+  }
+  __device__ __forceinline__ void unit_done(int et) const { tile_done<128>(et); }
   __device__ __forceinline__ void operator()(int ta, int tb, int /*split*/, int row, int c0,
                                              const float (&vin)[32], int ncols) const {
     const int i = ta * kTileA + row;
@@ -82,6 +101,13 @@ struct LocalSink {
         return;
       }
       __nv_bfloat16* orow = out + size_t(m) * ldo;
+      if (pworld > 0) {
+        const int gm = prow0 + m;
+        const int owner = gm / ptpr;
+        const size_t buf = pstage_off + size_t(*pseq & 1u) * (2 * size_t(pworld) * pstage_slice);
+        orow = reinterpret_cast<__nv_bfloat16*>(parena[owner] + buf + size_t(prank) * pstage_slice) +
+               size_t(gm - owner * ptpr) * ldo;
+      }
       const __nv_bfloat16* rrow = residual ? residual + size_t(m) * ldo : nullptr;
       if (ncols == 32 && j0 + 32 <= rb && (ldo & 7) == 0) {
 #pragma unroll
@@ -402,6 +428,30 @@ static int env_int_or(const char* name, int dflt) {
   return (v && *v) ? atoi(v) : dflt;
 }
 
+template <class SinkT>
+static void fill_push(SinkT& sink, const blRowPush* p) {
+  sink.pworld = 0;
+  sink.pseq = nullptr;
+  sink.pstage_off = sink.pstage_slice = 0;
+  sink.prank = sink.ptpr = sink.prow0 = 0;
+  for (int r = 0; r < kMaxRanks; ++r) {
+    sink.parena[r] = nullptr;
+    sink.pflag[r] = nullptr;
+  }
+  if (!p) return;
+  sink.pworld = p->world;
+  sink.prank = p->rank;
+  sink.ptpr = p->rows_per_rank;
+  sink.prow0 = p->row0;
+  sink.pseq = static_cast<const uint32_t*>(p->seq_word);
+  sink.pstage_off = p->stage_off;
+  sink.pstage_slice = p->stage_slice;
+  for (int r = 0; r < p->world; ++r) {
+    sink.parena[r] = static_cast<char*>(p->arena[r]);
+    sink.pflag[r] = static_cast<uint32_t*>(p->flag[r]);
+  }
+}
+
 template <int BN, int CPS>
 static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, char* err,
                        size_t errlen) {
@@ -442,6 +492,7 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
     const size_t need = size_t(tiles) * g.splits * BN * kTileA * sizeof(float);
     if (!a.ws || a.ws_bytes < need || !a.counters || a.n_counters < tiles) g.splits = 1;
   }
+  if (a.push) g.splits = 1;  // a tile is pushed once, whole
   g.direct = 0;
   g.tiled = a_tiled ? 1 : b_tiled ? 2 : 0;
   g.tiled_base = static_cast<const uint8_t*>(a_tiled ? a.a : a.b);
@@ -527,6 +578,7 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
     sink.swap = a.swap;
     sink.epi = (a.bias ? 1 : 0) | (a.residual ? 2 : 0) | (a.silu_mul ? 4 : 0) | (a.gelu ? 8 : 0);
     sink.scale = nullptr;
+    fill_push(sink, a.push);
     static bool attr_set = false;
     if (!attr_set) {
       e = cudaFuncSetAttribute(k_gemm<BN, CPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -664,6 +716,7 @@ static int launch_w8(const blW8A16Args& a, cudaStream_t st, char* err, size_t er
     sink.swap = 1;
     sink.epi = (a.bias ? 1 : 0) | (a.silu_mul ? 4 : 0);
     sink.scale = static_cast<const __nv_bfloat16*>(a.scale);
+    fill_push(sink, nullptr);
     static bool attr = false;
     if (!attr) {
       e = cudaFuncSetAttribute(k_gemm_w8<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes);
@@ -704,6 +757,10 @@ constexpr int kPairStages = 6;
 constexpr int kPairStageBytes = 2 * kTileA * kTileK * 2;  // A 16 KiB + B 16 KiB per CTA
 constexpr int kPairSmem = kPairStages * kPairStageBytes + 1024 + 1024;
 constexpr int kPairBN = 256;
+// warp 0 producer, warp 1 MMA issuer, warps 2..9 epilogue: two warps per TMEM lane quarter, each
+// draining half of the 256 accumulator columns, so that the epilogue of a tile (bias, GELU,
+// residual, stores) stays shorter than the main loop of the next one
+constexpr int kPairThreads = 320;
 
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const void* tmap, uint32_t leader_bar,
                                                  int x, int y, uint64_t hint) {
@@ -731,7 +788,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     k_gemm_pair(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 GemmShape g, LocalSink<kPairBN> sink, uint64_t hint_a, uint64_t hint_b) {
   extern __shared__ uint8_t smem_raw[];
@@ -760,7 +817,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 256);
+      mbar_init(&tempty_bar[a], 2 * (kPairThreads - 64));
     }
     *s_abort = 0;
     mbar_fence_init();
@@ -855,6 +912,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     // ------------------------------ epilogue (both CTAs) ------------------
     const int q = warp & 3;
     const int row = q * 32 + lane;
+    const int chalf = (warp - 2) >> 2;  // which half of the columns this warp drains
     uint32_t tphase[2] = {0, 0};
     int it = 0;
     for (int u = pair; u < units; u += n_pairs, ++it) {
@@ -865,7 +923,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(acc * kPairBN);
 #pragma unroll 1
-      for (int c0 = 0; c0 < kPairBN; c0 += 32) {
+      for (int c0 = chalf * (kPairBN / 2); c0 < (chalf + 1) * (kPairBN / 2); c0 += 32) {
         float v[32];
         uint32_t r[32];
         tmem_ld_32x32(taddr + c0, r);
@@ -877,6 +935,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       }
       tc_fence_before_sync();
       mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+      sink.template tile_done<256>(int(threadIdx.x) - 64);
     }
   }
 
@@ -925,6 +984,7 @@ static int launch_gemm_pair(const blGemmArgs& a, cudaStream_t st, char* err, siz
   sink.swap = 0;
   sink.epi = (a.bias ? 1 : 0) | (a.residual ? 2 : 0) | (a.gelu ? 8 : 0);
   sink.scale = nullptr;
+  fill_push(sink, a.push);
   static bool attr = false;
   if (!attr) {
     cudaError_t e = cudaFuncSetAttribute(k_gemm_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem);
@@ -939,7 +999,7 @@ static int launch_gemm_pair(const blGemmArgs& a, cudaStream_t st, char* err, siz
   if (pairs > units) pairs = units;
   if (pairs < 1) pairs = 1;
   // the cluster shape is compiled into the kernel (__cluster_dims__); the grid is a whole number of pairs
-  cudaError_t e = launch_k(k_gemm_pair, dim3(2 * pairs), dim3(kGemmThreads), size_t(kPairSmem), st, ta, tb, g, sink,
+  cudaError_t e = launch_k(k_gemm_pair, dim3(2 * pairs), dim3(kPairThreads), size_t(kPairSmem), st, ta, tb, g, sink,
                            kHintEvictLast, kHintEvictFirst);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -1061,8 +1121,22 @@ extern "C" int bl_gemm_splits(int n, int k, int tokens) {
   return pick_splits(tiles, kblocks, sm_count(), 0);
 }
 
+// arrival counts (per owner) of a pushed linear: one per 128-row x 256-column tile of a CTA, in the
+// paired kernel as in the single-CTA one (both are only taken with 256-column tiles)
+extern "C" int bl_gemm_push_units(int rows, int n) {
+  const int col_tiles = (n + 255) / 256;
+  if (gemm_pair_enabled() && rows >= 512) return ((rows + 255) / 256) * 2 * col_tiles;  // two CTAs per 256-row unit
+  return ((rows + kTileA - 1) / kTileA) * col_tiles;
+}
+
 extern "C" int bl_gemm_bf16(const blGemmArgs* a, void* stream, char* err, size_t errlen) {
-  if (!a || !a->a || !a->b || (!a->out && !a->partial_out && !a->peer) || a->ra < 1 || a->rb < 1 || a->k < 8 || (a->k & 7)) {
+  if (a && a->push) {
+    if (a->swap || a->partial_out || a->peer || a->silu_mul || a->ldo != a->rb || (a->rb & 7) || a->rb < 256) {
+      set_err(err, errlen, "barlink: a pushed linear is token-major, dense (ldo == n), n >= 256 and a multiple of 8");
+      return -1;
+    }
+  }
+  if (!a || !a->a || !a->b || (!a->out && !a->partial_out && !a->peer && !a->push) || a->ra < 1 || a->rb < 1 || a->k < 8 || (a->k & 7)) {
     set_err(err, errlen, "barlink: gemm needs non-null operands and K a multiple of 8");
     return -1;
   }

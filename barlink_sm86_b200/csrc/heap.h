@@ -45,6 +45,7 @@ enum Proto : int {
   P_AG_GEMM = 12,
   P_COPY = 13,
   P_USER0 = 14,
+  P_ROWPUSH = 15,  // row-parallel GEMM that scatters its output tiles itself + the kernel that finishes the all-reduce
 };
 
 // word indices inside the pad

@@ -241,19 +241,19 @@ class MMDiTModel:
             a3 = att.view(batch, L, hl * hd)
             at, ai = a3[:, :nt].reshape(rt, hl * hd), a3[:, nt:].reshape(ri, hl * hd)
         o = torch.empty_like(h)
-        ops.linear(at, blk["txt"]["proj_w"], blk["txt"]["proj_b"], out=o[:rt])
-        ops.linear(ai, blk["img"]["proj_w"], blk["img"]["proj_b"], out=o[rt:])
-        self.comm.all_reduce(o)
+        self.comm.row_parallel(o, [(at, blk["txt"]["proj_w"], blk["txt"]["proj_b"], None, False, 0),
+                                   (ai, blk["img"]["proj_w"], blk["img"]["proj_b"], None, False, rt)])
         ops.gate_residual(ht, o[:rt], mods["txt"][2], nt)
         ops.gate_residual(hi, o[rt:], mods["img"][2], ni)
 
         o = torch.empty_like(h)
-        for name, x, n, lo, hi_ in (("txt", ht, nt, 0, rt), ("img", hi, ni, rt, rt + ri)):
+        parts = []
+        for name, x, n, lo in (("txt", ht, nt, 0), ("img", hi, ni, rt)):
             s, (sh, sc) = blk[name], mods[name][3:5]
             xm = ops.layernorm_modulate(x, sh, sc, n, cfg.eps)
             f = ops.linear(xm, s["fc1_w"], s["fc1_b"], gelu=True)
-            ops.linear(f, s["fc2_w"], s["fc2_b"], out=o[lo:hi_])
-        self.comm.all_reduce(o)
+            parts.append((f, s["fc2_w"], s["fc2_b"], None, False, lo))
+        self.comm.row_parallel(o, parts)
         ops.gate_residual(ht, o[:rt], mods["txt"][5], nt)
         ops.gate_residual(hi, o[rt:], mods["img"][5], ni)
 
@@ -267,9 +267,9 @@ class MMDiTModel:
         ops.qknorm_rope(qkv, s["gq"], s["gk"], pos, hl, cfg.eps, cfg.rope_theta, 2)
         f = ops.linear(xm, s["mlp_w"], s["mlp_b"], gelu=True)
         att = self._attention(qkv, batch, L)
-        o = ops.linear(att, s["out_attn_w"], s["out_b"])
-        o = ops.linear(f, s["out_mlp_w"], residual=o)
-        self.comm.all_reduce(o)
+        o_attn = ops.linear(att, s["out_attn_w"], s["out_b"])
+        o = torch.empty_like(o_attn)
+        self.comm.row_parallel(o, [(f, s["out_mlp_w"], None, o_attn, False, 0)])
         ops.gate_residual(x, o, gt, L)
 
     # ---- forward -----------------------------------------------------------

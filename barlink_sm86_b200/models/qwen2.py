@@ -278,6 +278,10 @@ class Qwen2Model:
         h = ops.embedding(ids, w.embed)
         res = torch.zeros_like(h)
         split_k = split_k and h.is_cuda
+        # prefill sizes on the link: the row-parallel linears scatter their output tiles into the
+        # owners' staging inboxes from the GEMM epilogue and one kernel finishes the all-reduce
+        pushed = (not split_k and h.is_cuda and w.quant == "none" and c.world > 1 and c.use_link
+                  and h.shape[0] > 128 and h.shape[0] % c.world == 0 and not w.tiled)
         pending = False  # h holds a partial sum that still needs the all-reduce
         for li, L in enumerate(w.layers):
             if pending:
@@ -298,19 +302,30 @@ class Qwen2Model:
                         qkv = qkv + L["bqkv"]
                     a = attn_factory(li)(qkv, None)
                 h = ops.linear_split(a, L["wo"])
+            elif pushed:
+                qkv = ops.linear(normed, L["wqkv"], L["bqkv"])
+                a = attn_factory(li)(qkv, None)
+                h = c.row_parallel(torch.empty_like(res), [(a, L["wo"], None, None, False, 0)])
             else:
                 qkv = ops.linear(normed, L["wqkv"], L["bqkv"])
                 a = attn_factory(li)(qkv, None)
                 h = ops.linear(a, L["wo"])
-            normed, res = c.allreduce_rmsnorm(h, res, L["ln2"], cfg.eps)
+            if pushed:
+                normed, res = ops.rmsnorm(h, L["ln2"], cfg.eps, res)
+            else:
+                normed, res = c.allreduce_rmsnorm(h, res, L["ln2"], cfg.eps)
             if split_k and w.quant == "none" and ops.k_splits(normed, L["wgu"]) > 1:
                 # a gate/up shard with few row tiles fills the SMs only with a k-split;
                 # SiLU*mul then runs over the slabs (one small kernel) instead of in the epilogue
                 act = ops.silu_mul(ops.linear_split(normed, L["wgu"]), interleaved=True)
             else:
                 act = qlinear(normed, L["wgu"], silu_mul=True)
-            h = qlinear(act, L["wdown"], split=split_k)
-            pending = True
+            if pushed:
+                h = c.row_parallel(torch.empty_like(res), [(act, L["wdown"], None, None, False, 0)])
+                pending = False
+            else:
+                h = qlinear(act, L["wdown"], split=split_k)
+                pending = True
         if pending:
             normed, res = c.allreduce_rmsnorm(h, res, w.ln_f, cfg.eps)
         else:
@@ -410,11 +425,16 @@ class Qwen2Model:
         nq, nkv, hd = self.nq, self.nkv, self.hd
         H = cfg.hidden
         res, xn, link = self._dlin_buffers(ids.shape[0])
+        # BL_DLIN_PRO=1: the gather + residual + norm runs in the prologue of the linear that needs it
+        # (five launches per layer); default: in a small kernel of its own that becomes resident while
+        # the row-parallel linear before it is still running (seven launches per layer)
+        import os
+        in_prologue = os.environ.get("BL_DLIN_PRO", "0") == "1"
         ops.embedding(ids, w.embed, out=res)
         ops.rmsnorm(res, w.layers[0]["ln1"], cfg.eps, out=xn)
         for li, L in enumerate(w.layers):
-            ops._count(5)
-            if li == 0:
+            ops._count(5 if in_prologue else 7)
+            if li == 0 or not in_prologue:
                 qkv = C.dlin(xn, L["wqkv"], epi="store", bias=L["bqkv"])
             else:
                 qkv = C.dlin(xn, L["wqkv"], pro="gather_norm", epi="store", bias=L["bqkv"], residual=res,
@@ -422,9 +442,15 @@ class Qwen2Model:
             a = C.rope_attn_decode(qkv, None, positions, slots, cache.k[li], cache.v[li], cache.block_tables,
                                    ctx_lens, nq, nkv, hd, cfg.theta, self.scale, splits)
             C.dlin(a, L["wo"], epi="push", hidden=H, link=link)
-            act = C.dlin(xn, L["wgu"], pro="gather_norm", epi="silu_mul", residual=res, gamma=L["ln2"],
-                         eps=cfg.eps, link=link)
+            if in_prologue:
+                act = C.dlin(xn, L["wgu"], pro="gather_norm", epi="silu_mul", residual=res, gamma=L["ln2"],
+                             eps=cfg.eps, link=link)
+            else:
+                C.gather_norm(xn, res, L["ln2"], cfg.eps, link=link)
+                act = C.dlin(xn, L["wgu"], epi="silu_mul")
             C.dlin(act, L["wdown"], epi="push", hidden=H, link=link)
+            if not in_prologue and li + 1 < len(w.layers):
+                C.gather_norm(xn, res, w.layers[li + 1]["ln1"], cfg.eps, link=link)
             c.ar_calls += 2 if c.world > 1 else 0
             c.ar_bytes += (2 * xn.numel() * 2) if c.world > 1 else 0
         ops._count()

@@ -104,6 +104,40 @@ class TPComm:
         self._timed_call(lambda: dist.all_reduce(x, group=self.group))
         return x
 
+    def row_parallel(self, out, parts):
+        """out[row0 : row0 + rows] = sum over ranks of (x @ w.T (+ bias) (GELU) (+ residual)) for every
+        part (x, w, bias, residual, gelu, row0); the parts tile the rows of out [T, n].
+
+        On the link, for token-major sizes, the GEMM epilogue is the scatter half of a two-shot
+        all-reduce: every finished 128 x 256 tile is stored as bf16 straight into the staging inbox
+        of the rank that owns those rows (peer stores over NVLink while the other tiles are still
+        in the tensor cores) and one more kernel reduces this rank's rows and hands the sums to
+        every rank.  BL_PUSH_AR=0, other sizes and other backends: GEMM into out, then all_reduce."""
+        import os
+        T, n = out.shape
+        fused = (self.world > 1 and self.use_link and out.is_cuda and not self.no_comm
+                 and out.dtype == torch.bfloat16 and out.is_contiguous()
+                 and os.environ.get("BL_PUSH_AR", "1") != "0"
+                 and T % self.world == 0 and n >= 256 and n % 8 == 0
+                 and (T // self.world) * n * 2 <= self.max_chunk // self.world
+                 and all(p[0].shape[0] > 128 and p[0].dtype == torch.bfloat16 for p in parts))
+        if fused:
+            C = load_extension()
+            units = 0
+            for x, w, bias, residual, gelu, row0 in parts:
+                _ops._count()
+                units += C.linear_push(x, w, bias, residual, gelu, T, row0)
+            _ops._count()
+            self.ar_calls += 1
+            self.ar_bytes += out.numel() * out.element_size()
+            self._timed_call(lambda: C.allreduce_pushed(out, units))
+            return out
+        for x, w, bias, residual, gelu, row0 in parts:
+            _ops.linear(x, w, bias, residual=residual, gelu=gelu, out=out[row0:row0 + x.shape[0]])
+        if self.world > 1:
+            self.all_reduce(out)
+        return out
+
     def all_gather_cols(self, x):
         """[rows, n_local] on every rank -> [rows, world * n_local] (rank-major columns)."""
         if self.world == 1:

@@ -5,7 +5,12 @@ target of `ncu` captures (see profiles/).  Weights are larger than L2 or
 rotate, launches are few, memory stays within a few GB.
 
     python bench/gemm/one_kernel.py gate_up|down_slabs|qkv_slabs|lm_head|w8a16|attn_decode|rmsnorm|attn_prefill|
-                                    attn_joint|attn_joint_small|linear_big [reps]
+                                    attn_joint|attn_joint_small|linear_big|dlin_gate_up|dlin_down|rope_attn [reps]
+
+dlin_gate_up / dlin_down: the decode linears of a TP=8 shard with the collective folded in (gather +
+residual + norm prologue and SiLU*mul epilogue; inbox-push epilogue), on the one-rank stand-in for the
+link, weights rotating through copies larger than L2.  rope_attn: RoPE + KV write + paged attention +
+split merge in one kernel, the TP=8 shard's heads (4 query slots, 1 KV head), batch 64 x 1024 tokens.
 """
 import math
 import sys
@@ -79,6 +84,37 @@ elif which == "linear_big":
     # MMDiT MLP-in at 4608 tokens: [4608, 3072] x [12288, 3072]^T with bias + GELU
     x, w, b = bf(4608, 3072), bf(12288, 3072, std=0.02), bf(12288)
     fn = lambda i: C.linear(x, w, b, None, False, None, gelu=True)  # noqa: E731
+elif which in ("dlin_gate_up", "dlin_down"):
+    T, inter = B, 2368                      # TP=8 shard of the 7B shape
+    link = C.dlin_local_link(T, H, 0)
+    res, xn, gamma = bf(T, H), bf(T, H), bf(H)
+    wo, a_in = bf(H, 512, std=0.02), bf(T, 512)
+    if which == "dlin_gate_up":
+        ws = [bf(2 * inter, H, std=0.02) for _ in range(6)]       # 6 x 34 MB
+
+        def fn(i):
+            C.dlin(a_in, wo, epi="push", hidden=H, link=link)     # fills the inbox the prologue gathers
+            C.dlin(xn, ws[i % 6], pro="gather_norm", epi="silu_mul", residual=res, gamma=gamma, eps=1e-6, link=link)
+    else:
+        ws = [bf(H, inter, std=0.02) for _ in range(10)]          # 10 x 17 MB
+        act = bf(T, inter)
+
+        def fn(i):
+            C.dlin(act, ws[i % 10], epi="push", hidden=H, link=link)
+            C.gather_norm(xn, res, gamma, 1e-6, link=link)        # consumes the inbox
+elif which == "rope_attn":
+    nq, nkv, hd, bs, ctx = 4, 1, 128, 16, 1024
+    mb = ctx // bs + 2
+    nb = B * mb
+    kcs = [bf(nb, nkv, bs, hd) for _ in range(4)]
+    vcs = [bf(nb, nkv, bs, hd) for _ in range(4)]
+    bt = torch.arange(nb, device=dev, dtype=torch.int32).view(B, -1).contiguous()
+    cl = torch.full((B,), ctx, device=dev, dtype=torch.int32)
+    pos = cl - 1
+    slots = (bt[torch.arange(B, device=dev), (pos // bs).long()] * bs + pos % bs).to(torch.int32)
+    qkv = bf(B, (nq + 2 * nkv) * hd)
+    fn = lambda i: C.rope_attn_decode(qkv, None, pos, slots, kcs[i % 4], vcs[i % 4], bt, cl, nq, nkv, hd, 1e6,  # noqa: E731
+                                      1 / math.sqrt(hd), 0)
 else:
     raise SystemExit("unknown kernel " + which)
 

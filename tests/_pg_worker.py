@@ -295,6 +295,33 @@ for rows, hidden, S in ((8, 3584, 4), (64, 3584, 5)):
     assert ((normed.cpu().float() - want_n.float()).norm() / want_n.float().norm()) < 8e-3
 log("allreduce_rmsnorm ok")
 
+# ---- row-parallel linear whose epilogue is the scatter half of the all-reduce ------------------
+from barlink_sm86_b200.parallel import TPComm  # noqa: E402
+comm = TPComm(dist.group.WORLD)
+for T, n, k, split in ((1024, 512, 256, 384), (world * 320, 768, 192, 0), (2304, 3072, 512, 256)):
+    g = torch.Generator(device="cpu").manual_seed(4000 + rank)
+    x = (torch.randn(T, k, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+    w1 = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    w2 = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    bias = torch.randn(n, generator=g).to(torch.bfloat16).to(dev)
+    res = torch.randn(T, n, generator=g).to(torch.bfloat16).to(dev)
+    if split and T - split > 128 and split > 128:
+        parts = [(x[:split], w1, bias, None, False, 0), (x[split:], w2, None, res[split:], True, split)]
+    else:
+        parts = [(x, w1, bias, res, False, 0)]
+    os.environ["BL_PUSH_AR"] = "0"
+    want = comm.row_parallel(torch.empty(T, n, dtype=torch.bfloat16, device=dev), parts).clone()
+    os.environ["BL_PUSH_AR"] = "1"
+    calls = bl.stats()["ops"]
+    for it in range(3):   # consecutive calls alternate between the two staging buffers
+        got = comm.row_parallel(torch.empty(T, n, dtype=torch.bfloat16, device=dev), parts)
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), ("pushed all-reduce differs from GEMM + all_reduce", T, n, k, it,
+                                        (got.float() - want.float()).abs().max().item())
+    assert bl.stats()["ops"] == calls + 3, "the pushed path did not run"
+assert bl.status()["code"] == 0 and C.gemm_error_flag(rank) == 0
+log("row-parallel linear with pushed all-reduce ok (bit-equal to GEMM + all_reduce)")
+
 # ---- CUDA graph capture and replay ----------------------------------------------------------
 x = torch.zeros(5120, dtype=torch.bfloat16, device=dev)
 y = torch.empty_like(x)

@@ -28,7 +28,7 @@ cfg = Qwen2Config(hidden=1024, layers=3, n_heads=8, n_kv_heads=2, head_dim=128, 
                   vocab=4096, name="tp-test")
 tp = Qwen2Model(cfg, TPComm(dist.group.WORLD), dev, torch.bfloat16, seed=9)
 one = Qwen2Model(cfg, TPComm.single(), dev, torch.bfloat16, seed=9)
-B, S, steps = max(4, world), 32, 8  # the fused linears shard tokens over the ranks: B % world == 0
+B, S, steps = max(4, world), 40, 8  # B % world == 0 (token-sharded paths); B * S > 128: prefill takes the pushed row-parallel linears
 ids = torch.randint(0, cfg.vocab, (B, S), generator=torch.Generator().manual_seed(5), dtype=torch.int32).to(dev)
 lt = tp.logits(tp.prefill(ids)).float()
 l1 = one.logits(one.prefill(ids)).float()

@@ -52,7 +52,8 @@ def test_silu_mul_epilogue(ext, tokens, n, k, cluster):
     assert rel_l2(y, want) < 1e-2
 
 
-@pytest.mark.parametrize("tokens,hidden,k,n2", [(64, 3584, 512, 768), (8, 1024, 2368, 640), (33, 512, 1376, 256)])
+@pytest.mark.parametrize("tokens,hidden,k,n2", [(64, 3584, 512, 768), (8, 1024, 2368, 640), (33, 512, 1376, 256),
+                                                (64, 5120, 512, 4736), (5, 8192, 256, 384)])
 def test_push_then_gather_norm_chain(ext, tokens, hidden, k, n2):
     """row-parallel linear (push) -> [standalone gather + residual + norm] and
     -> [next linear with the gather in its prologue], several rounds so that the three inbox
@@ -74,14 +75,19 @@ def test_push_then_gather_norm_chain(ext, tokens, hidden, k, n2):
         if it % 2 == 0:
             ext.gather_norm(xn, res, gamma, eps, link=link)
             torch.cuda.synchronize()
+            assert rel_l2(xn, want_xn) < 6e-3, it
         else:
-            y = ext.dlin(xn, w2, pro="gather_norm", epi="store", residual=res, gamma=gamma, eps=eps, link=link)
+            # in-kernel form: the operand buffer receives residual * gamma, the 1 / rms of each
+            # token is applied to the product by the epilogue
+            bias = _bf(n2, seed=40 + it, std=0.3)
+            y = ext.dlin(xn, w2, pro="gather_norm", epi="store", bias=bias, residual=res, gamma=gamma, eps=eps,
+                         link=link, cluster=(it % 4) + 1)
             torch.cuda.synchronize()
-            want_y = want_xn.float() @ w2.float().t()
+            want_y = want_xn.float() @ w2.float().t() + bias.float()
             assert rel_l2(y, want_y) < 1.5e-2, it
+            assert rel_l2(xn, (res_ref.float() * gamma.float()).to(torch.bfloat16)) < 6e-3, it
         assert ext.dlin_error_flag(0) == 0, it
         assert rel_l2(res, res_ref) < 4e-3, it
-        assert rel_l2(xn, want_xn) < 6e-3, it
 
 
 def test_chain_inside_a_cuda_graph(ext):
