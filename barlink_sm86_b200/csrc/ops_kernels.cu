@@ -737,6 +737,23 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   };
   prologue();
   pdl_wait();
+  // Everything this block needs from the kernels ahead is requested in one go: the raw query heads
+  // and the new key / value (one rotation pair (i, i + 64) per thread and step, consecutive threads
+  // on consecutive columns: rows 0..G-1 are the query heads, G the new key, G + 1 the new value),
+  // the position and the context length.
+  constexpr int kPrepMax = (16 + 2) * (kHd / 2) / (kAttnWarps * 32);
+  float px1[kPrepMax], px2[kPrepMax];
+#pragma unroll
+  for (int it = 0; it < kPrepMax; ++it) {
+    const int p = threadIdx.x + it * (kAttnWarps * 32);
+    if (p < (G + 2) * (kHd / 2)) {
+      const int hh = p / (kHd / 2), i = p % (kHd / 2);
+      const int col = hh < G ? (h * G + hh) * kHd : hh == G ? (nq + h) * kHd : (nq + nkv + h) * kHd;
+      px1[it] = qkv_elem(src, b, col + i);
+      px2[it] = qkv_elem(src, b, col + i + kHd / 2);
+    }
+  }
+  const float pos = float(positions[b]);
   {
     const int pages_before = n_pages;
     ctx = *reinterpret_cast<const volatile int*>(ctx_lens + b);
@@ -755,7 +772,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   __shared__ float2 s_cs[kHd / 2];
   __shared__ __align__(16) __nv_bfloat16 s_q[16][kHd];   // rotated query heads of this group (rows < G)
   __shared__ __align__(16) __nv_bfloat16 s_new[2][kHd];  // rotated key, value of the new token
-  const float pos = float(positions[b]);
   if (threadIdx.x < kHd / 2) {
     const float inv = exp2f(-log2_theta * (2.f * float(threadIdx.x) / float(kHd)));
     float sn, cs;
@@ -766,13 +782,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
   const int last_page = n_pages - 1;
   const bool owns_last = last_page >= p0 && last_page < p1;
   {
-    // one rotation pair (i, i + 64) per thread and step, consecutive threads on consecutive
-    // columns: rows 0..G-1 are the query heads, G the new key, G + 1 the new value
     const int rows = owns_last ? G + 2 : G;
-    for (int p = threadIdx.x; p < rows * (kHd / 2); p += blockDim.x) {
+#pragma unroll
+    for (int it = 0; it < kPrepMax; ++it) {
+      const int p = threadIdx.x + it * (kAttnWarps * 32);
+      if (p >= rows * (kHd / 2)) continue;
       const int hh = p / (kHd / 2), i = p % (kHd / 2);
-      const int col = hh < G ? (h * G + hh) * kHd : hh == G ? (nq + h) * kHd : (nq + nkv + h) * kHd;
-      const float x1 = qkv_elem(src, b, col + i), x2 = qkv_elem(src, b, col + i + kHd / 2);
+      const float x1 = px1[it], x2 = px2[it];
       __nv_bfloat16 o1, o2;
       if (hh <= G) {
         const float2 cs = s_cs[i];

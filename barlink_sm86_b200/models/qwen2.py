@@ -27,6 +27,11 @@ from ..parallel import TPComm, head_plan, interleave_gate_up, shard_cols, shard_
 from ..parallel.plan import gather_head_cols, gather_heads
 
 
+# BL_DLIN when the environment does not set it: "auto" = the folded-collective decode path whenever
+# there is more than one rank, "0" = the k-split GEMM + all-reduce kernel path
+DLIN_DEFAULT = "0"
+
+
 @dataclass
 class Qwen2Config:
     hidden: int = 3584
@@ -392,7 +397,7 @@ class Qwen2Model:
         BL_DLIN=0 turns it off."""
         import os
         c = self.comm
-        mode = os.environ.get("BL_DLIN", "auto")
+        mode = os.environ.get("BL_DLIN", DLIN_DEFAULT)
         if mode == "0" or self.device.type != "cuda" or self.w.quant != "none" or self.dtype != torch.bfloat16:
             return False
         if tokens > 64 or self.cfg.hidden % 8 or self.cfg.hidden > 8192 or self.w.tiled:

@@ -17,6 +17,11 @@ from ..ops import reference as ref
 from .. import ops as _ops
 
 
+# BL_PUSH_AR when the environment does not set it ("1": row-parallel linears of 129 rows or more
+# scatter their tiles themselves, see TPComm.row_parallel)
+PUSH_AR_DEFAULT = "0"
+
+
 class TPComm:
     def __init__(self, group=None, use_link=None):
         if group is None and dist.is_available() and dist.is_initialized():
@@ -117,7 +122,7 @@ class TPComm:
         T, n = out.shape
         fused = (self.world > 1 and self.use_link and out.is_cuda and not self.no_comm
                  and out.dtype == torch.bfloat16 and out.is_contiguous()
-                 and os.environ.get("BL_PUSH_AR", "1") != "0"
+                 and os.environ.get("BL_PUSH_AR", PUSH_AR_DEFAULT) != "0"
                  and T % self.world == 0 and n >= 256 and n % 8 == 0
                  and (T // self.world) * n * 2 <= self.max_chunk // self.world
                  and all(p[0].shape[0] > 128 and p[0].dtype == torch.bfloat16 for p in parts))

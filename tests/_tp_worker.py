@@ -20,6 +20,8 @@ from barlink_sm86_b200.parallel import TPComm  # noqa: E402
 rank, world, port = int(sys.argv[1]), int(sys.argv[2]), int(sys.argv[3])
 os.environ["LOCAL_RANK"] = str(rank)
 os.environ.setdefault("BL_POOL_MB", "512")
+os.environ["BL_DLIN"] = "auto"     # the folded-collective decode path (whatever the library's default is)
+os.environ["BL_PUSH_AR"] = "1"     # prefill: row-parallel linears that scatter their tiles themselves
 torch.cuda.set_device(rank)
 dev = torch.device("cuda", rank)
 blpg.init_process_group(init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
