@@ -117,17 +117,23 @@ __global__ void __launch_bounds__(kThreads) k_lamport(CollArgs a) {
       typename E::acc_t acc[E::N];
 #pragma unroll
       for (int j = 0; j < E::N; ++j) acc[j] = 0;
-      for (int r = 0; r < world; ++r) {
-        uint4 v;
-        if (r == rank) {
-          v = scrub(in[i]);
-        } else if (!poll_vec(c, c.base[rank] + cur_off + size_t(r) * c.lamport_slice + i * 16, v,
-                             r)) {
-          ok = false;
-          break;
+      // all ranks' vectors are requested before the first one is looked at: one round trip to L2
+      // instead of one per rank; whatever has not landed yet is polled afterwards
+      uint4 got[kMaxRanks];
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < world)
+          got[r] = r == rank ? scrub(in[i])
+                             : ld_volatile_v4(c.base[rank] + cur_off + size_t(r) * c.lamport_slice + i * 16);
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < world && ok) {
+          uint4 v = got[r];
+          if (r != rank && !landed(v) &&
+              !poll_vec(c, c.base[rank] + cur_off + size_t(r) * c.lamport_slice + i * 16, v, r))
+            ok = false;
+          acc_add<DT>(acc, v);
         }
-        acc_add<DT>(acc, v);
-      }
       if (ok) out[i] = E::pack(acc);
     }
   } else {
@@ -183,25 +189,34 @@ __global__ void __launch_bounds__(kThreads) k_lamport(CollArgs a) {
           float acc[E::N];
 #pragma unroll
           for (int j = 0; j < E::N; ++j) acc[j] = 0.f;
-          for (int r = 0; r < world; ++r) {
-            uint4 v;
-            if (r == rank) {
+          // all ranks' vectors (and the residual) are requested before the first one is looked
+          // at; whatever has not landed yet is polled afterwards
+          uint4 got[kMaxRanks];
+#pragma unroll
+          for (int r = 0; r < kMaxRanks; ++r)
+            if (r < world) {
               // with slabs, my own contribution was parked in my inbox slot by this same thread
-              v = slabs ? ld_volatile_v4(c.base[rank] + cur_off + size_t(rank) * c.lamport_slice + g * 16)
-                        : scrub(in[g]);
-            } else if (!poll_vec(c, c.base[rank] + cur_off + size_t(r) * c.lamport_slice + g * 16,
-                                 v, r)) {
-              ok = false;
-              break;
+              got[r] = (r == rank && !slabs)
+                           ? scrub(in[g])
+                           : ld_volatile_v4(c.base[rank] + cur_off + size_t(r) * c.lamport_slice + g * 16);
             }
-            acc_add<DT>(acc, v);
-          }
+          uint4 resv = make_uint4(0, 0, 0, 0);
+          if (res_in) resv = res_in[g];
+#pragma unroll
+          for (int r = 0; r < kMaxRanks; ++r)
+            if (r < world && ok) {
+              uint4 v = got[r];
+              if (r != rank && !landed(v) &&
+                  !poll_vec(c, c.base[rank] + cur_off + size_t(r) * c.lamport_slice + g * 16, v, r))
+                ok = false;
+              acc_add<DT>(acc, v);
+            }
           if (res_in) {
             // the all-reduce result is rounded to the storage type first,
             // exactly as an unfused all_reduce followed by an add would
             uint4 rv = E::pack(acc);
             E::unpack(rv, acc);
-            acc_add<DT>(acc, res_in[g]);
+            acc_add<DT>(acc, resv);
           }
           uint4 packed = E::pack(acc);
           if (ok) res_out[g] = packed;

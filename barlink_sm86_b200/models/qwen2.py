@@ -544,9 +544,19 @@ class Qwen2Model:
         full = self.comm.all_gather_cols(self.logits_local(hidden))
         return full[:, : self.cfg.vocab]
 
-    def next_tokens(self, hidden, out=None):
-        """Greedy next token per row (local arg max + a few bytes per row exchanged)."""
-        return self.comm.argmax_vocab_parallel(self.logits_local(hidden), self.w.vocab_local, out)
+    def next_tokens(self, hidden, out=None, dlin=False):
+        """Greedy next token per row (local arg max + a few bytes per row exchanged).
+        dlin: the head may run on the decode-linear kernel; it does when its row tiles fit the GPU
+        at once (a vocabulary shard of 149 tiles takes the persistent GEMM two laps of its 148 CTAs)."""
+        head = self.w.lm_head
+        if (dlin and hidden.is_cuda and isinstance(head, torch.Tensor) and hidden.shape[0] <= 64
+                and -(-head.shape[0] // 128) <= 296):
+            from .. import load_extension
+            ops._count()
+            logits = load_extension().dlin(hidden, head, epi="store")
+        else:
+            logits = self.logits_local(hidden)
+        return self.comm.argmax_vocab_parallel(logits, self.w.vocab_local, out)
 
 
 class DecodeEngine:
@@ -611,7 +621,7 @@ class DecodeEngine:
         if self.m.dlin_ok(self.batch):
             hidden = self.m.decode_hidden_dlin(self.ids, self.positions, self.slots, self.ctx_lens,
                                                self.cache, self.attn_splits)
-            nxt = self.m.next_tokens(hidden, self.out_ids)
+            nxt = self.m.next_tokens(hidden, self.out_ids, dlin=True)
         elif self.m.fused_ok(self.batch):
             hidden, gate = self.m.decode_hidden_fused(self.ids, self.positions, self.slots,
                                                       self.ctx_lens, self.cache, self.attn_splits)

@@ -65,3 +65,21 @@ def test_k_split_choice(tiles, kblocks):
         assert s == 1                                       # enough tiles: no split
     if tiles * kblocks >= 148 and tiles < 74:
         assert s > 1                                        # few tiles with a long k: split
+
+
+@pytest.mark.parametrize("n,k,tokens", [(768, 3584, 64), (3584, 512, 64), (4736, 3584, 64), (3584, 2368, 64),
+                                        (37888, 3584, 64), (256, 128, 1), (19008, 3584, 8), (128, 64, 16)])
+def test_decode_linear_cluster_choice(n, k, tokens):
+    """Cluster size of the decode linears (host arithmetic, no GPU needed): between 1 and 8, never
+    more CTAs than k-blocks, at least two k-blocks per CTA when the product is split, a forced size
+    is honoured up to those limits, and a shape with more tiles than SMs is not split at all."""
+    kblocks = -(-k // 64)
+    auto = C.dlin_cluster(n, k, tokens, 0)
+    assert 1 <= auto <= 8 and auto <= max(1, kblocks)
+    if auto > 1:
+        assert kblocks // auto >= 2
+    if -(-n // 128) >= 148:
+        assert auto == 1
+    for want in (1, 2, 4, 8):
+        got = C.dlin_cluster(n, k, tokens, want)
+        assert 1 <= got <= min(want, max(1, kblocks))
