@@ -18,8 +18,7 @@
  *     every GPU that loads the library until the process exits).  More rows
  *     are rejected with an error message; nothing is launched.
  *   - The first call on a device looks up the array's device address
- *     (cudaGetSymbolAddress).  Make that first call outside any stream
- *     capture; later calls on that device do no set-up.
+ *     (cudaGetSymbolAddress); later calls on that device do no set-up.
  *   - All calls share the one array.  Every slot a call reads is written by
  *     that same call first, so nothing has to be cleared between calls; but
  *     two calls that overlap in time on one GPU (different streams) race on

@@ -86,6 +86,7 @@ log("all_reduce algorithms ok: %s" % algos)
 if info["multicast"]:
     # in-switch reduction on a bandwidth-sized message, integer-valued so that the sum is exact
     for nbytes, dtype in ((64 << 20, torch.bfloat16), (16 << 20, torch.float32)):
+        nbytes = min(nbytes, info["max_chunk"])   # one call's limit depends on the arena and the ranks
         n = nbytes // torch.empty(0, dtype=dtype).element_size()
         x = seeded(rank, n, dtype).to(dev)
         out = torch.empty_like(x)
@@ -225,28 +226,35 @@ for d in range(1, world):
         for r in reqs:
             r.wait()
         assert torch.equal(b.cpu(), seeded(frm, n, torch.float32, 0, 100).to(dtype)), (d, dtype)
-# interleaved outstanding sends of mixed sizes, then the receives, with all-reduces in between
+# several sends of mixed sizes outstanding before the first receive is posted, all-reduces before
+# and after; then p2p and all-reduce strictly interleaved (a collective on the caller's stream
+# waits for the sends queued so far, so it may only follow sends whose receives are already posted
+# on the peer -- the same rule NCCL imposes)
 to, frm = (rank + 1) % world, (rank - 1) % world
 sizes = (10, 70000, 3, 1 << 20)
 outs = [seeded(rank, n, torch.float32).add(i).to(dev) for i, n in enumerate(sizes)]
 ins = [torch.empty(n, dtype=torch.float32, device=dev) for n in sizes]
-pend = []
-for i, o in enumerate(outs):
-    pend.append(dist.isend(o, to))
-    if i == 1:
-        t = torch.ones(2560, dtype=torch.bfloat16, device=dev)
-        dist.all_reduce(t)
-        assert torch.all(t == world)
-for i, buf in enumerate(ins):
-    pend.append(dist.irecv(buf, frm))
-    if i == 2:
-        t = torch.ones(1 << 20, device=dev)
-        dist.all_reduce(t)
-        assert torch.all(t == world)
+t = torch.ones(2560, dtype=torch.bfloat16, device=dev)
+dist.all_reduce(t)
+assert torch.all(t == world)
+pend = [dist.isend(o, to) for o in outs] + [dist.irecv(buf, frm) for buf in ins]
 for r in pend:
     r.wait()
+t = torch.ones(1 << 20, device=dev)
+dist.all_reduce(t)
+assert torch.all(t == world)
 for i, (buf, n) in enumerate(zip(ins, sizes)):
     assert torch.equal(buf.cpu(), seeded(frm, n, torch.float32).add(i)), ("mixed", i)
+for i, n in enumerate(sizes):
+    o = seeded(rank, n, torch.float32).add(10 + i).to(dev)
+    buf = torch.empty(n, dtype=torch.float32, device=dev)
+    reqs = [dist.isend(o, to), dist.irecv(buf, frm)]
+    t = torch.full((4096,), float(i), dtype=torch.bfloat16, device=dev)
+    dist.all_reduce(t)
+    for r in reqs:
+        r.wait()
+    assert torch.all(t == float(i * world)), ("interleaved all_reduce", i)
+    assert torch.equal(buf.cpu(), seeded(frm, n, torch.float32).add(10 + i)), ("interleaved", i)
 # a message far above the p2p slice goes in chunks, full duplex (reference: repro_p2p_big.py:23-71)
 for mb in (48, 128):
     n = (mb << 20) // 4
