@@ -195,7 +195,7 @@ std::tuple<at::Tensor, at::Tensor> w8_group_scales(const at::Tensor& scales) {
 
 at::Tensor w8a16_linear(const at::Tensor& x, const at::Tensor& wq, const at::Tensor& scale,
                         const c10::optional<at::Tensor>& bias, bool silu_mul, int splits,
-                        const c10::optional<at::Tensor>& group_rel) {
+                        const c10::optional<at::Tensor>& group_rel, bool act_int8) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
               "barlink: x must be a 2-D bfloat16 CUDA tensor with unit inner stride");
   TORCH_CHECK(wq.is_cuda() && wq.is_contiguous() && wq.scalar_type() == at::kChar && wq.dim() == 2 &&
@@ -214,6 +214,64 @@ at::Tensor w8a16_linear(const at::Tensor& x, const at::Tensor& wq, const at::Ten
                     group_rel->dim() == 2 && group_rel->size(0) == n && k % group_rel->size(1) == 0,
                 "barlink: group_rel must be contiguous float16 [n, k / group] (see w8_group_scales)");
     TORCH_CHECK(m <= 256, "barlink: in-kernel group scales take at most 256 tokens");
+  }
+  if (act_int8) {
+    // the reference's numerics (w8a16.cu:37-92 there quantises the activations per token and
+    // multiplies int8 by int8): both operands go to the tensor cores as int8
+    TORCH_CHECK(!group_rel, "barlink: int8 activations go with per-channel weight scales");
+    TORCH_CHECK(k % 16 == 0, "barlink: int8 activations need K % 16 == 0");
+    at::Tensor xc = x.is_contiguous() ? x : x.contiguous();
+    at::Tensor xq = at::empty({m, k}, x.options().dtype(at::kChar));
+    at::Tensor xs = at::empty({m}, x.options().dtype(at::kFloat));
+    BL_CHECK(bl_w8a16_quant_act(xc.data_ptr(), m, k, xq.data_ptr(), xs.data_ptr(), st, err, errlen));
+    W8Scratch& s = w8_scratch(dev);
+    if (bias) {
+      check_bf16x(*bias, "bias");
+      TORCH_CHECK(bias->numel() == n, "barlink: bias must have n entries");
+    }
+    if (m <= 256) {
+      blW8A16Args a;
+      memset(&a, 0, sizeof(a));
+      a.xq = xq.data_ptr();
+      a.xs = xs.data_ptr();
+      a.m = m;
+      a.ldx = k;
+      a.wq = wq.data_ptr();
+      a.n = n;
+      a.k = k;
+      a.scale = scale.data_ptr();
+      a.bias = bias ? bias->data_ptr() : nullptr;
+      a.out = out.data_ptr();
+      a.ldo = silu_mul ? n / 2 : n;
+      a.silu_mul = silu_mul ? 1 : 0;
+      a.splits = splits;
+      a.ws = s.ws.data_ptr();
+      a.ws_bytes = size_t(s.ws.nbytes());
+      a.counters = s.counters.data_ptr();
+      a.n_counters = int(s.counters.numel());
+      a.err_flag = s.err_flag.data_ptr();
+      py::gil_scoped_release nogil;
+      BL_CHECK(bl_w8a16_linear(&a, st, err, errlen));
+    } else {
+      // prefill: token-major tiles
+      blGemmArgs g;
+      memset(&g, 0, sizeof(g));
+      g.a = xq.data_ptr(); g.ra = m; g.lda = k;
+      g.b = wq.data_ptr(); g.rb = n; g.ldb = k;
+      g.k = k;
+      g.out = out.data_ptr();
+      g.ldo = silu_mul ? n / 2 : n;
+      g.bias = bias ? bias->data_ptr() : nullptr;
+      g.silu_mul = silu_mul ? 1 : 0;
+      g.splits = 1;
+      g.err_flag = s.err_flag.data_ptr();
+      g.i8 = 1;
+      g.feat_scale = scale.data_ptr();
+      g.tok_scale = xs.data_ptr();
+      py::gil_scoped_release nogil;
+      BL_CHECK(bl_gemm_bf16(&g, st, err, errlen));
+    }
+    return out;
   }
   if (m > 256) {
     at::Tensor w = at::empty({n, k}, x.options());
@@ -590,7 +648,7 @@ void bind_extra(py::module_& m) {
         py::arg("rows_per_batch"));
   m.def("w8a16_linear", &w8a16_linear, py::arg("x"), py::arg("wq"), py::arg("scale"),
         py::arg("bias") = py::none(), py::arg("silu_mul") = false, py::arg("splits") = 0,
-        py::arg("group_rel") = py::none());
+        py::arg("group_rel") = py::none(), py::arg("act_int8") = false);
   m.def("w8_group_scales", &w8_group_scales, py::arg("scales"));
   m.def("w8_error_flag", &w8_error_flag, py::arg("device") = 0);
   m.def("dlin", &dlin, py::arg("x"), py::arg("weight"), py::arg("pro") = "none", py::arg("epi") = "store",

@@ -97,6 +97,12 @@ typedef struct blGemmArgs {
    * (lda/ldb of that operand are ignored) */
   int weight_tiled;
   void* trace; /* debug: u64[8 * grid] global-timer stamps per CTA, or null */
+  /* 1: a and b are signed 8-bit (lda/ldb/k in elements, k a multiple of 16); products accumulate in
+   * int32 on the tensor cores and the result is acc * feat_scale[feature] * tok_scale[token].
+   * Not with weight_tiled, peer, push or gate_flags. */
+  int i8;
+  const void* feat_scale; /* bf16 per output feature, or null */
+  const void* tok_scale;  /* fp32 per token, or null */
 } blGemmArgs;
 int bl_gemm_bf16(const blGemmArgs* a, void* stream, char* err, size_t errlen);
 /* Weights in 16 KiB tiles [ceil(n/128)][ceil(k/64)][128 x 128 B], each tile in the
@@ -139,6 +145,11 @@ typedef struct blW8A16Args {
    * scale (see bl_w8_group_scales).  group_k must be a multiple of 64.  null = per channel only */
   const void* group_rel;
   int group_k;
+  /* activations already quantised per token (bl_w8a16_quant_act): xq int8 [m x k] dense and xs fp32
+   * [m].  The product then runs as int8 x int8 on the tensor cores (no widening of the weights); x is
+   * ignored, group_rel must be null and partial_out is not supported. */
+  const void* xq;
+  const void* xs;
 } blW8A16Args;
 /* scales bf16 [n][groups] -> row_max bf16 [n] and rel fp16 [n][groups] = scale / row_max */
 int bl_w8_group_scales(const void* scales, int n, int groups, void* row_max, void* rel, void* stream, char* err,

@@ -41,6 +41,7 @@ struct GemmShape {
   int kblocks;              // ceil(k/64)
   int splits;               // k-splits per tile
   int ab_fmt;               // 1 = bf16, 0 = fp16
+  int i8;                   // 1: both operands are signed 8-bit, a k-block is 128 elements, int32 accumulators
   int direct;               // 1: every k-split hands its raw partial tile to the Sink (no in-kernel reduce)
   int weights_in_a;         // operand that no earlier kernel writes: 1 = A, 0 = B, 2 = neither
   float* ws;                // [tiles*splits][BN][128] fp32 partials (splits > 1)
@@ -69,36 +70,46 @@ struct GemmShape {
   uint32_t gate_add;
   int gate_n;
   unsigned long long gate_timeout_ns;
+  // paired-CTA kernel: walk order of the output tiles (see pair_tile_of)
+  int band, band_m;
 };
 
 // W8: the A operand (weight rows) is int8 in global memory; its 128x64-byte raw
-// tile lands in a third region of the stage and four extra warps widen it to
-// bf16 into the swizzled A region before the MMA warp may use the stage.
+// tile lands in a third region of the stage and eight extra warps (two groups that
+// take alternate k-blocks) widen it to bf16 into a swizzled A tile before the MMA
+// warp may use it.
 template <int BN, int CPS = 1, bool W8 = false>
 struct GemmSmem {
   static constexpr int kStageA = kTileA * kTileK * 2;
-  static constexpr int kStageB = BN * kTileK * 2;
-  static constexpr int kStageRaw = W8 ? kTileA * kTileK : 0;
-  // bf16: a stage is [A 16 KiB][B]; W8: a stage is [B][raw int8 A 8 KiB] and the
+  static constexpr int kStageB = BN * kTileK * 2;  // one k-block of the B operand
+  // W8, narrow tiles: a stage holds TWO k-blocks.  The raw int8 A tile is then 128 rows of 128
+  // bytes (one request per row and per 128-byte line instead of two of 64 bytes): the number of
+  // row requests per k-block, which bounds these weight-streaming shapes, drops by a third to a
+  // half.
+  static constexpr int kKS = (W8 && BN <= 64) ? 2 : 1;
+  static constexpr int kStageRaw = W8 ? kTileA * kTileK * kKS : 0;
+  // bf16: a stage is [A 16 KiB][B]; W8: a stage is [B of each k-block][raw int8 A] and the
   // widened A tiles live in a short ring of their own behind the stages, so
   // that many raw stages (= bytes in flight from HBM) fit
-  static constexpr int kStageBytes = W8 ? kStageB + kStageRaw : kStageA + kStageB;
+  static constexpr int kStageBytes = W8 ? kKS * kStageB + kStageRaw : kStageA + kStageB;
   static constexpr int kOffB = W8 ? 0 : kStageA;
-  static constexpr int kOffRaw = kStageB;
+  static constexpr int kOffRaw = kKS * kStageB;
   static constexpr int kA16Stages = W8 ? (BN <= 64 ? 4 : 3) : 0;
-  static constexpr int kTxBytes = kStageBytes;  // bytes TMA delivers per stage
+  static constexpr int kTxBytes = kStageBytes;  // bytes TMA delivers per full stage
   static constexpr int kConvThreads = W8 ? 256 : 0;
   static constexpr int kThreads = kGemmThreads + kConvThreads;
   // narrow tiles (decode): 4 stages so that two CTAs share an SM -- the same
   // bytes in flight per SM, but a CTA of the next kernel can move in and
   // prefetch weights while one of this kernel is still in its epilogue
-  static constexpr int kStages = W8 ? (BN <= 16 ? 16 : BN <= 32 ? 13 : BN <= 64 ? 10 : BN <= 128 ? 7 : 4)
+  static constexpr int kStages = W8 ? (BN <= 16 ? 8 : BN <= 32 ? 6 : BN <= 64 ? 5 : BN <= 128 ? 7 : 4)
                                     : (CPS == 2) ? 4 : (BN <= 64 ? 8 : (BN <= 128 ? 6 : 4));
   static constexpr int kCtasPerSm = CPS;
   static constexpr int kBarBytes = 1024;
   // + 1024 so that the tile ring can be aligned to the swizzle atom
   static constexpr int kBytes = kStages * kStageBytes + kA16Stages * kStageA + kBarBytes + 1024;
   static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  static_assert(kBytes <= 232448, "stage ring does not fit the shared memory of one CTA");
+  static_assert(kStageBytes % 1024 == 0 && kOffRaw % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 };
 
 // Sink concept:
@@ -131,6 +142,11 @@ __device__ __forceinline__ void s8x4_to_bf16x4_scaled(uint32_t w, float sc, uint
   const float f3 = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)), sc, nb);
   lo = pack_bf16x2(f0, f1);
   hi = pack_bf16x2(f2, f3);
+}
+
+// an accumulator word as fp32: the bits of a float, or (int8 products) an int32 to convert
+__device__ __forceinline__ float acc_f32(uint32_t bits, bool i8) {
+  return i8 ? float(int32_t(bits)) : __uint_as_float(bits);
 }
 
 template <int BN, int CPS, bool W8, class Sink>
@@ -167,7 +183,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
       bulk_load_s(dst, g.tiled_base + (size_t(ta) * g.tiled_kblocks + kb) * S::kStageA, S::kStageA, bar,
                   hint_a);
     else
-      tma_load_2d_hint_s(dst, tmap_a, bar, kb * kTileK, ta * kTileA, hint_a);
+      tma_load_2d_hint_s(dst, tmap_a, bar, kb * (g.i8 ? 2 * kTileK : kTileK), ta * kTileA, hint_a);
   };
   auto load_b = [&](uint32_t dst, uint32_t bar, int kb, int tb) {
     if (!W8 && g.tiled == 2) {
@@ -185,7 +201,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
                       S::kStageA, bar, hint_b);
       }
     } else {
-      tma_load_2d_hint_s(dst, tmap_b, bar, kb * kTileK, tb * BN, hint_b);
+      tma_load_2d_hint_s(dst, tmap_b, bar, kb * (g.i8 ? 2 * kTileK : kTileK), tb * BN, hint_b);
     }
   };
 
@@ -195,7 +211,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
       mbar_init(&empty_bar[s], 1);
     }
     for (int s = 0; s < 4; ++s) {
-      mbar_init(&ready_bar[s], S::kConvThreads > 0 ? S::kConvThreads : 1);
+      mbar_init(&ready_bar[s], S::kConvThreads > 0 ? S::kConvThreads / 64 : 1);  // one lane of each warp of a widening group  // one group of widening threads per k-block
       mbar_init(&afree_bar[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -230,8 +246,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
         const int ta = tile / g.tiles_b, tb = tile - ta * g.tiles_b;
         const int kb0 = sp * kb_per;
         const int kb1 = min(g.kblocks, kb0 + kb_per);
-        for (int kb = kb0; kb < kb1 && pre < S::kStages; ++kb, ++pre) {
-          mbar_expect_tx(&full_bar[pre], S::kTxBytes);
+        for (int kb = kb0; kb < kb1 && pre < S::kStages; kb += S::kKS, ++pre) {
+          const int nsub = min(S::kKS, kb1 - kb);  // k-blocks in this stage
+          mbar_expect_tx(&full_bar[pre], S::kTxBytes - (S::kKS - nsub) * S::kStageB);
           const uint32_t sa = ring + pre * S::kStageBytes;
           if (g.weights_in_a)
             load_a(sa + (W8 ? S::kOffRaw : 0), smem_u32(&full_bar[pre]), kb, ta);
@@ -272,11 +289,12 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
         const int ta = tile / g.tiles_b, tb = tile - ta * g.tiles_b;
         const int kb0 = sp * kb_per;
         const int kb1 = min(g.kblocks, kb0 + kb_per);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0; kb < kb1; kb += S::kKS) {
           if (*s_abort && armed >= pre) {
             ok = false;
             break;
           }
+          const int nsub = min(S::kKS, kb1 - kb);
           const uint32_t sa = ring + stage * S::kStageBytes;
           const bool early = armed < pre;  // weight tile of this stage is already on its way
           if (!early) {
@@ -284,12 +302,15 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
               ok = false;
               break;
             }
-            mbar_expect_tx(&full_bar[stage], S::kTxBytes);
+            mbar_expect_tx(&full_bar[stage], S::kTxBytes - (S::kKS - nsub) * S::kStageB);
           }
           if (!early || !g.weights_in_a)
             load_a(sa + (W8 ? S::kOffRaw : 0), smem_u32(&full_bar[stage]), kb, ta);
-          if (!early || g.weights_in_a)
-            load_b(sa + S::kOffB, smem_u32(&full_bar[stage]), kb, tb);
+          if (!early || g.weights_in_a) {
+#pragma unroll
+            for (int sb = 0; sb < S::kKS; ++sb)
+              if (sb < nsub) load_b(sa + S::kOffB + sb * S::kStageB, smem_u32(&full_bar[stage]), kb + sb, tb);
+          }
           ++armed;
           if (++stage == S::kStages) {
             stage = 0;
@@ -316,7 +337,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ----------------------------
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc_f16(kTileA, BN, g.ab_fmt);
+      const uint32_t idesc = (!W8 && g.i8) ? umma_idesc_i8(kTileA, BN) : umma_idesc_f16(kTileA, BN, g.ab_fmt);
       int stage = 0, astage = 0;
       uint32_t phase = 0, aphase = 0;
       uint32_t tphase[2] = {0, 0};
@@ -331,32 +352,46 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
         tphase[acc] ^= 1u;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait_bounded(W8 ? &ready_bar[astage] : &full_bar[stage], W8 ? aphase : phase,
-                                 s_abort)) {
+        for (int kb = kb0; kb < kb1 && ok; kb += S::kKS) {
+          const int nsub = min(S::kKS, kb1 - kb);
+          const uint32_t sa = ring + stage * S::kStageBytes;
+          if (!W8 && !mbar_wait_bounded(&full_bar[stage], phase, s_abort)) {
             ok = false;
             break;
           }
-          tc_fence_after_sync();
-          if (tr && kb == kb0 && it == 0) tr[3] = globaltimer_ns();
-          const uint32_t sa = ring + stage * S::kStageBytes;
-          const uint64_t da =
-              umma_desc_k_sw128(W8 ? ring + S::kStages * S::kStageBytes + astage * S::kStageA : sa);
-          const uint64_t db = umma_desc_k_sw128(sa + S::kOffB);
 #pragma unroll
-          for (int k = 0; k < kTileK / 16; ++k) {
-            // +32 bytes along K inside the swizzle atom = +2 in the address field
-            umma_f16_ss(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), idesc,
-                        (kb > kb0 || k > 0) ? 1u : 0u);
-          }
-          umma_commit(&empty_bar[stage]);
-          if (W8) {
-            umma_commit(&afree_bar[astage]);
-            if (++astage == S::kA16Stages) {
-              astage = 0;
-              aphase ^= 1u;
+          for (int sb = 0; sb < S::kKS; ++sb) {
+            if (sb >= nsub) break;
+            // W8: the widening threads have waited for the stage; the widened tile is what counts
+            if (W8 && !mbar_wait_bounded(&ready_bar[astage], aphase, s_abort)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            if (tr && kb == kb0 && sb == 0 && it == 0) tr[3] = globaltimer_ns();
+            const uint64_t da =
+                umma_desc_k_sw128(W8 ? ring + S::kStages * S::kStageBytes + astage * S::kStageA : sa);
+            const uint64_t db = umma_desc_k_sw128(sa + S::kOffB + sb * S::kStageB);
+#pragma unroll
+            for (int k = 0; k < kTileK / 16; ++k) {
+              // +32 bytes along K inside the swizzle atom = +2 in the address field
+              if (!W8 && g.i8)
+                umma_i8_ss(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), idesc,
+                           (kb + sb > kb0 || k > 0) ? 1u : 0u);
+              else
+                umma_f16_ss(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), idesc,
+                            (kb + sb > kb0 || k > 0) ? 1u : 0u);
+            }
+            if (W8) {
+              umma_commit(&afree_bar[astage]);
+              if (++astage == S::kA16Stages) {
+                astage = 0;
+                aphase ^= 1u;
+              }
             }
           }
+          if (!ok) break;
+          umma_commit(&empty_bar[stage]);
           if (++stage == S::kStages) {
             stage = 0;
             phase ^= 1u;
@@ -367,11 +402,21 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
     }
   } else if (W8 && warp >= 6) {
     // ------------------------ int8 -> bf16 widening -----------------------
-    // two threads per tile row: 32 int8 in, 4 swizzled 16-byte chunks of bf16 out
+    // Two groups of 128 threads take alternate stages, so that the load -> convert -> store ->
+    // proxy fence chain of one stage overlaps the next one's.  A thread widens one whole tile
+    // row per k-block: 64 int8 in (four 16-byte loads issued together), eight swizzled 16-byte
+    // chunks of bf16 out; one warp lane per warp then reports the tile.  Bank conflicts: with two
+    // k-blocks per stage the raw tile has 128-byte rows in the 128-byte swizzle, so the eight
+    // rows of a quarter warp find the same logical chunk in eight different banks groups.  With
+    // one k-block per stage the raw rows are 64 plain bytes and thread t reads its chunks in the
+    // order sig(t) ^ c, sig a permutation of 0..3 over (t / 2) & 3 for which sig ^ ((t / 2) & 3)
+    // is a permutation too: again 32 different banks per quarter warp, loads and stores.
     const int ct = threadIdx.x - kGemmThreads;
-    const int row = ct >> 1, half = ct & 1;
-    int stage = 0, astage = 0;
-    uint32_t phase = 0, aphase = 0;
+    const int grp = ct >> 7, row = ct & 127;
+    const int sig = S::kKS == 1 ? (0x2130 >> (4 * ((row >> 1) & 3))) & 3 : 0;
+    constexpr int kA16 = S::kA16Stages > 0 ? S::kA16Stages : 1;
+    int nst = 0;  // stages of this CTA so far, over all its units
+    int nkb = 0;  // k-blocks so far
     bool ok = true;
     for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
       const int tile = u / g.splits, sp = u - tile * g.splits;
@@ -379,50 +424,61 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
       const int kb1 = min(g.kblocks, kb0 + kb_per);
       const int grow = (tile / g.tiles_b) * kTileA + row;
       const __half* gs = (g.gscale && grow < g.ra) ? g.gscale + size_t(grow) * g.gs_groups : nullptr;
-      for (int kb = kb0; kb < kb1; ++kb) {
-        const float sc = gs ? __half2float(gs[kb / g.gs_kblocks]) : 1.f;
-        if (!mbar_wait_bounded(&full_bar[stage], phase, s_abort) ||
-            !mbar_wait_bounded(&afree_bar[astage], aphase ^ 1u, s_abort)) {
+      for (int kb = kb0; kb < kb1 && ok; kb += S::kKS, ++nst) {
+        const int nsub = min(S::kKS, kb1 - kb);
+        if ((nst & 1) != grp) {
+          nkb += nsub;
+          continue;
+        }
+        const int stage = nst % S::kStages;
+        if (!mbar_wait_bounded(&full_bar[stage], uint32_t(nst / S::kStages) & 1u, s_abort)) {
           ok = false;
           break;
         }
-        const uint32_t src = ring + stage * S::kStageBytes + S::kOffRaw + row * kTileK + half * 32;
-        const uint32_t dst = ring + S::kStages * S::kStageBytes + astage * S::kStageA + row * 128;
+        const uint32_t raw = ring + stage * S::kStageBytes + S::kOffRaw + row * (kTileK * S::kKS);
 #pragma unroll
-        for (int qd = 0; qd < 2; ++qd) {
-          uint32_t w0, w1, w2, w3;
-          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                       : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
-                       : "r"(src + qd * 16));
-          uint32_t o0, o1, o2, o3, o4, o5, o6, o7;
-          if (g.gscale) {
-            s8x4_to_bf16x4_scaled(w0, sc, o0, o1);
-            s8x4_to_bf16x4_scaled(w1, sc, o2, o3);
-            s8x4_to_bf16x4_scaled(w2, sc, o4, o5);
-            s8x4_to_bf16x4_scaled(w3, sc, o6, o7);
-          } else {
-            s8x4_to_bf16x4(w0, o0, o1);
-            s8x4_to_bf16x4(w1, o2, o3);
-            s8x4_to_bf16x4(w2, o4, o5);
-            s8x4_to_bf16x4(w3, o6, o7);
+        for (int sb = 0; sb < S::kKS; ++sb, ++nkb) {
+          if (sb >= nsub) break;
+          const int astage = nkb % kA16;
+          const float sc = gs ? __half2float(gs[(kb + sb) / g.gs_kblocks]) : 1.f;
+          if (!mbar_wait_bounded(&afree_bar[astage], (uint32_t(nkb / kA16) & 1u) ^ 1u, s_abort)) {
+            ok = false;
+            break;
           }
-          const int c0 = half * 4 + qd * 2, c1 = c0 + 1;
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + (((c0 ^ (row & 7))) << 4)),
-                       "r"(o0), "r"(o1), "r"(o2), "r"(o3)
-                       : "memory");
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + (((c1 ^ (row & 7))) << 4)),
-                       "r"(o4), "r"(o5), "r"(o6), "r"(o7)
-                       : "memory");
-        }
-        fence_proxy_async_smem();  // the tensor core reads what these threads just wrote
-        mbar_arrive(&ready_bar[astage]);
-        if (++astage == S::kA16Stages) {
-          astage = 0;
-          aphase ^= 1u;
-        }
-        if (++stage == S::kStages) {
-          stage = 0;
-          phase ^= 1u;
+          const uint32_t dst = ring + S::kStages * S::kStageBytes + astage * S::kStageA + row * 128;
+          uint32_t w[4][4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int ch = S::kKS == 1 ? (sig ^ c) : ((sb * 4 + c) ^ (row & 7));
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(w[c][0]), "=r"(w[c][1]), "=r"(w[c][2]), "=r"(w[c][3])
+                         : "r"(raw + (ch << 4)));
+          }
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o0, o1, o2, o3, o4, o5, o6, o7;
+            if (g.gscale) {
+              s8x4_to_bf16x4_scaled(w[c][0], sc, o0, o1);
+              s8x4_to_bf16x4_scaled(w[c][1], sc, o2, o3);
+              s8x4_to_bf16x4_scaled(w[c][2], sc, o4, o5);
+              s8x4_to_bf16x4_scaled(w[c][3], sc, o6, o7);
+            } else {
+              s8x4_to_bf16x4(w[c][0], o0, o1);
+              s8x4_to_bf16x4(w[c][1], o2, o3);
+              s8x4_to_bf16x4(w[c][2], o4, o5);
+              s8x4_to_bf16x4(w[c][3], o6, o7);
+            }
+            const int c0 = (S::kKS == 1 ? (sig ^ c) : c) * 2, c1 = c0 + 1;
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + (((c0 ^ (row & 7))) << 4)),
+                         "r"(o0), "r"(o1), "r"(o2), "r"(o3)
+                         : "memory");
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + (((c1 ^ (row & 7))) << 4)),
+                         "r"(o4), "r"(o5), "r"(o6), "r"(o7)
+                         : "memory");
+          }
+          fence_proxy_async_smem();  // the tensor core reads what these threads just wrote
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ready_bar[astage]);
         }
       }
     }
@@ -431,6 +487,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int row = q * 32 + lane;
     const int et = threadIdx.x - 64;  // 0..127
+    const bool i8 = !W8 && g.i8;
     uint32_t tphase[2] = {0, 0};
     int it = 0;
     pdl_wait();  // outputs, residuals and the split-K scratch belong to earlier kernels until now
@@ -452,13 +509,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
             tmem_ld_32x32(taddr + c0, r);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            for (int i = 0; i < 32; ++i) v[i] = acc_f32(r[i], i8);
           } else {
             uint32_t r[16];
             tmem_ld_32x16(taddr + c0, r);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+            for (int i = 0; i < 16; ++i) v[i] = acc_f32(r[i], i8);
 #pragma unroll
             for (int i = 16; i < 32; ++i) v[i] = 0.f;
           }
@@ -478,16 +535,16 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; i += 4)
-              __stcg(wp + (c0 + i) / 4, make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]),
-                                                    __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])));
+              __stcg(wp + (c0 + i) / 4,
+                     make_float4(acc_f32(r[i], i8), acc_f32(r[i + 1], i8), acc_f32(r[i + 2], i8), acc_f32(r[i + 3], i8)));
           } else {
             uint32_t r[16];
             tmem_ld_32x16(taddr + c0, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; i += 4)
-              __stcg(wp + (c0 + i) / 4, make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]),
-                                                    __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])));
+              __stcg(wp + (c0 + i) / 4,
+                     make_float4(acc_f32(r[i], i8), acc_f32(r[i + 1], i8), acc_f32(r[i + 2], i8), acc_f32(r[i + 3], i8)));
           }
         }
         tc_fence_before_sync();

@@ -40,6 +40,7 @@ struct LocalSink {
   const __nv_bfloat16* residual;
   int ldo, ra, rb, swap, epi;
   const __nv_bfloat16* scale;  // per output feature (W8A16), or null
+  const float* xscale;         // per token (int8 activations), or null
   // Row push (token-major only, pworld > 0): row m belongs to rank (prow0 + m) / ptpr and is stored
   // into that rank's staging inbox slot for this rank -- the scatter half of a two-shot all-reduce
   // done by the GEMM epilogue over NVLink, tile by tile, while the other tiles are still in the
@@ -79,6 +80,16 @@ struct LocalSink {
     } else {
 #pragma unroll
       for (int c = 0; c < 32; ++c) v[c] = vin[c];
+    }
+    if (xscale) {
+      if (swap) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c] *= (c < ncols && j0 + c < rb) ? xscale[j0 + c] : 0.f;
+      } else {
+        const float sc = i < ra ? xscale[i] : 0.f;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c] *= sc;
+      }
     }
     if (!swap) {
       const int m = i;
@@ -328,10 +339,10 @@ __global__ void k_tile_weight(const __nv_bfloat16* __restrict__ src, uint4* __re
 struct TmapKey {
   const void* ptr;
   uint64_t rows, cols, ld;
-  uint32_t box_rows, esize;  // esize 1 = int8 rows of 64 bytes, unswizzled
+  uint32_t box_rows, esize, box_cols;
   bool operator==(const TmapKey& o) const {
     return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld &&
-           box_rows == o.box_rows && esize == o.esize;
+           box_rows == o.box_rows && esize == o.esize && box_cols == o.box_cols;
   }
 };
 struct TmapHash {
@@ -341,17 +352,22 @@ struct TmapHash {
     h = h * 1000003u ^ k.cols;
     h = h * 1000003u ^ k.ld;
     h = h * 1000003u ^ k.box_rows;
-    return h * 31u + k.esize;
+    return (h * 31u + k.esize) * 31u + k.box_cols;
   }
 };
 static std::unordered_map<TmapKey, CUtensorMap, TmapHash> g_tmaps;
 static std::mutex g_tmap_mu;
 
-// K-major matrix [rows x cols] of 1- or 2-byte elements, row pitch ld
-// elements, box = box_rows x 128 bytes, 128-byte swizzle.
+// K-major matrix [rows x cols] of 1- or 2-byte elements, row pitch ld elements, box = box_rows x
+// box_cols elements: 128 bytes per box row in the 128-byte swizzle (64 bf16, or 128 int8 = two
+// k-blocks), or 64 plain bytes of int8.
 int make_tmap_kmajor(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
-                     uint32_t esize, CUtensorMap* out, char* err, size_t errlen) {
-  TmapKey key{ptr, rows, cols, ld, box_rows, esize};
+                     uint32_t esize, CUtensorMap* out, char* err, size_t errlen, uint32_t box_cols) {
+  TmapKey key{ptr, rows, cols, ld, box_rows, esize, box_cols};
+  if (box_cols * esize != 128 && !(esize == 1 && box_cols == 64)) {
+    set_err(err, errlen, "barlink: unsupported tensor-map box of %u elements of %u bytes", box_cols, esize);
+    return -1;
+  }
   {
     std::lock_guard<std::mutex> g(g_tmap_mu);
     auto it = g_tmaps.find(key);
@@ -370,14 +386,13 @@ int make_tmap_kmajor(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
   }
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {ld * esize};
-  // 64 elements along K per box row: 128 swizzled bytes of bf16, or 64 plain bytes of int8
-  cuuint32_t box[2] = {64u, box_rows};
+  cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
   CUresult r = d->cuTensorMapEncodeTiled(
       &m, esize == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
       const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-      esize == 2 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+      box_cols * esize == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     const char* s = nullptr;
@@ -459,8 +474,9 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
   CUtensorMap ta, tb;
   // a pre-tiled weight operand needs no tensor map (the other operand's map stands in)
   const bool a_tiled = a.weight_tiled && a.swap, b_tiled = a.weight_tiled && !a.swap;
-  if (!b_tiled && make_tmap_kmajor(a.b, a.rb, a.k, a.ldb, BN, 2, &tb, err, errlen) != 0) return -1;
-  if (!a_tiled && make_tmap_kmajor(a.a, a.ra, a.k, a.lda, kTileA, 2, &ta, err, errlen) != 0) return -1;
+  const uint32_t esize = a.i8 ? 1 : 2, box_cols = a.i8 ? 2 * kTileK : kTileK;  // 128 bytes per box row either way
+  if (!b_tiled && make_tmap_kmajor(a.b, a.rb, a.k, a.ldb, BN, esize, &tb, err, errlen, box_cols) != 0) return -1;
+  if (!a_tiled && make_tmap_kmajor(a.a, a.ra, a.k, a.lda, kTileA, esize, &ta, err, errlen, box_cols) != 0) return -1;
   if (a_tiled) ta = tb;
   if (b_tiled) tb = ta;
   GemmShape g;
@@ -469,7 +485,8 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
   g.k = a.k;
   g.tiles_a = (a.ra + kTileA - 1) / kTileA;
   g.tiles_b = (a.rb + BN - 1) / BN;
-  g.kblocks = (a.k + kTileK - 1) / kTileK;
+  g.kblocks = (a.k + int(box_cols) - 1) / int(box_cols);
+  g.i8 = a.i8 ? 1 : 0;
   const int tiles = g.tiles_a * g.tiles_b;
   const int sms = sm_count();
   // CTAs launched at most (BL_GEMM_WAVE: percent of the resident slots)
@@ -577,7 +594,8 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
     sink.rb = a.rb;
     sink.swap = a.swap;
     sink.epi = (a.bias ? 1 : 0) | (a.residual ? 2 : 0) | (a.silu_mul ? 4 : 0) | (a.gelu ? 8 : 0);
-    sink.scale = nullptr;
+    sink.scale = static_cast<const __nv_bfloat16*>(a.feat_scale);
+    sink.xscale = static_cast<const float*>(a.tok_scale);
     fill_push(sink, a.push);
     static bool attr_set = false;
     if (!attr_set) {
@@ -644,7 +662,7 @@ template <int BN>
 static int launch_w8(const blW8A16Args& a, cudaStream_t st, char* err, size_t errlen) {
   using S = GemmSmem<BN, 1, true>;
   CUtensorMap ta, tb;
-  if (make_tmap_kmajor(a.wq, a.n, a.k, a.k, kTileA, 1, &ta, err, errlen) != 0) return -1;
+  if (make_tmap_kmajor(a.wq, a.n, a.k, a.k, kTileA, 1, &ta, err, errlen, 64 * S::kKS) != 0) return -1;
   if (make_tmap_kmajor(a.x, a.m, a.k, a.ldx, BN, 2, &tb, err, errlen) != 0) return -1;
   GemmShape g;
   memset(&g, 0, sizeof(g));
@@ -716,6 +734,7 @@ static int launch_w8(const blW8A16Args& a, cudaStream_t st, char* err, size_t er
     sink.swap = 1;
     sink.epi = (a.bias ? 1 : 0) | (a.silu_mul ? 4 : 0);
     sink.scale = static_cast<const __nv_bfloat16*>(a.scale);
+    sink.xscale = nullptr;
     fill_push(sink, nullptr);
     static bool attr = false;
     if (!attr) {
@@ -788,6 +807,23 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
 }
 
+// Order in which the pairs walk the output tiles.  The tiles of one dimension are cut into bands
+// of `band` tiles; inside a band the other dimension is the slow index.  The operand slab of a band
+// (band x 256 rows x K) stays in L2 while the other operand streams past it once per band, so each
+// operand is fetched from DRAM a few times at most instead of once per wave of pairs.
+__device__ __forceinline__ void pair_tile_of(int u, int tiles_m, int tiles_n, int band, int along_m, int& tm,
+                                             int& tn) {
+  const int nf = along_m ? tiles_m : tiles_n;  // banded dimension
+  const int ns = along_m ? tiles_n : tiles_m;  // swept dimension
+  const int per = band * ns;
+  const int b = u / per, r = u - b * per;
+  const int f0 = b * band;
+  const int w = min(band, nf - f0);
+  const int sl = r / w, f = f0 + r - sl * w;
+  tm = along_m ? f : sl;
+  tn = along_m ? sl : f;
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     k_gemm_pair(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 GemmShape g, LocalSink<kPairBN> sink, uint64_t hint_a, uint64_t hint_b) {
@@ -846,7 +882,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
       int issued = 0;
       bool ok = true;
       for (int u = pair; u < units && ok; u += n_pairs) {
-        const int tm = u / tiles_n, tn = u - tm * tiles_n;
+        int tm, tn;
+        pair_tile_of(u, tiles_m, tiles_n, g.band, g.band_m, tm, tn);
         for (int kb = 0; kb < g.kblocks; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, s_abort)) {
             ok = false;
@@ -916,7 +953,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     uint32_t tphase[2] = {0, 0};
     int it = 0;
     for (int u = pair; u < units; u += n_pairs, ++it) {
-      const int tm = u / tiles_n, tn = u - tm * tiles_n;
+      int tm, tn;
+      pair_tile_of(u, tiles_m, tiles_n, g.band, g.band_m, tm, tn);
       const int acc = it & 1;
       if (!mbar_wait_bounded(&tfull_bar[acc], tphase[acc], s_abort)) break;
       tphase[acc] ^= 1u;
@@ -958,7 +996,7 @@ static bool gemm_pair_enabled() {
 
 // token-major product with at least 512 tokens, no k-split, no fused collective
 static bool gemm_pair_ok(const blGemmArgs& a) {
-  return gemm_pair_enabled() && !a.swap && a.ra >= 512 && a.rb >= 256 && !a.partial_out && !a.peer &&
+  return gemm_pair_enabled() && !a.i8 && !a.swap && a.ra >= 512 && a.rb >= 256 && !a.partial_out && !a.peer &&
          !a.gate_flags && !a.weight_tiled && !a.silu_mul && a.splits <= 1;
 }
 
@@ -984,6 +1022,7 @@ static int launch_gemm_pair(const blGemmArgs& a, cudaStream_t st, char* err, siz
   sink.swap = 0;
   sink.epi = (a.bias ? 1 : 0) | (a.residual ? 2 : 0) | (a.gelu ? 8 : 0);
   sink.scale = nullptr;
+  sink.xscale = nullptr;
   fill_push(sink, a.push);
   static bool attr = false;
   if (!attr) {
@@ -994,13 +1033,31 @@ static int launch_gemm_pair(const blGemmArgs& a, cudaStream_t st, char* err, siz
     }
     attr = true;
   }
-  const int units = ((a.ra + 255) / 256) * ((a.rb + 255) / 256);
+  const int tiles_m = (a.ra + 255) / 256, tiles_n = (a.rb + 255) / 256;
+  const int units = tiles_m * tiles_n;
+  // band width: the slab that has to stay in L2 is at most 32 MB; bands of equal width; the
+  // orientation that fetches fewer bytes from DRAM (slab operand once, the other once per band)
+  const double tile_bytes = 256.0 * a.k * 2;
+  int cap_tiles = int(32e6 / tile_bytes);
+  if (cap_tiles < 1) cap_tiles = 1;
+  auto even_band = [](int n, int wmax) {
+    const int nb = (n + wmax - 1) / wmax;
+    return (n + nb - 1) / nb;
+  };
+  const int wn = even_band(tiles_n, cap_tiles), wm = even_band(tiles_m, cap_tiles);
+  const double dram_n = tile_bytes * (tiles_n + double(tiles_m) * ((tiles_n + wn - 1) / wn));
+  const double dram_m = tile_bytes * (tiles_m + double(tiles_n) * ((tiles_m + wm - 1) / wm));
+  static const int band_env = env_int_or("BL_GEMM_BAND", 0);  // debug: 0 = choose, n > 0 = bands of n along n, n < 0 along m
+  g.band_m = band_env ? (band_env < 0) : (dram_m < dram_n);
+  g.band = band_env ? (band_env < 0 ? -band_env : band_env) : (g.band_m ? wm : wn);
+  if (g.band > (g.band_m ? tiles_m : tiles_n)) g.band = g.band_m ? tiles_m : tiles_n;
   int pairs = sm_count() / 2;
   if (pairs > units) pairs = units;
   if (pairs < 1) pairs = 1;
   // the cluster shape is compiled into the kernel (__cluster_dims__); the grid is a whole number of pairs
+  // the slab operand is the one to keep in L2
   cudaError_t e = launch_k(k_gemm_pair, dim3(2 * pairs), dim3(kPairThreads), size_t(kPairSmem), st, ta, tb, g, sink,
-                           kHintEvictLast, kHintEvictFirst);
+                           g.band_m ? kHintEvictLast : kHintEvictFirst, g.band_m ? kHintEvictFirst : kHintEvictLast);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_err(err, errlen, "barlink: paired GEMM launch failed: %s", cudaGetErrorString(e));
@@ -1014,7 +1071,7 @@ static int launch_gemm_pair(const blGemmArgs& a, cudaStream_t st, char* err, siz
 using namespace bl;
 
 extern "C" int bl_w8a16_linear(const blW8A16Args* a, void* stream, char* err, size_t errlen) {
-  if (!a || !a->x || !a->wq || !a->scale || (!a->out && !a->partial_out) || a->m < 1 || a->n < 1 ||
+  if (!a || (!a->x && !a->xq) || !a->wq || !a->scale || (!a->out && !a->partial_out) || a->m < 1 || a->n < 1 ||
       a->k < 16 || (a->k & 15)) {
     set_err(err, errlen, "barlink: w8a16_linear needs x, wq, scale, an output, and K a multiple of 16");
     return -1;
@@ -1030,6 +1087,31 @@ extern "C" int bl_w8a16_linear(const blW8A16Args* a, void* stream, char* err, si
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int bn = a->m <= 16 ? 16 : a->m <= 32 ? 32 : a->m <= 64 ? 64 : a->m <= 128 ? 128 : 256;
+  if (a->xq) {
+    // int8 activations: the weights go from HBM to the tensor cores as they are
+    if (!a->xs || a->group_rel || a->partial_out) {
+      set_err(err, errlen, "barlink: int8 activations need their per-token scales, per-channel weight scales and a plain output");
+      return -1;
+    }
+    blGemmArgs g;
+    memset(&g, 0, sizeof(g));
+    g.a = a->wq; g.ra = a->n; g.lda = a->k;
+    g.b = a->xq; g.rb = a->m; g.ldb = a->k;
+    g.k = a->k;
+    g.out = a->out; g.ldo = a->ldo;
+    g.swap = 1;
+    g.bias = a->bias;
+    g.silu_mul = a->silu_mul;
+    g.bn = bn;
+    g.splits = a->splits;
+    g.ws = a->ws; g.ws_bytes = a->ws_bytes;
+    g.counters = a->counters; g.n_counters = a->n_counters;
+    g.err_flag = a->err_flag;
+    g.i8 = 1;
+    g.feat_scale = a->scale;
+    g.tok_scale = a->xs;
+    return bl_gemm_bf16(&g, stream, err, errlen);
+  }
   switch (bn) {
     case 16: return launch_w8<16>(*a, st, err, errlen);
     case 32: return launch_w8<32>(*a, st, err, errlen);
@@ -1138,6 +1220,14 @@ extern "C" int bl_gemm_bf16(const blGemmArgs* a, void* stream, char* err, size_t
   }
   if (!a || !a->a || !a->b || (!a->out && !a->partial_out && !a->peer && !a->push) || a->ra < 1 || a->rb < 1 || a->k < 8 || (a->k & 7)) {
     set_err(err, errlen, "barlink: gemm needs non-null operands and K a multiple of 8");
+    return -1;
+  }
+  if (a->i8 && ((a->k & 15) || a->weight_tiled || a->peer || a->push || a->gate_flags || a->partial_out)) {
+    set_err(err, errlen, "barlink: the int8 product needs K a multiple of 16 and plain operands and output");
+    return -1;
+  }
+  if (!a->i8 && (a->feat_scale || a->tok_scale)) {
+    set_err(err, errlen, "barlink: feat_scale / tok_scale belong to the int8 product");
     return -1;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -203,7 +203,7 @@ Layout compute_layout(size_t pool_bytes, int world);
 int sm_count();
 int pick_splits(int tiles, int kblocks, int sms, int want);
 int make_tmap_kmajor(const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
-                     uint32_t esize, CUtensorMap* out, char* err, size_t errlen);
+                     uint32_t esize, CUtensorMap* out, char* err, size_t errlen, uint32_t box_cols = 64);
 
 // symmetric allocator (host only state)
 int64_t arena_alloc(Arena& a, size_t user_bytes, size_t bytes);

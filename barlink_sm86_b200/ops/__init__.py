@@ -258,15 +258,34 @@ def prepare_w8_scales(scale, k):
     return W8GroupScales(row, rel, k // scale.shape[1])
 
 
-def w8a16_linear(x, wq, scale, bias=None, silu_mul=False):
+def w8_act_mode():
+    """How `w8a16_linear` treats the activations by default: "bf16" (weights widened to bf16 in the
+    kernel, the activations as they are: the accurate form) or "int8" (activations quantised per token,
+    int8 x int8 on the tensor cores: the reference kernel's numerics).  Environment BL_W8_ACT."""
+    import os
+    v = os.environ.get("BL_W8_ACT", "bf16")
+    if v not in ("bf16", "int8"):
+        raise ValueError("BL_W8_ACT must be bf16 or int8")
+    return v
+
+
+def w8a16_linear(x, wq, scale, bias=None, silu_mul=False, act=None):
     """scale [n]: per output channel.  scale [n, k/group] or a W8GroupScales: per group, the
     reference's granularity (torch_ext/barlink_sm86/w8a16.cu:119-142 applies group scales inside
     its K loop; so does the tcgen05 kernel here, in the warps that widen the int8 tile).  Group
     sizes that are not multiples of 64, and more than 256 tokens, widen the weight once and run
-    the bf16 GEMM."""
+    the bf16 GEMM.
+
+    act="int8" (per-channel scales only): the activations are quantised per token to int8 first,
+    as the reference does (w8a16.cu:37-92 there), and the product runs as `tcgen05.mma kind::i8`
+    with int32 accumulators: the weights go from HBM to the tensor cores without being widened, for
+    any number of tokens.  act=None takes `w8_act_mode()`."""
     if x.is_cuda:
         k = wq.shape[1]
         gs = scale if isinstance(scale, W8GroupScales) else None
+        if (act or w8_act_mode()) == "int8" and gs is None and scale.dim() == 1 and k % 16 == 0:
+            _count(2)
+            return _C().w8a16_linear(x, wq, scale, bias, silu_mul, act_int8=True)
         if gs is None and scale.dim() == 2:
             if (k // scale.shape[1]) % 64 == 0 and x.shape[0] <= 256:
                 _count()

@@ -228,6 +228,22 @@ def w8a16_linear(x, wq, scale, bias=None, silu_mul=False):
     return y.to(x.dtype)
 
 
+def w8a8_dynamic_linear(x, wq, scale, bias=None, silu_mul=False):
+    """The int8-activation form of `w8a16_linear`: per-token scale amax / 127, activations rounded to
+    int8, exact integer products, result * scale[n] * xs[m] (torch_ext/barlink_sm86/w8a16.cu:37-150
+    of the reference, with per-channel weight scales)."""
+    xf = x.float()
+    xs = (xf.abs().amax(dim=1) / 127.0).clamp_min(1e-12)
+    xq = torch.round(xf / xs[:, None]).clamp(-127, 127)
+    y = (xq.double() @ wq.double().t()).float() * scale.float()[None, :] * xs[:, None]
+    if bias is not None:
+        y = y + bias.float()
+    if silu_mul:
+        g, u = y[..., 0::2], y[..., 1::2]
+        y = torch.nn.functional.silu(g) * u
+    return y.to(x.dtype)
+
+
 def allreduce_rmsnorm(parts, residual, gamma, eps):
     """What the fused kernel computes on every rank, given all ranks' inputs:
     sum in fp32 in rank order, round, add the residual, round, normalise."""

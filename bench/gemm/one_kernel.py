@@ -4,7 +4,7 @@
 target of `ncu` captures (see profiles/).  Weights are larger than L2 or
 rotate, launches are few, memory stays within a few GB.
 
-    python bench/gemm/one_kernel.py gate_up|down_slabs|qkv_slabs|lm_head|w8a16|attn_decode|rmsnorm|attn_prefill|
+    python bench/gemm/one_kernel.py gate_up|down_slabs|qkv_slabs|lm_head|w8a16|w8a16_int8|attn_decode|rmsnorm|attn_prefill|
                                     attn_joint|attn_joint_small|linear_big|dlin_gate_up|dlin_down|rope_attn [reps]
 
 dlin_gate_up / dlin_down: the decode linears of a TP=8 shard with the collective folded in (gather +
@@ -55,6 +55,11 @@ elif which == "w8a16":
     qs = [ref.quantize_w8(torch.randn(2 * I, H, device=dev, generator=g) * 0.02) for _ in range(3)]
     x = bf(B, H)
     fn = lambda i: C.w8a16_linear(x, qs[i % 3][0], qs[i % 3][1])  # noqa: E731
+elif which == "w8a16_int8":
+    # the same weights, activations quantised per token: k_quant_act + the int8 x int8 GEMM
+    qs = [ref.quantize_w8(torch.randn(2 * I, H, device=dev, generator=g) * 0.02) for _ in range(3)]
+    x = bf(B, H)
+    fn = lambda i: C.w8a16_linear(x, qs[i % 3][0], qs[i % 3][1], act_int8=True)  # noqa: E731
 elif which == "attn_decode":
     nq, nkv, hd, bs, ctx = 28, 4, 128, 16, 1024
     nb = B * (ctx // bs)

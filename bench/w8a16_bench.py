@@ -42,7 +42,7 @@ def main():
     dev = torch.device("cuda", 0)
     shapes = [(5120, 5120), (27648 * 2, 5120), (5120, 27648), (7168, 5120), (124160, 5120), (3072, 8704)]
     rows = []
-    for m in (1, 4, 16):
+    for m in (1, 4, 16, 64):
         for n, k in shapes:
             k128 = k // 128 * 128
             copies = max(2, int(300e6 // (n * k128)) + 1)
@@ -52,7 +52,10 @@ def main():
             t_mine = graph_time(lambda i: C.w8a16_linear(x, q[i % copies][0], q[i % copies][1]), copies * 3)
             row = dict(m=m, n=n, k=k128, tcgen05_us=round(t_mine, 1),
                        tcgen05_gbs=round(n * k128 / (t_mine * 1e-6) / 1e9, 1))
-            if R is not None:
+            # activations quantised per token (the reference kernel's numerics): quantise + int8 x int8 product
+            t_i8 = graph_time(lambda i: C.w8a16_linear(x, q[i % copies][0], q[i % copies][1], act_int8=True), copies * 3)
+            row.update(int8_act_us=round(t_i8, 1), int8_act_gbs=round(n * k128 / (t_i8 * 1e-6) / 1e9, 1))
+            if R is not None and m <= 16:
                 prep = []
                 for wq, s in q:
                     wq_t = wq.view(n, k128 // 16, 16).permute(1, 0, 2).contiguous()
@@ -65,7 +68,7 @@ def main():
 
                 t_ref = graph_time(ref_call, copies * 3)
                 row.update(reference_us=round(t_ref, 1), reference_gbs=round(n * k128 / (t_ref * 1e-6) / 1e9, 1),
-                           speedup=round(t_ref / t_mine, 2))
+                           speedup=round(t_ref / t_mine, 2), speedup_int8_act=round(t_ref / t_i8, 2))
             rows.append(row)
             print(row, flush=True)
             del w, q

@@ -32,6 +32,46 @@ def test_w8a16_linear(ext, m, n, k):
     assert rel_l2(got, ref.w8a16_linear(x, wq, scale)) < 1e-2
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 512, 3072), (3, 5120, 5120), (16, 1024, 8704), (64, 27648 // 8 * 2, 5120),
+                                   (64, 5120, 3456), (33, 640, 80), (200, 640, 512), (600, 768, 1024)])
+def test_w8a16_linear_with_int8_activations(ext, m, n, k):
+    """Activations quantised per token, int8 x int8 on the tensor cores (tcgen05.mma kind::i8): equal to
+    the integer arithmetic of the fp32 statement up to the bf16 rounding of the output, and within the
+    reference's tolerance of the unquantised product."""
+    from barlink_sm86_b200.ops import reference as ref
+    wq, scale = _quant(n, k, 11)
+    x = torch.randn(m, k, device="cuda", generator=torch.Generator("cuda").manual_seed(12)).to(torch.bfloat16)
+    got = ext.w8a16_linear(x, wq, scale, act_int8=True)
+    torch.cuda.synchronize()
+    assert ext.w8_error_flag(0) == 0 and ext.gemm_error_flag(0) == 0
+    assert rel_l2(got, ref.w8a8_dynamic_linear(x, wq, scale)) < 5e-3, (m, n, k)
+    want = (x.double() @ wq.double().t()) * scale.double()[None, :]
+    assert rel_l2(got, want) < 2e-2, (m, n, k)
+    x[0, 5] = 9.0   # an outlier sets the token's scale: coarser steps, the same integer arithmetic
+    got = ext.w8a16_linear(x, wq, scale, act_int8=True)
+    assert rel_l2(got, ref.w8a8_dynamic_linear(x, wq, scale)) < 5e-3, (m, n, k)
+
+
+def test_w8a16_int8_activations_epilogues_splits_and_row_pitch(ext):
+    from barlink_sm86_b200.ops import reference as ref
+    m, n, k = 8, 1024, 4096
+    wq, scale = _quant(n, k, 13)
+    wide = torch.randn(m, k + 64, device="cuda", generator=torch.Generator("cuda").manual_seed(14)).to(torch.bfloat16)
+    x = wide[:, :k]   # row pitch larger than k
+    bias = torch.randn(n, device="cuda").to(torch.bfloat16)
+    assert rel_l2(ext.w8a16_linear(x, wq, scale, bias, act_int8=True), ref.w8a8_dynamic_linear(x, wq, scale, bias)) < 5e-3
+    assert rel_l2(ext.w8a16_linear(x, wq, scale, None, True, act_int8=True),
+                  ref.w8a8_dynamic_linear(x, wq, scale, None, True)) < 1e-2
+    a = ext.w8a16_linear(x, wq, scale, None, False, 4, act_int8=True)
+    b = ext.w8a16_linear(x, wq, scale, None, False, 4, act_int8=True)
+    assert torch.equal(a, b)
+    assert rel_l2(a, ref.w8a8_dynamic_linear(x, wq, scale)) < 5e-3
+    # prefill orientation with the SiLU*mul epilogue
+    xp = torch.randn(700, k, device="cuda", generator=torch.Generator("cuda").manual_seed(15)).to(torch.bfloat16)
+    assert rel_l2(ext.w8a16_linear(xp, wq, scale, bias, True, act_int8=True),
+                  ref.w8a8_dynamic_linear(xp, wq, scale, bias, True)) < 1e-2
+
+
 def test_w8a16_linear_epilogues_and_splits(ext):
     from barlink_sm86_b200.ops import reference as ref
     m, n, k = 8, 1024, 4096
