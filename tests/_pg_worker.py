@@ -324,11 +324,23 @@ for T, n, k, split in ((1024, 512, 256, 384), (world * 320, 768, 192, 0), (2304,
     for it in range(3):   # consecutive calls alternate between the two staging buffers
         got = comm.row_parallel(torch.empty(T, n, dtype=torch.bfloat16, device=dev), parts)
         torch.cuda.synchronize()
-        assert torch.equal(got, want), ("pushed all-reduce differs from GEMM + all_reduce", T, n, k, it,
-                                        (got.float() - want.float()).abs().max().item())
+        diff = (got.float() - want.float()).abs()
+        if world == 2 and not info["multicast"]:
+            # two addends: the sum does not depend on the order, so the two paths agree bit for bit
+            assert torch.equal(got, want), ("pushed all-reduce differs from GEMM + all_reduce", T, n, k, it, diff.max().item())
+        else:
+            # more ranks (or the switch adds): the fp32 sums may be taken in another order, which can move
+            # a result by one bf16 step
+            ulp = torch.maximum(got.float().abs(), want.float().abs()) * 2.0 ** -7
+            assert bool((diff <= ulp).all()), ("pushed all-reduce differs from GEMM + all_reduce by more than one bf16 step",
+                                               T, n, k, it, diff.max().item())
+        if it == 0:
+            first_got = got.clone()
+        else:
+            assert torch.equal(got, first_got), ("pushed all-reduce is not repeatable", T, n, k, it)
     assert bl.stats()["ops"] == calls + 3, "the pushed path did not run"
 assert bl.status()["code"] == 0 and C.gemm_error_flag(rank) == 0
-log("row-parallel linear with pushed all-reduce ok (bit-equal to GEMM + all_reduce)")
+log("row-parallel linear with pushed all-reduce ok (against GEMM + all_reduce; repeatable)")
 
 # ---- CUDA graph capture and replay ----------------------------------------------------------
 x = torch.zeros(5120, dtype=torch.bfloat16, device=dev)

@@ -117,3 +117,29 @@ def test_folded_collective_decode_path_matches_default(ext, monkeypatch):
     # greedy tokens of a random-init model are near ties now and then: allow a late divergence
     agree = (want == got).float().mean().item()
     assert torch.equal(want[:3], got[:3]) and agree > 0.9, (agree, want, got)
+
+
+def test_w8a16_model_with_int8_activations_tracks_the_widening_form(ext, monkeypatch):
+    """The int8-quantised decoder with its linears run as int8 x int8 (activations quantised per token,
+    the reference kernel's numerics) against the same model with the weights widened to bf16: prefill
+    (token-major tiles) and one decode step (weights on the 128-row side) agree to a few percent and
+    pick the same tokens almost everywhere."""
+    from barlink_sm86_b200.models import DecodeEngine, Qwen2Model
+    from barlink_sm86_b200.parallel import TPComm
+    cfg = _cfg()
+    B, S = 4, 320
+    ids = torch.randint(0, cfg.vocab, (B, S + 1), generator=torch.Generator().manual_seed(5), dtype=torch.int32).cuda()
+    out = {}
+    for act in ("bf16", "int8"):
+        monkeypatch.setenv("BL_W8_ACT", act)
+        m = Qwen2Model(cfg, TPComm.single(), "cuda:0", torch.bfloat16, seed=6, quant="w8a16")
+        eng = DecodeEngine(m, B, S + 8, use_graph=False)
+        pre = m.logits(m.prefill(ids[:, :S].contiguous())).view(B, S, -1)[:, -1].float()
+        eng.prefill(ids[:, :S].contiguous())
+        step = m.logits(m.decode_hidden(ids[:, S].contiguous(), eng.positions, eng.slots, eng.ctx_lens, eng.cache)).float()
+        torch.cuda.synchronize()
+        out[act] = (pre, step)
+    assert ext.gemm_error_flag(0) == 0 and ext.w8_error_flag(0) == 0
+    for a, b in zip(out["bf16"], out["int8"]):
+        assert rel_l2(b, a) < 8e-2
+        assert torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0) > 0.995
