@@ -1,3 +1,6 @@
+#ifndef _GNU_SOURCE
+#define _GNU_SOURCE  // struct ucred
+#endif
 // SPDX-License-Identifier: MIT
 //
 // Host side of the symmetric heap: driver entry points, arena layout,
@@ -657,6 +660,16 @@ extern "C" int bl_init_peer(blCtx** out, int device, size_t poolBytes, const cha
         return fail();
       }
       set_sock_timeout(c, tmo);
+      {
+        // memory handles go only to processes of the same user
+        struct ucred cred;
+        socklen_t clen = sizeof(cred);
+        if (getsockopt(c, SOL_SOCKET, SO_PEERCRED, &cred, &clen) != 0 || cred.uid != geteuid()) {
+          set_err(err, errlen, "barlink: a process of another user connected to %s; refused", sockPath);
+          close(c);
+          return fail();
+        }
+      }
       Hello h;
       int fd = -1;
       if (recv_fds(c, &fd, 1, &h, sizeof(h)) != 0 || h.magic != kMagic) {

@@ -28,8 +28,11 @@ from ..parallel.plan import gather_head_cols, gather_heads
 
 
 # BL_DLIN when the environment does not set it: "auto" = the folded-collective decode path whenever
-# there is more than one rank, "0" = the k-split GEMM + all-reduce kernel path
-DLIN_DEFAULT = "0"
+# there is more than one rank, "0" = the k-split GEMM + all-reduce kernel path, "tuned" = the folded
+# path at the tensor-parallel degrees where it measured faster on B200s (7B shape, batch 64:
+# 4 ranks 2.73 against 2.81 ms per step; slower at 1, 2 and 8 ranks: 4.93 / 4.26, 3.87 / 3.41, 2.65 / 2.53)
+DLIN_DEFAULT = "tuned"
+DLIN_TUNED_WORLDS = (4,)
 
 
 @dataclass
@@ -403,8 +406,11 @@ class Qwen2Model:
         if tokens > 64 or self.cfg.hidden % 8 or self.cfg.hidden > 8192 or self.w.tiled:
             return False
         if c.world > 1 and c.no_comm:
-            return mode != "0"  # timing control: same kernels, inboxes in local memory, nothing crosses NVLink
+            # timing control: same kernels, inboxes in local memory, nothing crosses NVLink
+            return mode != "tuned" or c.world in DLIN_TUNED_WORLDS
         if c.world > 1:
+            if mode == "tuned" and c.world not in DLIN_TUNED_WORLDS:
+                return False
             return bool(c.use_link) and tokens * self.cfg.hidden * 2 <= c.oneshot_max
         return mode == "1"
 

@@ -63,7 +63,14 @@ def _agree_socket_path(store, rank):
     key = "barlink/sock"
     if rank == 0:
         tag = os.environ.get("BL_PG_ID") or "%d" % os.getpid()
-        path = os.path.join(tempfile.gettempdir(), "barlink-pg-%d-%s.sock" % (os.getuid(), tag))
+        # a directory only this user can enter, so that nobody else can put a socket of that name there
+        # (rank 0 also checks the uid of every process that connects)
+        d = tempfile.mkdtemp(prefix="barlink-pg-%d-" % os.getuid())
+        os.chmod(d, 0o700)
+        import atexit
+        import shutil
+        atexit.register(shutil.rmtree, d, True)
+        path = os.path.join(d, "%s.sock" % tag)
         store.set(key, path)
         return path
     return store.get(key).decode()

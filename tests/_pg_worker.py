@@ -331,7 +331,8 @@ for T, n, k, split in ((1024, 512, 256, 384), (world * 320, 768, 192, 0), (2304,
         else:
             # more ranks (or the switch adds): the fp32 sums may be taken in another order, which can move
             # a result by one bf16 step
-            ulp = torch.maximum(got.float().abs(), want.float().abs()) * 2.0 ** -7
+            # (the in-switch reduction of the comparison path adds in bf16 steps of its own: allow four there)
+            ulp = torch.maximum(got.float().abs(), want.float().abs()) * 2.0 ** -7 * (4 if info["multicast"] else 1)
             assert bool((diff <= ulp).all()), ("pushed all-reduce differs from GEMM + all_reduce by more than one bf16 step",
                                                T, n, k, it, diff.max().item())
         if it == 0:
