@@ -320,10 +320,10 @@ for T, n, k, split in ((1024, 512, 256, 384), (world * 320, 768, 192, 0), (2304,
     os.environ["BL_PUSH_AR"] = "0"
     want = comm.row_parallel(torch.empty(T, n, dtype=torch.bfloat16, device=dev), parts).clone()
     # the statement of the operation: every rank's bf16 product, summed in fp32 in rank order, rounded once
-    from barlink_sm86_b200 import ops as _ops  # noqa: E402
     mine = torch.empty(T, n, dtype=torch.bfloat16, device=dev)
     for x_, w_, b_, r_, gelu_, row0_ in parts:
-        _ops.linear(x_, w_, b_, residual=r_, gelu=gelu_, out=mine[row0_:row0_ + x_.shape[0]])
+        # no k-split: the pushed GEMM has none either, and a k-split sums the products in another order
+        C.linear(x_, w_, b_, r_, False, mine[row0_:row0_ + x_.shape[0]], splits=1, gelu=gelu_)
     every = torch.empty(world, T, n, dtype=torch.bfloat16, device=dev)
     dist.all_gather_into_tensor(every.view(-1), mine.view(-1))
     acc = torch.zeros(T, n, dtype=torch.float32, device=dev)
@@ -332,8 +332,8 @@ for T, n, k, split in ((1024, 512, 256, 384), (world * 320, 768, 192, 0), (2304,
     truth = acc.to(torch.bfloat16)
     step = torch.maximum(truth.float().abs(), want.float().abs()) * 2.0 ** -7
     off = (want.float() - truth.float()).abs()
-    # the plain path may add in another order (or in the switch): within one bf16 step, four with the switch
-    assert bool((off <= step * (4 if info["multicast"] else 1)).all()), ("GEMM + all_reduce is off", T, n, k, off.max().item())
+    # the plain path may k-split its GEMMs and add in another order (or in the switch): a few bf16 steps
+    assert bool((off <= step * 4).all()), ("GEMM + all_reduce is off", T, n, k, off.max().item())
     os.environ["BL_PUSH_AR"] = "1"
     calls = bl.stats()["ops"]
     for it in range(3):   # consecutive calls alternate between the two staging buffers
