@@ -195,7 +195,8 @@ std::tuple<at::Tensor, at::Tensor> w8_group_scales(const at::Tensor& scales) {
 
 at::Tensor w8a16_linear(const at::Tensor& x, const at::Tensor& wq, const at::Tensor& scale,
                         const c10::optional<at::Tensor>& bias, bool silu_mul, int splits,
-                        const c10::optional<at::Tensor>& group_rel, bool act_int8) {
+                        const c10::optional<at::Tensor>& group_rel, bool act_int8,
+                        const c10::optional<at::Tensor>& group_scale) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1,
               "barlink: x must be a 2-D bfloat16 CUDA tensor with unit inner stride");
   TORCH_CHECK(wq.is_cuda() && wq.is_contiguous() && wq.scalar_type() == at::kChar && wq.dim() == 2 &&
@@ -203,7 +204,14 @@ at::Tensor w8a16_linear(const at::Tensor& x, const at::Tensor& wq, const at::Ten
               "barlink: wq must be a contiguous int8 [n, k] CUDA tensor with k = x.shape[1]");
   check_bf16x(scale, "scale");
   const int m = int(x.size(0)), k = int(x.size(1)), n = int(wq.size(0));
-  TORCH_CHECK(scale.numel() == n, "barlink: scale must have one entry per output channel");
+  TORCH_CHECK(group_scale || scale.numel() == n, "barlink: scale must have one entry per output channel");
+  if (group_scale) {
+    TORCH_CHECK(act_int8 && m <= 64, "barlink: group_scale goes with act_int8 and at most 64 tokens");
+    TORCH_CHECK(group_scale->is_cuda() && group_scale->is_contiguous() && group_scale->scalar_type() == at::kBFloat16 &&
+                    group_scale->dim() == 2 && group_scale->size(0) == n && k % group_scale->size(1) == 0 &&
+                    (k / group_scale->size(1)) % 128 == 0,
+                "barlink: group_scale must be contiguous bfloat16 [n, k / group] with a group size that is a multiple of 128");
+  }
   const int dev = x.device().index();
   c10::cuda::CUDAGuard guard(x.device());
   void* st = at::cuda::getCurrentCUDAStream(dev).stream();
@@ -240,6 +248,10 @@ at::Tensor w8a16_linear(const at::Tensor& x, const at::Tensor& wq, const at::Ten
       a.n = n;
       a.k = k;
       a.scale = scale.data_ptr();
+      if (group_scale) {
+        a.group_scale = group_scale->data_ptr();
+        a.group_k = k / int(group_scale->size(1));
+      }
       a.bias = bias ? bias->data_ptr() : nullptr;
       a.out = out.data_ptr();
       a.ldo = silu_mul ? n / 2 : n;
@@ -648,7 +660,7 @@ void bind_extra(py::module_& m) {
         py::arg("rows_per_batch"));
   m.def("w8a16_linear", &w8a16_linear, py::arg("x"), py::arg("wq"), py::arg("scale"),
         py::arg("bias") = py::none(), py::arg("silu_mul") = false, py::arg("splits") = 0,
-        py::arg("group_rel") = py::none(), py::arg("act_int8") = false);
+        py::arg("group_rel") = py::none(), py::arg("act_int8") = false, py::arg("group_scale") = py::none());
   m.def("w8_group_scales", &w8_group_scales, py::arg("scales"));
   m.def("w8_error_flag", &w8_error_flag, py::arg("device") = 0);
   m.def("dlin", &dlin, py::arg("x"), py::arg("weight"), py::arg("pro") = "none", py::arg("epi") = "store",

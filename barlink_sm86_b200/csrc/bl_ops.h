@@ -103,6 +103,11 @@ typedef struct blGemmArgs {
   int i8;
   const void* feat_scale; /* bf16 per output feature, or null */
   const void* tok_scale;  /* fp32 per token, or null */
+  /* i8 with one weight scale per (feature, k-group) instead of feat_scale: bf16 [ra][k / group_k], group_k a
+   * multiple of 128.  Weights-first orientation (swap) and at most 64 tokens only: every k-block gets an
+   * accumulator of its own and the epilogue warps add acc * scale, k-block by k-block; no k-split. */
+  const void* group_scale;
+  int group_k;
 } blGemmArgs;
 int bl_gemm_bf16(const blGemmArgs* a, void* stream, char* err, size_t errlen);
 /* Weights in 16 KiB tiles [ceil(n/128)][ceil(k/64)][128 x 128 B], each tile in the
@@ -150,6 +155,9 @@ typedef struct blW8A16Args {
    * ignored, group_rel must be null and partial_out is not supported. */
   const void* xq;
   const void* xs;
+  /* with xq: per-group weight scales bf16 [n][k / group_k] (the reference's checkpoint format, group 128)
+   * instead of `scale`; at most 64 tokens, group_k a multiple of 128 */
+  const void* group_scale;
 } blW8A16Args;
 /* scales bf16 [n][groups] -> row_max bf16 [n] and rel fp16 [n][groups] = scale / row_max */
 int bl_w8_group_scales(const void* scales, int n, int groups, void* row_max, void* rel, void* stream, char* err,

@@ -41,7 +41,11 @@ struct GemmShape {
   int kblocks;              // ceil(k/64)
   int splits;               // k-splits per tile
   int ab_fmt;               // 1 = bf16, 0 = fp16
-  int i8;                   // 1: both operands are signed 8-bit, a k-block is 128 elements, int32 accumulators
+  int i8;                   // 1: both operands are signed 8-bit, a k-block is 128 elements, int32 accumulators;
+                            // 2: the same with one weight scale per (A row, k-group): every k-block is multiplied
+                            //    into an accumulator of its own (the two TMEM buffers alternate) and the epilogue
+                            //    warps add acc * scale into fp32 registers, k-block by k-block (BN <= 64, no k-split)
+  const __nv_bfloat16* gscale_bf;  // i8 == 2: [ra][gs_groups], gs_kblocks k-blocks of 128 per group
   int direct;               // 1: every k-split hands its raw partial tile to the Sink (no in-kernel reduce)
   int weights_in_a;         // operand that no earlier kernel writes: 1 = A, 0 = B, 2 = neither
   float* ws;                // [tiles*splits][BN][128] fp32 partials (splits > 1)
@@ -342,22 +346,37 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
       uint32_t phase = 0, aphase = 0;
       uint32_t tphase[2] = {0, 0};
       int it = 0;
+      int gcount = 0;  // grouped int8: k-blocks issued so far (selects the accumulator buffer)
+      const bool grouped = !W8 && g.i8 == 2;
       bool ok = true;
       for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++it) {
         const int tile = u / g.splits, sp = u - tile * g.splits;
         const int kb0 = sp * kb_per;
         const int kb1 = min(g.kblocks, kb0 + kb_per);
-        const int acc = it & 1;
-        if (!mbar_wait_bounded(&tempty_bar[acc], tphase[acc] ^ 1u, s_abort)) break;
-        tphase[acc] ^= 1u;
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
+        int acc = it & 1;
+        if (!grouped) {
+          if (!mbar_wait_bounded(&tempty_bar[acc], tphase[acc] ^ 1u, s_abort)) break;
+          tphase[acc] ^= 1u;
+          tc_fence_after_sync();
+        }
+        uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
         for (int kb = kb0; kb < kb1 && ok; kb += S::kKS) {
           const int nsub = min(S::kKS, kb1 - kb);
           const uint32_t sa = ring + stage * S::kStageBytes;
           if (!W8 && !mbar_wait_bounded(&full_bar[stage], phase, s_abort)) {
             ok = false;
             break;
+          }
+          if (grouped) {
+            // an accumulator per k-block: wait until the epilogue warps have drained this buffer
+            acc = gcount & 1;
+            if (!mbar_wait_bounded(&tempty_bar[acc], tphase[acc] ^ 1u, s_abort)) {
+              ok = false;
+              break;
+            }
+            tphase[acc] ^= 1u;
+            tc_fence_after_sync();
+            d_tmem = tmem_base + uint32_t(acc * BN);
           }
 #pragma unroll
           for (int sb = 0; sb < S::kKS; ++sb) {
@@ -377,7 +396,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
               // +32 bytes along K inside the swizzle atom = +2 in the address field
               if (!W8 && g.i8)
                 umma_i8_ss(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), idesc,
-                           (kb + sb > kb0 || k > 0) ? 1u : 0u);
+                           ((!grouped && kb + sb > kb0) || k > 0) ? 1u : 0u);
               else
                 umma_f16_ss(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), idesc,
                             (kb + sb > kb0 || k > 0) ? 1u : 0u);
@@ -392,12 +411,16 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
           }
           if (!ok) break;
           umma_commit(&empty_bar[stage]);
+          if (grouped) {
+            umma_commit(&tfull_bar[acc]);
+            ++gcount;
+          }
           if (++stage == S::kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) umma_commit(&tfull_bar[acc]);
+        if (ok && !grouped) umma_commit(&tfull_bar[acc]);
       }
     }
   } else if (W8 && warp >= 6) {
@@ -490,10 +513,62 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
     const bool i8 = !W8 && g.i8;
     uint32_t tphase[2] = {0, 0};
     int it = 0;
+    int gcount = 0;  // grouped int8: k-blocks drained so far
     pdl_wait();  // outputs, residuals and the split-K scratch belong to earlier kernels until now
     for (int u = blockIdx.x; u < units; u += gridDim.x, ++it) {
       const int tile = u / g.splits, sp = u - tile * g.splits;
       const int ta = tile / g.tiles_b, tb = tile - ta * g.tiles_b;
+      if constexpr (!W8 && BN <= 64) {
+        if (g.i8 == 2) {
+          // one accumulator per k-block: acc * scale[row][group] summed in registers
+          const int kb0 = sp * kb_per, kb1 = min(g.kblocks, kb0 + kb_per);
+          const int grow = ta * kTileA + row;
+          const __nv_bfloat16* gs = grow < g.ra ? g.gscale_bf + size_t(grow) * g.gs_groups : nullptr;
+          float accf[BN];
+#pragma unroll
+          for (int i = 0; i < BN; ++i) accf[i] = 0.f;
+          bool ok = true;
+          for (int kb = kb0; kb < kb1; ++kb, ++gcount) {
+            const int gb = gcount & 1;
+            const float sc = gs ? __bfloat162float(gs[kb / g.gs_kblocks]) : 0.f;
+            if (!mbar_wait_bounded(&tfull_bar[gb], tphase[gb], s_abort)) {
+              ok = false;
+              break;
+            }
+            tphase[gb] ^= 1u;
+            tc_fence_after_sync();
+            const uint32_t ta2 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(gb * BN);
+            if constexpr (BN >= 32) {
+#pragma unroll
+              for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32(ta2 + c0, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) accf[c0 + i] = fmaf(float(int32_t(r[i])), sc, accf[c0 + i]);
+              }
+            } else {
+              uint32_t r[16];
+              tmem_ld_32x16(ta2, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) accf[i] = fmaf(float(int32_t(r[i])), sc, accf[i]);
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&tempty_bar[gb]);
+          }
+          if (!ok) break;
+#pragma unroll
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = (c0 + i < BN) ? accf[(c0 + i) < BN ? (c0 + i) : 0] : 0.f;
+            sink(ta, tb, sp, row, c0, v, BN < 32 ? BN : 32);
+          }
+          sink.unit_done(et);
+          continue;
+        }
+      }
       const int acc = it & 1;
       if (!mbar_wait_bounded(&tfull_bar[acc], tphase[acc], s_abort)) break;
       tphase[acc] ^= 1u;

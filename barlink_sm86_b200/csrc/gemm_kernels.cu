@@ -487,13 +487,20 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
   g.tiles_b = (a.rb + BN - 1) / BN;
   g.kblocks = (a.k + int(box_cols) - 1) / int(box_cols);
   g.i8 = a.i8 ? 1 : 0;
+  g.gscale_bf = nullptr;
+  if (a.i8 && a.group_scale) {
+    g.i8 = 2;
+    g.gscale_bf = static_cast<const __nv_bfloat16*>(a.group_scale);
+    g.gs_groups = (a.k + a.group_k - 1) / a.group_k;
+    g.gs_kblocks = a.group_k / int(box_cols);
+  }
   const int tiles = g.tiles_a * g.tiles_b;
   const int sms = sm_count();
   // CTAs launched at most (BL_GEMM_WAVE: percent of the resident slots)
   static const int wave = env_int_or("BL_GEMM_WAVE", 100);
   int slots = sms * S::kCtasPerSm * wave / 100;
   if (slots < 1) slots = 1;
-  g.splits = pick_splits(tiles, g.kblocks, slots, splits_want);
+  g.splits = g.i8 == 2 ? 1 : pick_splits(tiles, g.kblocks, slots, splits_want);
   const bool partial = a.partial_out != nullptr || a.peer != nullptr;
   if (partial) {
     if (a.partial_splits < 1 || g.splits > a.partial_splits) g.splits = a.partial_splits;
@@ -522,8 +529,10 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
   g.gate_timeout_ns = a.gate_timeout_ns ? a.gate_timeout_ns : 2000000000ull;
   g.ab_fmt = 1;
   g.gscale = nullptr;
-  g.gs_groups = 0;
-  g.gs_kblocks = 1;
+  if (g.i8 != 2) {
+    g.gs_groups = 0;
+    g.gs_kblocks = 1;
+  }
   g.weights_in_a = a.dynamic_weights ? 2 : (a.swap ? 1 : 0);
   g.ws = static_cast<float*>(a.ws);
   g.counters = static_cast<uint32_t*>(a.counters);
@@ -1071,7 +1080,7 @@ static int launch_gemm_pair(const blGemmArgs& a, cudaStream_t st, char* err, siz
 using namespace bl;
 
 extern "C" int bl_w8a16_linear(const blW8A16Args* a, void* stream, char* err, size_t errlen) {
-  if (!a || (!a->x && !a->xq) || !a->wq || !a->scale || (!a->out && !a->partial_out) || a->m < 1 || a->n < 1 ||
+  if (!a || (!a->x && !a->xq) || !a->wq || (!a->scale && !a->group_scale) || (!a->out && !a->partial_out) || a->m < 1 || a->n < 1 ||
       a->k < 16 || (a->k & 15)) {
     set_err(err, errlen, "barlink: w8a16_linear needs x, wq, scale, an output, and K a multiple of 16");
     return -1;
@@ -1090,7 +1099,7 @@ extern "C" int bl_w8a16_linear(const blW8A16Args* a, void* stream, char* err, si
   if (a->xq) {
     // int8 activations: the weights go from HBM to the tensor cores as they are
     if (!a->xs || a->group_rel || a->partial_out) {
-      set_err(err, errlen, "barlink: int8 activations need their per-token scales, per-channel weight scales and a plain output");
+      set_err(err, errlen, "barlink: int8 activations need their per-token scales and a plain output (group scales: group_scale)");
       return -1;
     }
     blGemmArgs g;
@@ -1108,7 +1117,12 @@ extern "C" int bl_w8a16_linear(const blW8A16Args* a, void* stream, char* err, si
     g.counters = a->counters; g.n_counters = a->n_counters;
     g.err_flag = a->err_flag;
     g.i8 = 1;
-    g.feat_scale = a->scale;
+    if (a->group_scale) {
+      g.group_scale = a->group_scale;
+      g.group_k = a->group_k;
+    } else {
+      g.feat_scale = a->scale;
+    }
     g.tok_scale = a->xs;
     return bl_gemm_bf16(&g, stream, err, errlen);
   }
@@ -1224,6 +1238,11 @@ extern "C" int bl_gemm_bf16(const blGemmArgs* a, void* stream, char* err, size_t
   }
   if (a->i8 && ((a->k & 15) || a->weight_tiled || a->peer || a->push || a->gate_flags || a->partial_out)) {
     set_err(err, errlen, "barlink: the int8 product needs K a multiple of 16 and plain operands and output");
+    return -1;
+  }
+  if (a->group_scale && (!a->i8 || !a->swap || a->rb > 64 || a->group_k < 128 || (a->group_k & 127) || a->feat_scale ||
+                         (a->bn > 64))) {
+    set_err(err, errlen, "barlink: per-group scales go with the int8 product, weights first, at most 64 tokens, groups of a multiple of 128");
     return -1;
   }
   if (!a->i8 && (a->feat_scale || a->tok_scale)) {

@@ -279,13 +279,21 @@ def w8a16_linear(x, wq, scale, bias=None, silu_mul=False, act=None):
     act="int8" (per-channel scales only): the activations are quantised per token to int8 first,
     as the reference does (w8a16.cu:37-92 there), and the product runs as `tcgen05.mma kind::i8`
     with int32 accumulators: the weights go from HBM to the tensor cores without being widened, for
-    any number of tokens.  act=None takes `w8_act_mode()`."""
+    any number of tokens; with group scales [n, k/group] (group a multiple of 128, at most 64 tokens)
+    every k-block is accumulated on its own and the epilogue warps apply the scales.  act=None takes
+    `w8_act_mode()`."""
     if x.is_cuda:
         k = wq.shape[1]
         gs = scale if isinstance(scale, W8GroupScales) else None
-        if (act or w8_act_mode()) == "int8" and gs is None and scale.dim() == 1 and k % 16 == 0:
-            _count(2)
-            return _C().w8a16_linear(x, wq, scale, bias, silu_mul, act_int8=True)
+        if (act or w8_act_mode()) == "int8" and gs is None and k % 16 == 0:
+            if scale.dim() == 1:
+                _count(2)
+                return _C().w8a16_linear(x, wq, scale, bias, silu_mul, act_int8=True)
+            if x.shape[0] <= 64 and (k // scale.shape[1]) % 128 == 0:
+                # group scales (the reference's checkpoint format): one accumulator per k-block,
+                # scaled and summed by the epilogue warps
+                _count(2)
+                return _C().w8a16_linear(x, wq, scale, bias, silu_mul, act_int8=True, group_scale=scale.contiguous())
         if gs is None and scale.dim() == 2:
             if (k // scale.shape[1]) % 64 == 0 and x.shape[0] <= 256:
                 _count()

@@ -235,7 +235,14 @@ def w8a8_dynamic_linear(x, wq, scale, bias=None, silu_mul=False):
     xf = x.float()
     xs = (xf.abs().amax(dim=1) / 127.0).clamp_min(1e-12)
     xq = torch.round(xf / xs[:, None]).clamp(-127, 127)
-    y = (xq.double() @ wq.double().t()).float() * scale.float()[None, :] * xs[:, None]
+    if scale.dim() == 2:
+        # per-group weight scales: integer sums per group, scaled and added in fp32 (w8a16.cu:119-142 there)
+        n, groups = scale.shape
+        gk = wq.shape[1] // groups
+        part = torch.einsum("mgk,ngk->mng", xq.double().view(-1, groups, gk), wq.double().view(n, groups, gk))
+        y = (part * scale.double()[None, :, :]).sum(-1).float() * xs[:, None]
+    else:
+        y = (xq.double() @ wq.double().t()).float() * scale.float()[None, :] * xs[:, None]
     if bias is not None:
         y = y + bias.float()
     if silu_mul:

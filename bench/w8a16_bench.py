@@ -55,6 +55,11 @@ def main():
             # activations quantised per token (the reference kernel's numerics): quantise + int8 x int8 product
             t_i8 = graph_time(lambda i: C.w8a16_linear(x, q[i % copies][0], q[i % copies][1], act_int8=True), copies * 3)
             row.update(int8_act_us=round(t_i8, 1), int8_act_gbs=round(n * k128 / (t_i8 * 1e-6) / 1e9, 1))
+            # the same with group-128 weight scales (the reference's format)
+            qg = [ref.quantize_w8_grouped(t, 128) for t in w]
+            t_g = graph_time(lambda i: C.w8a16_linear(x, qg[i % copies][0], qg[i % copies][1], act_int8=True,
+                                                      group_scale=qg[i % copies][1]), copies * 3)
+            row.update(int8_act_group128_us=round(t_g, 1), int8_act_group128_gbs=round(n * k128 / (t_g * 1e-6) / 1e9, 1))
             if R is not None and m <= 16:
                 prep = []
                 for wq, s in q:

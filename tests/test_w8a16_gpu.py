@@ -52,6 +52,31 @@ def test_w8a16_linear_with_int8_activations(ext, m, n, k):
     assert rel_l2(got, ref.w8a8_dynamic_linear(x, wq, scale)) < 5e-3, (m, n, k)
 
 
+@pytest.mark.parametrize("m,n,k,group", [(1, 512, 3072, 128), (5, 5120, 5120, 128), (16, 1024, 8704, 128),
+                                         (64, 6912, 5120, 128), (33, 640, 1024, 256), (64, 300, 384, 128)])
+def test_w8a16_int8_activations_with_group_scales(ext, m, n, k, group):
+    """Group-128 weight scales (the reference's checkpoint format) with int8 activations: every k-block of
+    128 is multiplied into an accumulator of its own and the epilogue warps add acc * scale[row][group]."""
+    from barlink_sm86_b200.ops import reference as ref
+    g = torch.Generator(device="cuda").manual_seed(21)
+    w = torch.randn(n, k, device="cuda", generator=g) * 0.02
+    w[:, : k // 2] *= 4.0   # groups of different magnitude: the scales matter
+    wq, scale = ref.quantize_w8_grouped(w, group)
+    x = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+    bias = torch.randn(n, device="cuda", generator=g).to(torch.bfloat16)
+    got = ext.w8a16_linear(x, wq, scale, bias, act_int8=True, group_scale=scale)
+    torch.cuda.synchronize()
+    assert ext.gemm_error_flag(0) == 0
+    assert rel_l2(got, ref.w8a8_dynamic_linear(x, wq, scale, bias)) < 5e-3, (m, n, k)
+    want = x.double() @ ref.w8_dequant(wq, scale).double().t() + bias.double()
+    assert rel_l2(got, want) < 2e-2, (m, n, k)
+    if n % 2 == 0:
+        got = ext.w8a16_linear(x, wq, scale, None, True, act_int8=True, group_scale=scale)
+        assert rel_l2(got, ref.w8a8_dynamic_linear(x, wq, scale, None, True)) < 1e-2
+    again = ext.w8a16_linear(x, wq, scale, bias, act_int8=True, group_scale=scale)
+    assert torch.equal(again, ext.w8a16_linear(x, wq, scale, bias, act_int8=True, group_scale=scale))
+
+
 def test_w8a16_int8_activations_epilogues_splits_and_row_pitch(ext):
     from barlink_sm86_b200.ops import reference as ref
     m, n, k = 8, 1024, 4096
