@@ -289,7 +289,8 @@ def w8a16_linear(x, wq, scale, bias=None, silu_mul=False, act=None):
             if scale.dim() == 1:
                 _count(2)
                 return _C().w8a16_linear(x, wq, scale, bias, silu_mul, act_int8=True)
-            if x.shape[0] <= 64 and (k // scale.shape[1]) % 128 == 0:
+            # (no k-split in that form: it pays from one 128-row tile per SM upwards; below, the widening form)
+            if x.shape[0] <= 64 and (k // scale.shape[1]) % 128 == 0 and wq.shape[0] >= 148 * 128:
                 # group scales (the reference's checkpoint format): one accumulator per k-block,
                 # scaled and summed by the epilogue warps
                 _count(2)
