@@ -330,10 +330,11 @@ for T, n, k, split in ((1024, 512, 256, 384), (world * 320, 768, 192, 0), (2304,
     for r_ in range(world):
         acc += every[r_].float()
     truth = acc.to(torch.bfloat16)
-    step = torch.maximum(truth.float().abs(), want.float().abs()) * 2.0 ** -7
+    # the plain path may k-split its GEMMs (each rank's bf16 product can then differ by one step of ITS
+    # magnitude, which matters where the ranks' values cancel) and add in another order or in the switch
+    step = torch.maximum(every.float().abs().amax(0), truth.float().abs()) * 2.0 ** -7
     off = (want.float() - truth.float()).abs()
-    # the plain path may k-split its GEMMs and add in another order (or in the switch): a few bf16 steps
-    assert bool((off <= step * 4).all()), ("GEMM + all_reduce is off", T, n, k, off.max().item())
+    assert bool((off <= step * (world + 2)).all()), ("GEMM + all_reduce is off", T, n, k, off.max().item())
     os.environ["BL_PUSH_AR"] = "1"
     calls = bl.stats()["ops"]
     for it in range(3):   # consecutive calls alternate between the two staging buffers
