@@ -52,3 +52,22 @@ def test_barlink_w8a16_method_registers_and_matches_fp32():
     # own interpreter: importing vLLM's model executor is heavy and leaves global state behind
     p = subprocess.run([sys.executable, "-c", SCRIPT % ROOT], capture_output=True, text=True, timeout=600)
     assert p.returncode == 0 and "QUANT OK" in p.stdout, p.stdout[-1500:] + p.stderr[-3000:]
+
+
+def test_quantization_config_pickles_by_reference():
+    """vLLM starts its engine and worker processes with `spawn` once CUDA is initialised and pickles the
+    configuration for them: the method's classes must travel by reference (classes defined inside a function
+    would be pickled by value, together with `torch.ops`, which cannot be)."""
+    import pickle
+
+    pytest.importorskip("vllm")
+    cloudpickle = pytest.importorskip("cloudpickle")
+    from vllm_barlink import quant
+
+    quant.register()
+    cfg = quant.register.config_cls()
+    for obj in (cfg, quant.register.config_cls, quant.register.method_cls()):
+        blob = cloudpickle.dumps(obj)
+        assert len(blob) < 4096          # a reference, not the class body
+        back = pickle.loads(blob)
+        assert (back if isinstance(back, type) else type(back)).__module__ == "vllm_barlink._quant_classes"

@@ -67,64 +67,16 @@ def quantize_channelwise(w):
 
 
 def register():
-    """Make quantization="barlink_w8a16" known to vLLM (idempotent)."""
+    """Make quantization="barlink_w8a16" known to vLLM (idempotent).  The classes live at the top level of
+    `vllm_barlink._quant_classes` (imported here, because it needs vLLM) so that vLLM can pickle a config that
+    carries them by reference when it starts its engine and worker processes with `spawn`."""
     global _registered
     if _registered:
         return NAME
-    from vllm.model_executor.layers.linear import LinearBase, LinearMethodBase, UnquantizedLinearMethod
-    from vllm.model_executor.layers.quantization import register_quantization_config
-    from vllm.model_executor.layers.quantization.base_config import QuantizationConfig
-
     _define_op()
+    from . import _quant_classes as qc
 
-    class BarlinkW8A16LinearMethod(LinearMethodBase):
-        def __init__(self):
-            self._plain = UnquantizedLinearMethod()
-
-        def create_weights(self, layer, input_size_per_partition, output_partition_sizes, input_size, output_size,
-                           params_dtype, **extra_weight_attrs):
-            # same parameter as an unquantised layer: every loader keeps working
-            self._plain.create_weights(layer, input_size_per_partition, output_partition_sizes, input_size,
-                                       output_size, params_dtype, **extra_weight_attrs)
-
-        def process_weights_after_loading(self, layer):
-            wq, scale = quantize_channelwise(layer.weight.data)
-            layer.register_buffer("bl_wq", wq, persistent=False)
-            layer.register_buffer("bl_scale", scale, persistent=False)
-            # keep an empty parameter under the old name so that code that only inspects it keeps working
-            layer.weight = torch.nn.Parameter(torch.empty(0, dtype=scale.dtype, device=wq.device), requires_grad=False)
-
-        def apply(self, layer, x, bias=None):
-            if x.dtype != torch.bfloat16 and x.is_cuda:
-                return torch.ops.barlink.w8a16_linear(x.to(torch.bfloat16), layer.bl_wq, layer.bl_scale,
-                                                      None if bias is None else bias.to(torch.bfloat16)).to(x.dtype)
-            return torch.ops.barlink.w8a16_linear(x, layer.bl_wq, layer.bl_scale, bias)
-
-    @register_quantization_config(NAME)
-    class BarlinkW8A16Config(QuantizationConfig):
-        def get_name(self):
-            return NAME
-
-        def get_supported_act_dtypes(self):
-            return [torch.bfloat16]
-
-        @classmethod
-        def get_min_capability(cls):
-            return 100  # the kernel is written for sm_100a
-
-        @staticmethod
-        def get_config_filenames():
-            return []  # nothing is read from the checkpoint: weights are quantised after loading
-
-        @classmethod
-        def from_config(cls, config):
-            return cls()
-
-        def get_quant_method(self, layer, prefix):
-            if isinstance(layer, LinearBase):
-                return BarlinkW8A16LinearMethod()
-            return None  # embeddings, the LM head's vocab embedding and attention stay as they are
-
+    BarlinkW8A16Config, BarlinkW8A16LinearMethod = qc.BarlinkW8A16Config, qc.BarlinkW8A16LinearMethod
     register.config_cls = BarlinkW8A16Config
     register.method_cls = BarlinkW8A16LinearMethod
     _registered = True
