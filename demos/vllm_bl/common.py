@@ -43,6 +43,12 @@ def load_hook():
         os.environ["PYTHONPATH"] = ROOT + os.pathsep + os.environ.get("PYTHONPATH", "")
         import vllm_barlink  # noqa: F401
         vllm_barlink.install()
+    elif "6" in os.environ.get("BL_SHIM_STEPS", "").split(","):
+        # the NCCL arm of an A/B run keeps this library's linears: only the quantization method is
+        # registered (workers get its classes, and with them the op, when they unpickle the configuration)
+        os.environ["PYTHONPATH"] = ROOT + os.pathsep + os.environ.get("PYTHONPATH", "")
+        from vllm_barlink import quant
+        quant.register()
     return "nccl" if os.environ.get("BL_SHIM_OFF") == "1" else "barlink"
 
 
