@@ -153,7 +153,10 @@ __device__ __forceinline__ float acc_f32(uint32_t bits, bool i8) {
   return i8 ? float(int32_t(bits)) : __uint_as_float(bits);
 }
 
-template <int BN, int CPS, bool W8, class Sink>
+// MODE = GemmShape::i8 (0 bf16/fp16 operands, 1 int8 operands, 2 int8 with per-group weight scales) is a
+// compile-time switch: with the int8 branches taken at run time the bf16 decode GEMMs measured 20-45 % slower
+// (gate/up at 64 tokens 64-73 us instead of 51-53), so each mode is a kernel of its own.
+template <int BN, int CPS, bool W8, int MODE = 0, class Sink>
 __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUtensorMap* tmap_b,
                                           const GemmShape& g, const Sink& sink, uint64_t hint_a,
                                           uint64_t hint_b) {
@@ -187,7 +190,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
       bulk_load_s(dst, g.tiled_base + (size_t(ta) * g.tiled_kblocks + kb) * S::kStageA, S::kStageA, bar,
                   hint_a);
     else
-      tma_load_2d_hint_s(dst, tmap_a, bar, kb * (g.i8 ? 2 * kTileK : kTileK), ta * kTileA, hint_a);
+      tma_load_2d_hint_s(dst, tmap_a, bar, kb * (MODE ? 2 * kTileK : kTileK), ta * kTileA, hint_a);
   };
   auto load_b = [&](uint32_t dst, uint32_t bar, int kb, int tb) {
     if (!W8 && g.tiled == 2) {
@@ -205,7 +208,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
                       S::kStageA, bar, hint_b);
       }
     } else {
-      tma_load_2d_hint_s(dst, tmap_b, bar, kb * (g.i8 ? 2 * kTileK : kTileK), tb * BN, hint_b);
+      tma_load_2d_hint_s(dst, tmap_b, bar, kb * (MODE ? 2 * kTileK : kTileK), tb * BN, hint_b);
     }
   };
 
@@ -251,7 +254,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
         const int kb0 = sp * kb_per;
         const int kb1 = min(g.kblocks, kb0 + kb_per);
         for (int kb = kb0; kb < kb1 && pre < S::kStages; kb += S::kKS, ++pre) {
-          const int nsub = min(S::kKS, kb1 - kb);  // k-blocks in this stage
+          const int nsub = S::kKS == 1 ? 1 : min(S::kKS, kb1 - kb);  // k-blocks in this stage
           mbar_expect_tx(&full_bar[pre], S::kTxBytes - (S::kKS - nsub) * S::kStageB);
           const uint32_t sa = ring + pre * S::kStageBytes;
           if (g.weights_in_a)
@@ -298,7 +301,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
             ok = false;
             break;
           }
-          const int nsub = min(S::kKS, kb1 - kb);
+          const int nsub = S::kKS == 1 ? 1 : min(S::kKS, kb1 - kb);
           const uint32_t sa = ring + stage * S::kStageBytes;
           const bool early = armed < pre;  // weight tile of this stage is already on its way
           if (!early) {
@@ -341,13 +344,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ----------------------------
     if (lane == 0) {
-      const uint32_t idesc = (!W8 && g.i8) ? umma_idesc_i8(kTileA, BN) : umma_idesc_f16(kTileA, BN, g.ab_fmt);
+      const uint32_t idesc = MODE ? umma_idesc_i8(kTileA, BN) : umma_idesc_f16(kTileA, BN, g.ab_fmt);
       int stage = 0, astage = 0;
       uint32_t phase = 0, aphase = 0;
       uint32_t tphase[2] = {0, 0};
       int it = 0;
       int gcount = 0;  // grouped int8: k-blocks issued so far (selects the accumulator buffer)
-      const bool grouped = !W8 && g.i8 == 2;
+      constexpr bool grouped = MODE == 2;
       bool ok = true;
       for (int u = blockIdx.x; u < units && ok; u += gridDim.x, ++it) {
         const int tile = u / g.splits, sp = u - tile * g.splits;
@@ -361,7 +364,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
         }
         uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
         for (int kb = kb0; kb < kb1 && ok; kb += S::kKS) {
-          const int nsub = min(S::kKS, kb1 - kb);
+          const int nsub = S::kKS == 1 ? 1 : min(S::kKS, kb1 - kb);
           const uint32_t sa = ring + stage * S::kStageBytes;
           if (!W8 && !mbar_wait_bounded(&full_bar[stage], phase, s_abort)) {
             ok = false;
@@ -394,7 +397,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
 #pragma unroll
             for (int k = 0; k < kTileK / 16; ++k) {
               // +32 bytes along K inside the swizzle atom = +2 in the address field
-              if (!W8 && g.i8)
+              if constexpr (MODE != 0)
                 umma_i8_ss(d_tmem, da + uint64_t(2 * k), db + uint64_t(2 * k), idesc,
                            ((!grouped && kb + sb > kb0) || k > 0) ? 1u : 0u);
               else
@@ -448,7 +451,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
       const int grow = (tile / g.tiles_b) * kTileA + row;
       const __half* gs = (g.gscale && grow < g.ra) ? g.gscale + size_t(grow) * g.gs_groups : nullptr;
       for (int kb = kb0; kb < kb1 && ok; kb += S::kKS, ++nst) {
-        const int nsub = min(S::kKS, kb1 - kb);
+        const int nsub = S::kKS == 1 ? 1 : min(S::kKS, kb1 - kb);
         if ((nst & 1) != grp) {
           nkb += nsub;
           continue;
@@ -510,16 +513,16 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap* tmap_a, const CUten
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int row = q * 32 + lane;
     const int et = threadIdx.x - 64;  // 0..127
-    const bool i8 = !W8 && g.i8;
+    constexpr bool i8 = MODE != 0;
     uint32_t tphase[2] = {0, 0};
     int it = 0;
-    int gcount = 0;  // grouped int8: k-blocks drained so far
+    [[maybe_unused]] int gcount = 0;  // grouped int8: k-blocks drained so far
     pdl_wait();  // outputs, residuals and the split-K scratch belong to earlier kernels until now
     for (int u = blockIdx.x; u < units; u += gridDim.x, ++it) {
       const int tile = u / g.splits, sp = u - tile * g.splits;
       const int ta = tile / g.tiles_b, tb = tile - ta * g.tiles_b;
-      if constexpr (!W8 && BN <= 64) {
-        if (g.i8 == 2) {
+      if constexpr (MODE == 2) {
+        {
           // one accumulator per k-block: acc * scale[row][group] summed in registers
           const int kb0 = sp * kb_per, kb1 = min(g.kblocks, kb0 + kb_per);
           const int grow = ta * kTileA + row;

@@ -204,6 +204,15 @@ __global__ void __launch_bounds__(kGemmThreads, CPS)
   gemm_body<BN, CPS, false>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
 }
 
+// int8 operands (GemmShape::i8 = MODE: 1 plain, 2 per-group weight scales with one accumulator per k-block)
+template <int BN, int MODE>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    k_gemm_i8(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+              GemmShape g, LocalSink<BN> sink, uint64_t hint_a, uint64_t hint_b) {
+  static_assert(MODE == 1 || (MODE == 2 && BN <= 64), "the per-group accumulators live in registers");
+  gemm_body<BN, 1, false, MODE>(&tmap_a, &tmap_b, g, sink, hint_a, hint_b);
+}
+
 // Epilogue of the split-K decode path: every k-split stores its raw fp32
 // partial tile to slab[split][token][feature]; the kernel that consumes the
 // linear's output (add+RMSNorm, RoPE+KV write, the fused all-reduce) sums the
@@ -617,8 +626,30 @@ static int launch_gemm(const blGemmArgs& a, int splits_want, cudaStream_t st, ch
       }
       attr_set = true;
     }
-    e = launch_k(k_gemm<BN, CPS>, dim3(grid), dim3(kGemmThreads), size_t(S::kBytes), st, ta, tb, g,
-                 sink, a.swap ? hint_w : hint_x, a.swap ? hint_x : hint_w);
+    bool done = false;
+    if (g.i8) {
+      using S1 = GemmSmem<BN, 1>;
+      auto go = [&](auto kern) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S1::kBytes);
+        if (e == cudaSuccess)
+          e = launch_k(kern, dim3(grid), dim3(kGemmThreads), size_t(S1::kBytes), st, ta, tb, g, sink,
+                       a.swap ? hint_w : hint_x, a.swap ? hint_x : hint_w);
+      };
+      if (g.i8 == 1) {
+        go(k_gemm_i8<BN, 1>);
+        done = true;
+      } else if constexpr (BN <= 64) {
+        go(k_gemm_i8<BN, 2>);
+        done = true;
+      }
+      if (!done) {
+        set_err(err, errlen, "barlink: per-group int8 scales need a tile of at most 64 tokens");
+        return -1;
+      }
+    }
+    if (!done)
+      e = launch_k(k_gemm<BN, CPS>, dim3(grid), dim3(kGemmThreads), size_t(S::kBytes), st, ta, tb, g,
+                   sink, a.swap ? hint_w : hint_x, a.swap ? hint_x : hint_w);
   }
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) {
