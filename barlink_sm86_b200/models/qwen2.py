@@ -29,10 +29,11 @@ from ..parallel.plan import gather_head_cols, gather_heads
 
 # BL_DLIN when the environment does not set it: "auto" = the folded-collective decode path whenever
 # there is more than one rank, "0" = the k-split GEMM + all-reduce kernel path, "tuned" = the folded
-# path at the tensor-parallel degrees where it measured faster on B200s (7B shape, batch 64:
-# 4 ranks 2.73 against 2.81 ms per step; slower at 1, 2 and 8 ranks: 4.93 / 4.26, 3.87 / 3.41, 2.65 / 2.53)
+# path at the tensor-parallel degrees listed in DLIN_TUNED_WORLDS.  Measured on B200s (7B shape,
+# batch 64, ms per step, folded / k-split): 4.93 / 4.26 on one GPU, 3.87 / 3.41 on two, 2.72 / 2.56 on
+# four, 2.65 / 2.53 on eight: the k-split path wins everywhere, so the list is empty.
 DLIN_DEFAULT = "tuned"
-DLIN_TUNED_WORLDS = (4,)
+DLIN_TUNED_WORLDS = ()
 
 
 @dataclass
