@@ -30,10 +30,10 @@ from ..parallel.plan import gather_head_cols, gather_heads
 # BL_DLIN when the environment does not set it: "auto" = the folded-collective decode path whenever
 # there is more than one rank, "0" = the k-split GEMM + all-reduce kernel path, "tuned" = the folded
 # path at the tensor-parallel degrees listed in DLIN_TUNED_WORLDS.  Measured on B200s (7B shape,
-# batch 64, ms per step, folded / k-split): 4.93 / 4.26 on one GPU, 3.87 / 3.41 on two, 2.72 / 2.56 on
-# four, 2.65 / 2.36 on eight: the k-split path wins everywhere, so the list is empty.
+# batch 64, ms per step, folded / k-split): 4.93 / 4.30 on one GPU, 3.31 / 3.44 on two, 2.72 / 2.56 on
+# four, 2.65 / 2.36 on eight: the folded path pays at two ranks only.
 DLIN_DEFAULT = "tuned"
-DLIN_TUNED_WORLDS = ()
+DLIN_TUNED_WORLDS = (2,)
 
 
 @dataclass
