@@ -136,12 +136,13 @@ def main():
 
     tflops = model.flops_per_forward(a.batch, a.img_tokens, a.txt_tokens) / (mean * 1e-3) / 1e12
     mem = 0 if cpu else torch.cuda.max_memory_allocated(dev) / (1 << 30)
-    print("[tp=%d rank=%d %s] load=%.1fs | %d steps: mean=%.1f ms/step min=%.1f max=%.1f | %.0f TFLOP/s whole job | "
-          "%d kernels/step | peak_mem=%.1f GiB%s"
-          % (world, rank, a.backend if world > 1 else "local", load_s, a.steps, mean, min(times), max(times),
-             tflops, launches, mem,
-             "" if sec_per_image is None else " | %d-step sampler: %.2f s/image" % (a.denoise, sec_per_image)),
-          flush=True)
+    # one write per line: the ranks share the launcher's pipe, and a line written in two pieces gets interleaved
+    sys.stdout.write("[tp=%d rank=%d %s] load=%.1fs | %d steps: mean=%.1f ms/step min=%.1f max=%.1f | %.0f TFLOP/s whole job | "
+                     "%d kernels/step | peak_mem=%.1f GiB%s\n"
+                     % (world, rank, a.backend if world > 1 else "local", load_s, a.steps, mean, min(times), max(times),
+                        tflops, launches, mem,
+                        "" if sec_per_image is None else " | %d-step sampler: %.2f s/image" % (a.denoise, sec_per_image)))
+    sys.stdout.flush()
 
     tag = a.tag or ("tp%d" % world)
     if rank == 0:
